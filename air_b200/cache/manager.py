@@ -1,0 +1,279 @@
+"""The cache manager: pages of keys and values with a block table per request, and slots
+for per-request state of fixed size.
+
+AIR's CUDA cache allocates a device page per request on demand, all layers in one page,
+and keeps a table of page pointers per sequence (src/cuda/cuda_backend.cu:1186-1433).  Here
+the memory is one slab per layer made at start, pages are numbers, and:
+
+* Runs of layers with the same need (kv heads, head size, window) form a *group*.  A group
+  has its own pool of pages and its own block table per request; page n of a group is row
+  n of every run's slab in that group.
+* A page belongs to one request from `reserve` until the request is closed, or, in a group
+  with a window, until every key in it is older than the window of any future query.
+  Freed pages go back on the pool's stack and are handed out again at once.
+* `reserve` for a batch either gets every page the batch needs or changes nothing.
+* A request's length advances only at `commit`, after the step has succeeded
+  (AIR: begin_transaction / commit_kv / rollback, src/cuda/cuda_backend.cu:1397-1432, 2291-2298).
+* A request also holds one slot index; every run that keeps a fixed-size state has a tensor
+  [slots, *shape] that is zeroed at the slot's row when the request opens.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..parts.base import PagedKV, SlotState
+
+
+class OutOfPages(RuntimeError):
+    """The pool of a group cannot hold what a step needs.  Nothing was changed."""
+
+
+class CacheError(RuntimeError):
+    pass
+
+
+class PagePool:
+    """Page numbers 0..n-1 with an owner each.  LIFO: the page freed last is reused first."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self._free: List[int] = list(range(num_pages - 1, -1, -1))
+        self._owner: List[Optional[Hashable]] = [None] * num_pages
+        self.peak_used = 0
+
+    @property
+    def free_pages(self) -> int:
+        return len(self._free)
+
+    @property
+    def used_pages(self) -> int:
+        return self.num_pages - len(self._free)
+
+    def take(self, owner: Hashable) -> int:
+        if owner is None:
+            raise CacheError("a page needs an owner")
+        if not self._free:
+            raise OutOfPages("out of KV pages")
+        page = self._free.pop()
+        if self._owner[page] is not None:
+            raise CacheError(f"page {page} was on the free stack while owned by {self._owner[page]!r}")
+        self._owner[page] = owner
+        self.peak_used = max(self.peak_used, self.used_pages)
+        return page
+
+    def give(self, page: int, owner: Hashable) -> None:
+        if not (0 <= page < self.num_pages):
+            raise CacheError(f"page {page} does not exist")
+        if self._owner[page] is None:
+            raise CacheError(f"page {page} is freed twice")
+        if self._owner[page] != owner:
+            raise CacheError(f"page {page} belongs to {self._owner[page]!r}, not to {owner!r}")
+        self._owner[page] = None
+        self._free.append(page)
+
+    def owner(self, page: int):
+        return self._owner[page]
+
+    def check(self) -> None:
+        """No page lost, none held twice: free and owned pages partition the pool."""
+        free = set(self._free)
+        if len(free) != len(self._free):
+            raise CacheError("a page is on the free stack twice")
+        for p in range(self.num_pages):
+            if (p in free) == (self._owner[p] is not None):
+                raise CacheError(f"page {p} is {'both free and owned' if p in free else 'neither free nor owned'}")
+
+
+@dataclass
+class PagedKVView:
+    """What a mixer gets for a PagedKV need: its slab [pages, 2, kv_heads, page_tokens, head_dim]
+    and the index of its group (for the step's block table)."""
+    kv: Optional[torch.Tensor]
+    group: int
+    need: PagedKV
+
+
+@dataclass
+class SlotStateView:
+    """What a mixer gets for a SlotState need: [slots, *shape]; row = the request's slot."""
+    state: Optional[torch.Tensor]
+    need: SlotState
+
+
+@dataclass
+class Group:
+    need: PagedKV
+    pool: PagePool
+    runs: List[int] = field(default_factory=list)
+
+
+@dataclass
+class Sequence_:
+    request: Hashable
+    slot: int
+    length: int = 0                      # committed tokens
+    pages: List[List[int]] = field(default_factory=list)  # per group: page of block b, or -1 once given back
+
+
+class CacheManager:
+    """needs_per_run[i]: the needs of the i-th run of the order list (empty for a run that
+    reads another run's cache).  allocate=False builds the bookkeeping without device memory
+    (for tests of the bookkeeping)."""
+
+    def __init__(self, needs_per_run: Sequence[Sequence[object]], page_tokens: int, num_pages: int,
+                 max_requests: int, dtype: torch.dtype = torch.float32, device="cpu", allocate: bool = True):
+        if page_tokens <= 0 or page_tokens % 16:
+            raise CacheError(f"page size {page_tokens} must be a positive multiple of 16")
+        if num_pages <= 0:
+            raise CacheError("the pool needs at least one page")
+        self.page_tokens, self.num_pages, self.max_requests = page_tokens, num_pages, max_requests
+        self.dtype, self.device = dtype, device
+        self.groups: List[Group] = []
+        self._views: List[Tuple[object, ...]] = []
+        self._state_tensors: List[torch.Tensor] = []
+        for run, needs in enumerate(needs_per_run):
+            views = []
+            for need in needs:
+                if isinstance(need, PagedKV):
+                    g = self._group_of(need)
+                    self.groups[g].runs.append(run)
+                    kv = None
+                    if allocate:
+                        kv = torch.zeros((num_pages, 2, need.kv_heads, page_tokens, need.head_dim),
+                                         dtype=dtype, device=device)
+                    views.append(PagedKVView(kv, g, need))
+                elif isinstance(need, SlotState):
+                    st = None
+                    if allocate:
+                        st = torch.zeros((max_requests,) + tuple(need.shape), dtype=getattr(torch, need.dtype),
+                                         device=device)
+                        self._state_tensors.append(st)
+                    views.append(SlotStateView(st, need))
+                else:
+                    raise CacheError(f"run {run}: unknown cache need {need!r}")
+            self._views.append(tuple(views))
+        self._free_slots = list(range(max_requests - 1, -1, -1))
+        self.sequences: Dict[Hashable, Sequence_] = {}
+
+    def _group_of(self, need: PagedKV) -> int:
+        for i, g in enumerate(self.groups):
+            if g.need == need:
+                return i
+        self.groups.append(Group(need, PagePool(self.num_pages)))
+        return len(self.groups) - 1
+
+    # ------------------------------------------------------------------ what mixers see
+    def views(self, run: int):
+        return self._views[run]
+
+    # ------------------------------------------------------------------ requests
+    def open(self, request: Hashable) -> Sequence_:
+        if request in self.sequences:
+            raise CacheError(f"request {request!r} is already open")
+        if not self._free_slots:
+            raise CacheError(f"all {self.max_requests} request slots are in use")
+        slot = self._free_slots.pop()
+        for st in self._state_tensors:
+            st[slot].zero_()
+        seq = Sequence_(request, slot, 0, [[] for _ in self.groups])
+        self.sequences[request] = seq
+        return seq
+
+    def close(self, request: Hashable) -> None:
+        seq = self.sequences.pop(request, None)
+        if seq is None:
+            raise CacheError(f"request {request!r} is not open")
+        for g, pages in zip(self.groups, seq.pages):
+            for p in pages:
+                if p >= 0:
+                    g.pool.give(p, request)
+        self._free_slots.append(seq.slot)
+
+    def pages_needed(self, tokens: int) -> int:
+        return -(-tokens // self.page_tokens)
+
+    def _first_live_block(self, need: PagedKV, length: int) -> int:
+        """Blocks below this hold only keys that no query at position >= length can see."""
+        if need.window is None:
+            return 0
+        return max(0, length - need.window + 1) // self.page_tokens
+
+    def reserve(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
+        """Makes room for `n` more tokens of each request in the batch: all of it or none."""
+        taken: List[Tuple[int, Hashable, int]] = []  # (group, request, blocks appended)
+        try:
+            for request, n in batch:
+                seq = self.sequences[request]
+                want = self.pages_needed(seq.length + n)
+                for gi, g in enumerate(self.groups):
+                    pages = seq.pages[gi]
+                    while len(pages) < want:
+                        pages.append(g.pool.take(request))
+                        taken.append((gi, request, 1))
+        except OutOfPages:
+            for gi, request, _ in reversed(taken):
+                page = self.sequences[request].pages[gi].pop()
+                self.groups[gi].pool.give(page, request)
+            raise
+
+    def commit(self, request: Hashable, n: int) -> None:
+        """The step that wrote `n` more tokens of the request has succeeded."""
+        seq = self.sequences[request]
+        seq.length += n
+        if self.groups and seq.length > len(seq.pages[0]) * self.page_tokens:
+            raise CacheError(f"request {request!r} holds fewer pages than its length needs")
+        for gi, g in enumerate(self.groups):
+            first = self._first_live_block(g.need, seq.length)
+            pages = seq.pages[gi]
+            for b in range(min(first, len(pages))):
+                if pages[b] >= 0:
+                    g.pool.give(pages[b], request)
+                    pages[b] = -1
+
+    def trim(self, request: Hashable) -> None:
+        """Gives back pages beyond the committed length (after a step that failed)."""
+        seq = self.sequences[request]
+        keep = self.pages_needed(seq.length)
+        for gi, g in enumerate(self.groups):
+            pages = seq.pages[gi]
+            while len(pages) > keep:
+                p = pages.pop()
+                if p >= 0:
+                    g.pool.give(p, request)
+
+    # ------------------------------------------------------------------ figures
+    def length(self, request: Hashable) -> int:
+        return self.sequences[request].length
+
+    def free_pages(self) -> int:
+        return min((g.pool.free_pages for g in self.groups), default=self.num_pages)
+
+    def used_pages(self, request: Optional[Hashable] = None) -> int:
+        if request is None:
+            return max((g.pool.used_pages for g in self.groups), default=0)
+        seq = self.sequences[request]
+        return max((sum(1 for p in pages if p >= 0) for pages in seq.pages), default=0)
+
+    def check(self) -> None:
+        for gi, g in enumerate(self.groups):
+            g.pool.check()
+            held = {}
+            for seq in self.sequences.values():
+                for p in seq.pages[gi]:
+                    if p < 0:
+                        continue
+                    if p in held:
+                        raise CacheError(f"page {p} of group {gi} is held by {held[p]!r} and {seq.request!r}")
+                    held[p] = seq.request
+                    if g.pool.owner(p) != seq.request:
+                        raise CacheError(f"page {p} of group {gi}: table and pool disagree on the owner")
+            if len(held) != g.pool.used_pages:
+                raise CacheError(f"group {gi}: {g.pool.used_pages - len(held)} pages are owned but in no table")
+        slots = [s.slot for s in self.sequences.values()]
+        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
+            raise CacheError("a request slot is held twice")
+        if len(slots) + len(self._free_slots) != self.max_requests:
+            raise CacheError("a request slot is lost")

@@ -1,0 +1,62 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions and the
+// dispatch from a run-time dtype code to a template argument.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define AIR_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with air_b200/csrc/ops.py
+#define AIR_F32 0
+#define AIR_BF16 1
+
+// error codes returned by the launchers (0 and CUDA's own codes apart)
+#define AIR_ERR_BAD_ARGUMENT 100001
+
+namespace air {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of
+// the additions depends only on the block size, never on the data or the grid.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int warps = (blockDim.x + 31) >> 5;
+    float total = 0.f;
+    for (int i = 0; i < warps; ++i) total += scratch[i];
+    return total;
+}
+
+}  // namespace air
+
+// Calls `body` with `T` bound to the element type of dtype code `code`.
+#define AIR_DISPATCH(code, T, ...)                                     \
+    do {                                                               \
+        if ((code) == AIR_F32) { using T = float; __VA_ARGS__; }       \
+        else if ((code) == AIR_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else return AIR_ERR_BAD_ARGUMENT;                              \
+    } while (0)

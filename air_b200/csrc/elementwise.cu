@@ -1,0 +1,210 @@
+// Embedding gather, residual-add + RMSNorm, bias + rotary + cache write, SiLU*mul.
+// All arithmetic is 32-bit; bfloat16 appears only where a value is read or stored.
+#include "common.cuh"
+
+namespace air {
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] as float32.  A token outside the table sets *status and
+// yields a row of zeros (the host checks ids first; this is the device's own guard).
+template <typename TT>
+__global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int E, int V, int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+    const TT* row = table + (size_t)(ok ? id : 0) * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)t * E + i] = ok ? to_float(row[i]) : 0.f;
+}
+
+// ---------------------------------------------------------------- add + RMSNorm
+// One block per row.  h (float32 residual stream) is updated in place with delta when
+// rows == nullptr; with rows the kernel reads h[rows[r]] (+ delta[rows[r]]) and leaves h
+// as it is.  out[r, i] = x_i * rsqrt(mean(x^2) + eps) * w_i, product order x*scale*w.
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                   const TW* __restrict__ w, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int E, float eps) {
+    __shared__ float scratch[32];
+    extern __shared__ float xrow[];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float x = h[src + i];
+        if (delta) x += to_float(delta[src + i]);
+        xrow[i] = x;
+        ss += x * x;
+    }
+    const float total = block_sum(ss, scratch);
+    const float scale = rsqrtf(total / (float)E + eps);
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        const float x = xrow[i];
+        if (!rows && delta) h[src + i] = x;
+        out[(size_t)r * E + i] = from_float<TO>(x * scale * to_float(w[i]));
+    }
+}
+
+// ---------------------------------------------------------------- bias + rotary + cache write
+// qkv [T, (H + 2K) d] is the output of the fused projection.  For every token: add the
+// bias, rotate the heads of q and k with the table's cos/sin of the token's position
+// (pairs (i, i + rot/2) of the first `rot` elements of a head), store q to q_out [T, H, d]
+// and k, v into the token's place in the pages: cache [page, 2, K, P, d].
+// table [positions, rot]: cos in the first rot/2 columns, sin in the second.
+template <typename TI, typename TB, typename TO>
+__global__ void qkv_rope_store_kernel(const TI* __restrict__ qkv, const TB* __restrict__ bias,
+                                      const float* __restrict__ table, int rot,
+                                      const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                      const int* __restrict__ block_table, int max_blocks,
+                                      TO* __restrict__ q_out, TO* __restrict__ cache,
+                                      int H, int K, int d, int P, int write_kv, int* status) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int width = (H + 2 * K) * d;
+    const TI* in = qkv + (size_t)t * width;
+    const int half = rot / 2;
+    TO* kdst = nullptr;
+    TO* vdst = nullptr;
+    if (write_kv) {
+        const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / P];
+        if (page < 0) {
+            if (threadIdx.x == 0 && status) atomicExch(status, 2);
+        } else {
+            kdst = cache + ((size_t)page * 2 * K * P + (size_t)(pos % P)) * d;
+            vdst = kdst + (size_t)K * P * d;
+        }
+    }
+    // one thread per (head, element below half or beyond the rotated part)
+    const int per_head = d - half;  // pairs in [0, half) plus unrotated tail [rot, d)
+    const int heads = H + 2 * K;
+    for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
+        const int head = idx / per_head;
+        const int j = idx % per_head;
+        const int base = head * d;
+        const bool is_v = head >= H + K;
+        if (!write_kv && head >= H) continue;
+        float a, b = 0.f;
+        bool pair = !is_v && j < half;
+        int i0, i1 = 0;
+        if (is_v) {
+            // values are not rotated: this thread copies element j and, if any, j + per_head
+            i0 = j;
+            i1 = j + per_head;
+            pair = i1 < d;
+        } else if (j < half) {
+            i0 = j;
+            i1 = j + half;
+        } else {
+            i0 = j + half;  // tail element beyond the rotated part
+        }
+        a = to_float(in[base + i0]);
+        if (bias) a += to_float(bias[base + i0]);
+        if (pair) {
+            b = to_float(in[base + i1]);
+            if (bias) b += to_float(bias[base + i1]);
+        }
+        if (!is_v && j < half) {
+            const float c = table[(size_t)pos * rot + j];
+            const float s = table[(size_t)pos * rot + half + j];
+            const float ra = a * c - b * s;
+            const float rb = a * s + b * c;
+            a = ra;
+            b = rb;
+        }
+        if (head < H) {
+            TO* dst = q_out + ((size_t)t * H + head) * d;
+            dst[i0] = from_float<TO>(a);
+            if (pair) dst[i1] = from_float<TO>(b);
+        } else if (kdst) {
+            const int kvh = is_v ? head - H - K : head - H;
+            TO* dst = (is_v ? vdst : kdst) + (size_t)kvh * P * d;
+            dst[i0] = from_float<TO>(a);
+            if (pair) dst[i1] = from_float<TO>(b);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+// in [T, 2I]: gate in the first I columns, up in the second.  out [T, I].
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx % I);
+        const float g = to_float(in[t * 2 * I + i]);
+        const float u = to_float(in[t * 2 * I + I + i]);
+        out[idx] = from_float<TO>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+// ---------------------------------------------------------------- conversions
+template <typename TI, typename TO>
+__global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_float<TO>(to_float(in[i]));
+}
+
+}  // namespace air
+
+using namespace air;
+
+AIR_API int air_embedding(const void* table, int table_dtype, const int* ids, float* out, int T, int E,
+                          int V, int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    AIR_DISPATCH(table_dtype, TT,
+                 embedding_kernel<TT><<<T, 256, 0, stream>>>((const TT*)table, ids, out, E, V, status));
+    return (int)cudaGetLastError();
+}
+
+AIR_API int air_add_rmsnorm(float* h, const void* delta, int delta_dtype, const void* w, int w_dtype,
+                            void* out, int out_dtype, const int* rows, int R, int E, float eps,
+                            cudaStream_t stream) {
+    if (R <= 0) return 0;
+    const size_t smem = (size_t)E * sizeof(float);
+    if (smem > 200 * 1024) return AIR_ERR_BAD_ARGUMENT;
+    const int threads = E >= 2048 ? 512 : 256;
+    AIR_DISPATCH(delta_dtype, TD, AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
+        auto kernel = add_rmsnorm_kernel<TD, TW, TO>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<R, threads, smem, stream>>>(h, (const TD*)delta, (const TW*)w, (TO*)out, rows, E, eps);
+    })));
+    return (int)cudaGetLastError();
+}
+
+AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, const void* bias, int bias_dtype,
+                               const float* table, int rot, const int* positions, const int* token_seq,
+                               const int* block_table, int max_blocks, void* q_out, void* cache,
+                               int out_dtype, int T, int H, int K, int d, int P, int write_kv,
+                               int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rot < 0 || rot > d || (rot & 1)) return AIR_ERR_BAD_ARGUMENT;
+    AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(bias_dtype, TB, AIR_DISPATCH(out_dtype, TO, {
+        qkv_rope_store_kernel<TI, TB, TO><<<T, 256, 0, stream>>>(
+            (const TI*)qkv, (const TB*)bias, table, rot, positions, token_seq, block_table, max_blocks,
+            (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
+    })));
+    return (int)cudaGetLastError();
+}
+
+AIR_API int air_silu_mul(const void* in, int in_dtype, void* out, int out_dtype, int T, int I,
+                         cudaStream_t stream) {
+    const size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(out_dtype, TO, {
+        silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, total);
+    }));
+    return (int)cudaGetLastError();
+}
+
+AIR_API int air_convert(const void* in, int in_dtype, void* out, int out_dtype, long long n,
+                        cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(out_dtype, TO, {
+        convert_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, (size_t)n);
+    }));
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,199 @@
+"""Python faces of the CUDA kernels.  Every function checks what it is given (device,
+dtype, shape, contiguity), launches on torch's current stream and raises on any error
+code.  There is no other implementation behind these functions: if the library cannot be
+built or loaded, or a tensor is not on a CUDA device, they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+_SIGNATURES = {
+    "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                        c_float, c_void_p],
+    "air_qkv_rope_store": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "air_convert": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
+    "air_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+}
+
+_fn = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _get(name):
+    f = _fn.get(name)
+    if f is None:
+        lib = build.library()
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[name]
+        f.restype = c_int
+        _fn[name] = f
+    return f
+
+
+def _check(code: int, name: str):
+    if code != 0:
+        if code == 100001:
+            raise KernelError(f"{name}: a size or dtype that the kernel does not take")
+        raise KernelError(f"{name}: CUDA error {code} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _req(t: torch.Tensor, name: str, dtypes=None, shape=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU implementation)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtypes is not None and t.dtype not in dtypes:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+    if shape is not None:
+        if t.dim() != len(shape) or any(s is not None and s != g for s, g in zip(shape, t.shape)):
+            raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+    return t
+
+
+_FLOATS = (torch.float32, torch.bfloat16)
+_I32 = (torch.int32,)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def embedding(table, ids, out, status=None):
+    """out[t] = table[ids[t]] as float32."""
+    V, E = table.shape
+    _req(table, "table", _FLOATS)
+    _req(ids, "ids", _I32, (out.shape[0],))
+    _req(out, "out", (torch.float32,), (None, E))
+    _check(_get("air_embedding")(table.data_ptr(), _DT[table.dtype], ids.data_ptr(), out.data_ptr(),
+                                 out.shape[0], E, V, _ptr(status), _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(h, delta, weight, eps, out, rows=None):
+    """Without rows: h += delta (in place, float32), out = rmsnorm(h) * weight.
+    With rows: out[r] = rmsnorm(h[rows[r]] + delta[rows[r]]) * weight, h unchanged."""
+    E = h.shape[-1]
+    _req(h, "h", (torch.float32,), (None, E))
+    if delta is not None:
+        _req(delta, "delta", _FLOATS, tuple(h.shape))
+    _req(weight, "weight", _FLOATS, (E,))
+    R = h.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _req(rows, "rows", _I32)
+    _req(out, "out", _FLOATS, (R, E))
+    _check(_get("air_add_rmsnorm")(h.data_ptr(), _ptr(delta), _DT[delta.dtype] if delta is not None else 0,
+                                   weight.data_ptr(), _DT[weight.dtype], out.data_ptr(), _DT[out.dtype],
+                                   _ptr(rows), R, E, float(eps), _stream()), "add_rmsnorm")
+    return out
+
+
+def qkv_rope_store(qkv, bias, table, positions, token_seq, block_table, q_out, cache, heads, kv_heads,
+                   head_dim, write_kv=True, status=None):
+    """Adds the bias, rotates q and k by the table's cos/sin of each token's position, writes
+    q to q_out [T, H, d] and k, v into the pages (cache [page, 2, K, P, d])."""
+    T = qkv.shape[0]
+    width = (heads + 2 * kv_heads) * head_dim
+    _req(qkv, "qkv", _FLOATS, (T, width))
+    if bias is not None:
+        _req(bias, "bias", _FLOATS, (width,))
+    rot = 0
+    if table is not None:
+        _req(table, "table", (torch.float32,))
+        rot = table.shape[1]
+        if rot > head_dim or rot % 2:
+            raise KernelError(f"rotary width {rot} does not fit head size {head_dim}")
+    _req(positions, "positions", _I32, (T,))
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(block_table, "block_table", _I32)
+    _req(q_out, "q_out", _FLOATS, (T, heads, head_dim))
+    _req(cache, "cache", (q_out.dtype,), (None, 2, kv_heads, None, head_dim))
+    _check(_get("air_qkv_rope_store")(
+        qkv.data_ptr(), _DT[qkv.dtype], _ptr(bias), _DT[bias.dtype] if bias is not None else 0,
+        _ptr(table), rot, positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], q_out.data_ptr(), cache.data_ptr(), _DT[q_out.dtype], T, heads, kv_heads,
+        head_dim, cache.shape[3], 1 if write_kv else 0, _ptr(status), _stream()), "qkv_rope_store")
+    return q_out
+
+
+def silu_mul(gate_up, out):
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    T, I = out.shape
+    _req(gate_up, "gate_up", _FLOATS, (T, 2 * I))
+    _req(out, "out", _FLOATS)
+    _check(_get("air_silu_mul")(gate_up.data_ptr(), _DT[gate_up.dtype], out.data_ptr(), _DT[out.dtype], T, I,
+                                _stream()), "silu_mul")
+    return out
+
+
+def convert(src, out):
+    _req(src, "src", _FLOATS)
+    _req(out, "out", _FLOATS, tuple(src.shape))
+    _check(_get("air_convert")(src.data_ptr(), _DT[src.dtype], out.data_ptr(), _DT[out.dtype], src.numel(),
+                               _stream()), "convert")
+    return out
+
+
+def gemm_f32(a, w, bias, out):
+    """out[M, N] = a[M, K] @ w[N, K]^T + bias, all float32, on the CUDA cores."""
+    M, K = a.shape
+    N = w.shape[0]
+    _req(a, "a", (torch.float32,))
+    _req(w, "w", (torch.float32,), (N, K))
+    if bias is not None:
+        _req(bias, "bias", (torch.float32,), (N,))
+    _req(out, "out", (torch.float32,), (M, N))
+    _check(_get("air_gemm_f32")(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, _stream()),
+           "gemm_f32")
+    return out
+
+
+def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window, scale):
+    T, H, d = q.shape
+    _req(q, "q", _FLOATS)
+    _req(cache, "cache", (q.dtype,), (None, 2, None, None, d))
+    _req(block_table, "block_table", _I32)
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(positions, "positions", _I32, (T,))
+    _req(out, "out", (q.dtype,), (T, H, d))
+    if d % 16 or d > 256:
+        raise KernelError(f"head size {d}: the attention kernels take multiples of 16 up to 256")
+    _check(_get("air_paged_attention_ref")(
+        q.data_ptr(), cache.data_ptr(), _DT[q.dtype], block_table.data_ptr(), block_table.shape[1],
+        token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), T, H, cache.shape[2], d, cache.shape[3],
+        int(window or 0), float(scale), _stream()), "paged_attention_ref")
+    return out
+
+
+def sample(logits, temperature, uniform, out, status=None):
+    """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or temperature is None), else the
+    index drawn from softmax(logits[r] / temperature[r]) with the uniform number uniform[r]."""
+    R, V = logits.shape
+    _req(logits, "logits", (torch.float32,))
+    if temperature is not None:
+        _req(temperature, "temperature", (torch.float32,), (R,))
+        _req(uniform, "uniform", (torch.float32,), (R,))
+    _req(out, "out", _I32, (R,))
+    _check(_get("air_sample")(logits.data_ptr(), _ptr(temperature), _ptr(uniform), out.data_ptr(), R, V,
+                              _ptr(status), _stream()), "sample")
+    return out

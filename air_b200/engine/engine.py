@@ -1,0 +1,167 @@
+"""The step function and what it stands on: a loaded model, its cache manager and the
+device context.  `Engine.step` is the only way tokens reach the model: generation, the
+scheduler and trace replay all call it.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+from ..config import load_config
+from ..parts import registry
+from ..parts.base import Runtime
+from ..weights.loader import load_tensors, random_tensors, write_model_folder
+from .batch import Entry, StepContext, build_context
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    try:
+        return _DTYPES[name]
+    except KeyError:
+        raise ValueError(f"dtype {name!r}: the engine computes in bfloat16 or float32") from None
+
+
+class StepError(RuntimeError):
+    """A step failed; no request's length has advanced."""
+
+
+@dataclass
+class EngineConfig:
+    """page_tokens: tokens per cache page.  max_tokens: how many tokens the cache pool holds
+    over all live requests (each request's count rounded up to whole pages).  max_requests:
+    live requests (state slots).  AIR: KvPolicy.page_tokens (include/air/execution.hpp:103-105)
+    and SchedulerConfig.max_active_requests (include/air/serving.hpp:46-62)."""
+    dtype: torch.dtype = torch.bfloat16
+    page_tokens: int = 64
+    max_tokens: int = 8192
+    max_requests: int = 8
+    device: str = "cuda:0"
+
+
+class Engine:
+    def __init__(self, model: Model, config: EngineConfig, model_config=None):
+        self.model, self.config, self.model_config = model, config, model_config
+        self.rt = model.rt
+        num_pages = max(1, -(-config.max_tokens // config.page_tokens))
+        self.cache = CacheManager(model.cache_needs(), config.page_tokens, num_pages, config.max_requests,
+                                  dtype=self.rt.dtype, device=self.rt.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        self.steps = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, folder: str, config: Optional[EngineConfig] = None) -> "Engine":
+        config = config or EngineConfig()
+        model_config = load_config(folder)
+        arch = registry.architecture(model_config.architecture)
+        model = Model(arch.build_spec(model_config))
+        device = _device(config.device)
+        rt = Runtime(device=device, dtype=parse_dtype(config.dtype), page_tokens=config.page_tokens)
+        tensors = load_tensors(folder, model.tensor_specs(), rt.dtype, device)
+        model.load(tensors, rt)
+        return cls(model, config, model_config)
+
+    @classmethod
+    def from_random(cls, model_config, seed: int = 0, config: Optional[EngineConfig] = None) -> "Engine":
+        """A model with seeded random weights drawn on the device, without files."""
+        config = config or EngineConfig()
+        if isinstance(model_config, dict):
+            model_config = load_config(model_config)
+        arch = registry.architecture(model_config.architecture)
+        model = Model(arch.build_spec(model_config))
+        device = _device(config.device)
+        rt = Runtime(device=device, dtype=parse_dtype(config.dtype), page_tokens=config.page_tokens)
+        model.load(random_tensors(model.tensor_specs(), seed, rt.dtype, device=device), rt)
+        return cls(model, config, model_config)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+        """Runs one batch: for each entry the request's next tokens (a portion of its prompt or
+        one decoded token, any mix).  Returns float32 logits [wanted places, vocab] on the
+        device, in the order of the entries and of their `want`.  A request is opened at its
+        first tokens.  On failure (OutOfPages, a token outside the vocabulary) nothing is
+        committed and pages taken for the step are given back."""
+        entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        vocab, limit = self.model.spec.vocab_size, self.model.spec.max_positions
+        seen = set()
+        for e in entries:
+            if e.request in seen:
+                raise StepError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.request!r} brings no tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < vocab):
+                    raise StepError("input token is outside model vocabulary")
+        opened = []
+        try:
+            for e in entries:
+                if e.request not in self.cache.sequences:
+                    self.cache.open(e.request)
+                    opened.append(e.request)
+                if self.cache.length(e.request) + len(e.tokens) > limit:
+                    raise StepError("model context length exceeded")
+            self.cache.reserve([(e.request, len(e.tokens)) for e in entries])
+        except Exception:
+            for r in opened:
+                self.cache.close(r)
+            raise
+        try:
+            ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+            logits = self.model.forward(ctx, self.cache)
+        except Exception:
+            for e in entries:
+                if e.request in opened:
+                    self.cache.close(e.request)
+                else:
+                    self.cache.trim(e.request)
+            raise
+        for e in entries:
+            self.cache.commit(e.request, len(e.tokens))
+        self.steps += 1
+        return logits
+
+    def finish(self, request: Hashable) -> None:
+        """The request is over: its pages and its slot are free for others."""
+        self.cache.close(request)
+
+    def check_status(self) -> None:
+        """Reads the device's error word (a synchronisation)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise StepError({1: "a token outside the vocabulary reached the embedding kernel",
+                             2: "a token was to be written to a page that its request does not hold",
+                             3: "non-finite logits"}.get(code, f"device status {code}"))
+
+
+def _device(name) -> torch.device:
+    device = torch.device(name)
+    if device.type != "cuda":
+        raise RuntimeError("air_b200 computes on a CUDA device only; there is no CPU path")
+    if not torch.cuda.is_available():
+        raise RuntimeError("air_b200: no CUDA device is available")
+    torch.cuda.set_device(device)
+    return device
+
+
+def write_random_model(folder: str, model_config, seed: int = 0, dtype="bfloat16") -> None:
+    """Random-weights mode: writes config.json and model.safetensors for a configuration and a
+    seed.  Weights and biases are N(0, 0.02), norm weights 1 + N(0, 0.02), drawn on the CPU
+    per tensor from (seed, tensor name) and rounded to `dtype`."""
+    if isinstance(model_config, dict):
+        model_config = load_config(model_config)
+    arch = registry.architecture(model_config.architecture)
+    model = Model(arch.build_spec(model_config))
+    tensors = random_tensors(model.tensor_specs(), seed, parse_dtype(dtype), device="cpu")
+    cfg = model_config.to_dict()
+    cfg["torch_dtype"] = "bfloat16" if parse_dtype(dtype) == torch.bfloat16 else "float32"
+    write_model_folder(folder, cfg, tensors)

@@ -1,0 +1,98 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import TensorSpec
+from .base import Mixer, PagedKV
+from .linear import Linear
+from .registry import register_mixer, POSITION_ENCODINGS
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    """q, k, v projections (with optional biases), position encoding of q and k, causal
+    softmax attention with scale 1/sqrt(head_dim) in which query head h reads kv head
+    floor(h * kv_heads / heads), output projection
+    (AIR: src/reference/reference_executor.cpp:74-138, 349-384).
+
+    params: hidden, heads, kv_heads, head_dim, qkv_bias, window (None: all keys),
+            position (a PartSpec of a position encoding).
+    Tensors: <prefix>{q,k,v}_proj.weight [heads*d | kv*d, hidden], <prefix>{q,k,v}_proj.bias
+    (absent tensors mean no bias, as in AIR: src/model/qwen2_contract.cpp:133-136),
+    <prefix>o_proj.weight [hidden, heads*d].
+
+    At load the three projections become one matrix [(heads + 2 kv) d, hidden].  One kernel
+    then adds the bias, rotates q and k and writes k and v into the request's pages; the
+    attention kernel reads keys and values only from the pages, for prompt portions and
+    decoded tokens alike."""
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.heads, self.kv_heads, self.head_dim = p["hidden"], p["heads"], p["kv_heads"], p["head_dim"]
+        self.window = p.get("window")
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        if self.heads % self.kv_heads:
+            raise ValueError("attention: heads must be a multiple of kv_heads")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ValueError(f"attention: head size {self.head_dim} is not a multiple of 16 up to 256")
+        pos = p["position"]
+        self.position = POSITION_ENCODINGS.get(pos.kind)(pos)
+
+    def cache_needs(self):
+        return (PagedKV(self.kv_heads, self.head_dim, self.window),)
+
+    def tensor_specs(self):
+        d, p = self.head_dim, self.prefix
+        specs = [TensorSpec(p + "q_proj.weight", (self.heads * d, self.hidden)),
+                 TensorSpec(p + "k_proj.weight", (self.kv_heads * d, self.hidden)),
+                 TensorSpec(p + "v_proj.weight", (self.kv_heads * d, self.hidden)),
+                 TensorSpec(p + "o_proj.weight", (self.hidden, self.heads * d))]
+        if self.qkv_bias:
+            specs += [TensorSpec(p + "q_proj.bias", (self.heads * d,), optional=True),
+                      TensorSpec(p + "k_proj.bias", (self.kv_heads * d,), optional=True),
+                      TensorSpec(p + "v_proj.bias", (self.kv_heads * d,), optional=True)]
+        return specs + self.position.tensor_specs()
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        p = self.prefix
+        ws = [tensors[p + f"{n}_proj.weight"] for n in "qkv"]
+        if len({w.dtype for w in ws}) != 1:
+            raise ValueError(f"{p}: q, k and v projections are stored in different precisions")
+        self.qkv = Linear(torch.cat(ws, dim=0).contiguous())
+        self.q_only = self.qkv.rows(0, self.heads * self.head_dim)
+        self.o = Linear(tensors[p + "o_proj.weight"])
+        self.bias = None
+        if any((p + f"{n}_proj.bias") in tensors for n in "qkv"):
+            parts = []
+            for n, rows in zip("qkv", (self.heads, self.kv_heads, self.kv_heads)):
+                b = tensors.get(p + f"{n}_proj.bias")
+                parts.append(b.to(torch.float32) if b is not None
+                             else torch.zeros(rows * self.head_dim, dtype=torch.float32, device=rt.device))
+            self.bias = torch.cat(parts).contiguous()
+        self.position.load(tensors, rt)
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+
+    def forward(self, x, ctx, cache, owns_cache=True):
+        (pages,) = cache
+        T = x.shape[0]
+        H, K, d = self.heads, self.kv_heads, self.head_dim
+        rt = self.rt
+        if owns_cache:
+            qkv = self.qkv(x, torch.float32)
+        else:
+            # this run reads another run's keys and values: only q is computed
+            qkv = torch.zeros((T, (H + 2 * K) * d), dtype=torch.float32, device=x.device)
+            qkv[:, : H * d] = self.q_only(x, torch.float32)
+        q = torch.empty((T, H, d), dtype=rt.dtype, device=x.device)
+        bt = ctx.block_tables[pages.group]
+        ops.qkv_rope_store(qkv, self.bias, self.position.table(), ctx.positions, ctx.token_seq, bt, q, pages.kv,
+                           H, K, d, write_kv=owns_cache, status=ctx.status)
+        out = torch.empty_like(q)
+        ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
+        return self.o(out.view(T, H * d), torch.float32)

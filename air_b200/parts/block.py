@@ -1,0 +1,42 @@
+"""How the parts of one layer stand around the residual stream."""
+from __future__ import annotations
+
+from .registry import register_block, MIXERS, FEED_FORWARDS, NORMS
+from .spec import BlockSpec
+
+
+@register_block("pre_norm")
+class PreNormBlock:
+    """h = h + mixer(norm1(h)); h = h + feed_forward(norm2(h))
+    (AIR: src/reference/reference_executor.cpp:343-413).
+
+    The residual stream h is float32.  Each addition is fused into the norm that follows
+    it: the block receives the previous block's output still pending, and hands its own
+    feed-forward output on in the same way; the model's final norm adds the last one."""
+
+    def __init__(self, spec: BlockSpec):
+        self.spec = spec
+        p, n = spec.prefix, spec.names
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, p + n["mixer_norm"])
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, p + n["mixer"])
+        self.ff_norm = NORMS.get(spec.feed_forward_norm.kind)(spec.feed_forward_norm, p + n["feed_forward_norm"])
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, p + n["feed_forward"])
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward)
+
+    def tensor_specs(self):
+        return [s for part in self.parts() for s in part.tensor_specs()]
+
+    def load(self, tensors, rt):
+        for part in self.parts():
+            part.load(tensors, rt)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def forward(self, h, pending, ctx, cache, owns_cache=True):
+        x = self.mixer_norm.forward(h, pending)
+        a = self.mixer.forward(x, ctx, cache, owns_cache)
+        x = self.ff_norm.forward(h, a)
+        return h, self.feed_forward.forward(x, ctx)
