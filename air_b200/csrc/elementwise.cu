@@ -5,13 +5,17 @@
 namespace air {
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] = table[ids[t], :] as float32.  A token outside the table sets *status and
+// out[t, :] = table[ids[t], :] as float32.  A negative id -(s+1) stands for "the token that
+// was sampled last for state slot s": it is read from last_token[s], so a decoded token can
+// be fed back without passing through the host.  A token outside the table sets *status and
 // yields a row of zeros (the host checks ids first; this is the device's own guard).
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int E, int V, int* status) {
+                                 const int* __restrict__ last_token, float* __restrict__ out, int E, int V,
+                                 int* status) {
     const int t = blockIdx.x;
-    const int id = ids[t];
+    int id = ids[t];
+    if (id < 0 && last_token) id = last_token[-id - 1];
     const bool ok = id >= 0 && id < V;
     if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
     const TT* row = table + (size_t)(ok ? id : 0) * E;
@@ -150,11 +154,11 @@ __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, 
 
 using namespace air;
 
-AIR_API int air_embedding(const void* table, int table_dtype, const int* ids, float* out, int T, int E,
-                          int V, int* status, cudaStream_t stream) {
+AIR_API int air_embedding(const void* table, int table_dtype, const int* ids, const int* last_token, float* out,
+                          int T, int E, int V, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
-    AIR_DISPATCH(table_dtype, TT,
-                 embedding_kernel<TT><<<T, 256, 0, stream>>>((const TT*)table, ids, out, E, V, status));
+    AIR_DISPATCH(table_dtype, TT, embedding_kernel<TT><<<T, 256, 0, stream>>>((const TT*)table, ids, last_token,
+                                                                               out, E, V, status));
     return (int)cudaGetLastError();
 }
 

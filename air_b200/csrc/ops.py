@@ -16,7 +16,7 @@ _DT = {torch.float32: 0, torch.bfloat16: 1}
 c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
 _SIGNATURES = {
-    "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "air_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                         c_float, c_void_p],
     "air_qkv_rope_store": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
@@ -26,10 +26,11 @@ _SIGNATURES = {
     "air_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
-    "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
 _fn = {}
+launches = 0   # kernels of this library launched so far (each wrapper launches one)
 
 
 class KernelError(RuntimeError):
@@ -48,6 +49,8 @@ def _get(name):
 
 
 def _check(code: int, name: str):
+    global launches
+    launches += 1
     if code != 0:
         if code == 100001:
             raise KernelError(f"{name}: a size or dtype that the kernel does not take")
@@ -79,14 +82,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
-def embedding(table, ids, out, status=None):
-    """out[t] = table[ids[t]] as float32."""
+def embedding(table, ids, out, status=None, last_token=None):
+    """out[t] = table[ids[t]] as float32; an id -(s+1) is replaced by last_token[s]."""
     V, E = table.shape
     _req(table, "table", _FLOATS)
     _req(ids, "ids", _I32, (out.shape[0],))
     _req(out, "out", (torch.float32,), (None, E))
-    _check(_get("air_embedding")(table.data_ptr(), _DT[table.dtype], ids.data_ptr(), out.data_ptr(),
-                                 out.shape[0], E, V, _ptr(status), _stream()), "embedding")
+    if last_token is not None:
+        _req(last_token, "last_token", _I32)
+    _check(_get("air_embedding")(table.data_ptr(), _DT[table.dtype], ids.data_ptr(), _ptr(last_token),
+                                 out.data_ptr(), out.shape[0], E, V, _ptr(status), _stream()), "embedding")
     return out
 
 
@@ -185,15 +190,19 @@ def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window
     return out
 
 
-def sample(logits, temperature, uniform, out, status=None):
+def sample(logits, temperature, uniform, out, status=None, slots=None, last_token=None):
     """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or temperature is None), else the
-    index drawn from softmax(logits[r] / temperature[r]) with the uniform number uniform[r]."""
+    index drawn from softmax(logits[r] / temperature[r]) with the uniform number uniform[r].
+    With slots and last_token, also last_token[slots[r]] = out[r]."""
     R, V = logits.shape
     _req(logits, "logits", (torch.float32,))
     if temperature is not None:
         _req(temperature, "temperature", (torch.float32,), (R,))
         _req(uniform, "uniform", (torch.float32,), (R,))
     _req(out, "out", _I32, (R,))
-    _check(_get("air_sample")(logits.data_ptr(), _ptr(temperature), _ptr(uniform), out.data_ptr(), R, V,
-                              _ptr(status), _stream()), "sample")
+    if slots is not None:
+        _req(slots, "slots", _I32, (R,))
+        _req(last_token, "last_token", _I32)
+    _check(_get("air_sample")(logits.data_ptr(), _ptr(temperature), _ptr(uniform), out.data_ptr(), _ptr(slots),
+                              _ptr(last_token), R, V, _ptr(status), _stream()), "sample")
     return out

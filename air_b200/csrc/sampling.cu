@@ -13,11 +13,14 @@ __device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int o
 
 // temperature == nullptr or temperature[r] <= 0: greedy.  Otherwise the drawn index is the
 // first i (in index order) with sum_{j<=i} w_j >= u * sum_j w_j, w_j = exp((x_j - max) / T).
+// With slots and last_token the chosen index is also stored at last_token[slots[r]], where the
+// embedding kernel of the next step finds it.
 // A row whose maximum is not finite sets *status (AIR flags non-finite logits on the device,
 // src/cuda/cuda_backend.cu:621-624).
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
-              const float* __restrict__ uniform, int* __restrict__ out, int V, int* status) {
+              const float* __restrict__ uniform, int* __restrict__ out, const int* __restrict__ slots,
+              int* __restrict__ last_token, int V, int* status) {
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ float partial[SAMPLE_THREADS];
@@ -51,7 +54,10 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __syncthreads();
     const float temp = temperature ? temperature[r] : 0.f;
     if (!(temp > 0.f)) {
-        if (tid == 0) out[r] = s_arg;
+        if (tid == 0) {
+            out[r] = s_arg;
+            if (slots && last_token) last_token[slots[r]] = s_arg;
+        }
         return;
     }
     // contiguous chunk per thread, so that the walk is in index order
@@ -80,15 +86,17 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
             if (cum >= target) break;
         }
         out[r] = chosen;
+        if (slots && last_token) last_token[slots[r]] = chosen;
     }
 }
 
 }  // namespace air
 
-AIR_API int air_sample(const float* logits, const float* temperature, const float* uniform, int* out, int R,
-                       int V, int* status, cudaStream_t stream) {
+AIR_API int air_sample(const float* logits, const float* temperature, const float* uniform, int* out,
+                       const int* slots, int* last_token, int R, int V, int* status, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return AIR_ERR_BAD_ARGUMENT;
-    air::sample_kernel<<<R, air::SAMPLE_THREADS, 0, stream>>>(logits, temperature, uniform, out, V, status);
+    air::sample_kernel<<<R, air::SAMPLE_THREADS, 0, stream>>>(logits, temperature, uniform, out, slots,
+                                                                    last_token, V, status);
     return (int)cudaGetLastError();
 }

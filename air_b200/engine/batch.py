@@ -16,10 +16,13 @@ from typing import Hashable, List, Optional, Sequence, Tuple
 import torch
 
 
+LAST_SAMPLED = -1   # as a token: "the token that the device sampled last for this request"
+
+
 @dataclass
 class Entry:
     request: Hashable
-    tokens: Sequence[int]
+    tokens: Sequence[int]        # token ids; [LAST_SAMPLED] feeds back the device's last choice
     want: Sequence[int] = ()     # places among `tokens` whose logits are wanted
 
 
@@ -34,6 +37,7 @@ class StepContext:
     kv_len: torch.Tensor           # [S] int32: length of the request after this step
     slots: torch.Tensor            # [S] int32: state slot of the request
     logit_rows: torch.Tensor       # [R] int32: flat indices of the tokens whose logits are wanted
+    row_slots: torch.Tensor        # [R] int32: state slot of the request of each wanted row
     block_tables: List[torch.Tensor]   # per group: [S, max_blocks] int32, -1 where no page is held
     status: Optional[torch.Tensor]     # [1] int32, set by kernels that meet an impossible index
     # host copies, for parts that plan on the host
@@ -43,6 +47,7 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     all_decode: bool = False
+    last_token: Optional[torch.Tensor] = None   # [slots] int32: the device's last choice per request
 
 
 def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepContext:
@@ -56,16 +61,18 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
     kv_len: List[int] = []
     slots: List[int] = []
     rows: List[int] = []
+    row_slots: List[int] = []
     for s, e in enumerate(entries):
         seq = cache.sequences[e.request]
         n = len(e.tokens)
-        ids.extend(int(t) for t in e.tokens)
+        ids.extend(int(t) if int(t) >= 0 else -(seq.slot + 1) for t in e.tokens)
         pos.extend(range(seq.length, seq.length + n))
         tseq.extend([s] * n)
         for w in e.want:
             if not (0 <= w < n):
                 raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
             rows.append(q_start[-1] + int(w))
+            row_slots.append(seq.slot)
         q_start.append(q_start[-1] + n)
         kv_len.append(seq.length + n)
         slots.append(seq.slot)
@@ -79,7 +86,7 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
             flat.extend(pages)
             flat.extend([-1] * (width - len(pages)))
         tables.append((width, flat))
-    sections = [ids, pos, tseq, q_start, kv_len, slots, rows] + [t[1] for t in tables]
+    sections = [ids, pos, tseq, q_start, kv_len, slots, rows, row_slots] + [t[1] for t in tables]
     total = sum(len(x) for x in sections)
     host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
     offset = 0
@@ -97,8 +104,8 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
 
     return StepContext(
         num_tokens=T, num_seqs=S, token_ids=cut(0), positions=cut(1), token_seq=cut(2), q_start=cut(3),
-        kv_len=cut(4), slots=cut(5), logit_rows=cut(6),
-        block_tables=[cut(7 + i).view(S, tables[i][0]) for i in range(len(tables))],
+        kv_len=cut(4), slots=cut(5), logit_rows=cut(6), row_slots=cut(7),
+        block_tables=[cut(8 + i).view(S, tables[i][0]) for i in range(len(tables))],
         status=status, q_start_host=q_start, kv_len_host=kv_len, slots_host=slots,
         max_q_len=max((len(e.tokens) for e in entries), default=0), max_kv_len=max(kv_len, default=0),
         all_decode=all(len(e.tokens) == 1 for e in entries))

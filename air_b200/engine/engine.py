@@ -15,7 +15,8 @@ from ..config import load_config
 from ..parts import registry
 from ..parts.base import Runtime
 from ..weights.loader import load_tensors, random_tensors, write_model_folder
-from .batch import Entry, StepContext, build_context
+from ..csrc import ops
+from .batch import Entry, StepContext, build_context, LAST_SAMPLED
 from .model import Model
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -54,7 +55,10 @@ class Engine:
         self.cache = CacheManager(model.cache_needs(), config.page_tokens, num_pages, config.max_requests,
                                   dtype=self.rt.dtype, device=self.rt.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        self.last_token = torch.zeros(config.max_requests, dtype=torch.int32, device=self.rt.device)
+        self.last_context: Optional[StepContext] = None
         self.steps = 0
+        self.graph_kernel_launches = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -98,6 +102,8 @@ class Engine:
             seen.add(e.request)
             if len(e.tokens) == 0:
                 raise StepError(f"request {e.request!r} brings no tokens")
+            if len(e.tokens) == 1 and int(e.tokens[0]) == LAST_SAMPLED and e.request in self.cache.sequences:
+                continue
             for t in e.tokens:
                 if not (0 <= int(t) < vocab):
                     raise StepError("input token is outside model vocabulary")
@@ -116,6 +122,7 @@ class Engine:
             raise
         try:
             ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+            ctx.last_token = self.last_token
             logits = self.model.forward(ctx, self.cache)
         except Exception:
             for e in entries:
@@ -127,7 +134,34 @@ class Engine:
         for e in entries:
             self.cache.commit(e.request, len(e.tokens))
         self.steps += 1
+        self.last_context = ctx
         return logits
+
+    def sample(self, logits: torch.Tensor, temperature=None, uniform=None) -> torch.Tensor:
+        """Chooses a token for every row of the last step's logits on the device: the lowest
+        index of the maximum where temperature[r] <= 0 (or temperature is None), else a draw from
+        softmax(logits / temperature) with the uniform number uniform[r].  Returns int32 [rows] on
+        the device; each choice is also remembered for its request, so that the next step can
+        take it as Entry(request, [LAST_SAMPLED]) without a copy to the host."""
+        ctx = self.last_context
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        if logits.shape[0] == 0:
+            return out
+        if ctx is None or ctx.row_slots.shape[0] != logits.shape[0]:
+            raise StepError("sample() takes the logits of the step that has just run")
+
+        def dev(x):
+            if x is None or isinstance(x, torch.Tensor):
+                return x
+            return torch.tensor(x, dtype=torch.float32).to(logits.device, non_blocking=True)
+
+        ops.sample(logits, dev(temperature), dev(uniform), out, status=self.status, slots=ctx.row_slots,
+                   last_token=self.last_token)
+        return out
+
+    def kernel_launches(self) -> int:
+        """Kernels of this package launched so far, those replayed inside CUDA graphs included."""
+        return ops.launches + self.graph_kernel_launches
 
     def finish(self, request: Hashable) -> None:
         """The request is over: its pages and its slot are free for others."""

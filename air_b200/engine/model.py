@@ -83,7 +83,7 @@ class Model:
         and returns float32 logits [wanted rows, vocab]."""
         rt = self.rt
         h = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=torch.float32, device=rt.device)
-        ops.embedding(self.embedding, ctx.token_ids, h, status=ctx.status)
+        ops.embedding(self.embedding, ctx.token_ids, h, status=ctx.status, last_token=ctx.last_token)
         pending = None
         for i, run in enumerate(self.spec.order):
             owner = i if run.cache_from is None else run.cache_from

@@ -1,0 +1,336 @@
+"""The Python entry point: requests in (token ids), tokens out.
+
+It follows AIR's InferenceService (include/air/serving.hpp:237-286; src/runtime/serving.cpp:
+1494-2010) in names and meanings: `SchedulerConfig`, `GenerationConfig`, `generate`,
+`generate_cohort`, `snapshot`; a bounded queue; admission of the queue's head only, by
+worst-case reservation; cycles of decode-first micro-batches under a token budget; the first
+token comes from the last prompt portion; a finished request gives its pages back before the
+next admission.  Differences: there is no worker thread (the caller's thread runs the cycles),
+no tokenizer (prompts are token ids), and every cycle is ONE engine step that holds the
+cycle's prompt portions and decoded tokens together.
+
+When pages run out.  With `reserve_worst_case` (the default, AIR's policy) an admitted request
+has its worst case reserved, so a step can never run out of pages.  Without it, requests are
+admitted while their next portion fits, and a step may find the pool empty: the engine then
+reports OutOfPages with nothing changed, and the scheduler takes the youngest active request
+out of the batch, gives its pages back and puts it at the head of the queue, to be computed
+again from its prompt and the tokens it has produced (its sampler keeps its state, so the
+continuation is the same); it retries the step with the rest.  A request that does not fit the
+empty pool fails with "insufficient KV pages for one sequence".
+"""
+from __future__ import annotations
+
+import collections
+import time
+from dataclasses import dataclass, field
+from typing import Deque, Dict, Hashable, List, Optional, Sequence
+
+from ..cache.manager import OutOfPages
+from ..sampling.sampler import GenerationConfig, HostSampler, SamplingConfig
+from .batch import Entry
+from .scheduler import (CapacityScheduler, MicrobatchScheduler, SchedulableSequence, WorkPhase)
+
+
+@dataclass
+class SchedulerConfig:
+    """AIR's names (include/air/serving.hpp:46-62).  The defaults are sized for a B200 rather
+    than for AIR's laptop GPU: AIR has 8 / 256 / 256 / 32 / 16."""
+    max_active_requests: int = 64
+    max_queued_requests: int = 256
+    token_budget_per_cycle: int = 2048
+    prefill_quantum_tokens: int = 512
+    kv_page_tokens: int = 64
+    reserve_worst_case: bool = True
+
+
+@dataclass
+class RequestMetrics:
+    """include/air/serving.hpp:75-104."""
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    queue_ms: float = 0.0
+    prefill_ms: float = 0.0
+    ttft_ms: float = 0.0
+    decode_ms: float = 0.0
+    total_ms: float = 0.0
+    preemptions: int = 0
+
+
+@dataclass
+class InferenceResponse:
+    request_id: int
+    tokens: List[int]
+    hit_eos: bool = False
+    error: Optional[str] = None
+    metrics: RequestMetrics = field(default_factory=RequestMetrics)
+
+
+class QueueFull(RuntimeError):
+    pass
+
+
+@dataclass
+class _WorkItem:
+    request_id: int
+    prompt: List[int]               # what has to be in the cache before decoding goes on
+    prompt_tokens: int              # length of the prompt as submitted
+    generation: GenerationConfig
+    sampler: HostSampler
+    generated: List[int] = field(default_factory=list)
+    prompt_position: int = 0
+    reservation_pages: int = 0
+    done: bool = False
+    hit_eos: bool = False
+    error: Optional[str] = None
+    submitted: float = 0.0
+    admitted: float = 0.0
+    first_token: float = 0.0
+    metrics: RequestMetrics = field(default_factory=RequestMetrics)
+
+    @property
+    def phase(self) -> WorkPhase:
+        return WorkPhase.prefill if self.prompt_position < len(self.prompt) else WorkPhase.decode
+
+
+class InferenceService:
+    def __init__(self, engine, scheduler: Optional[SchedulerConfig] = None):
+        self.engine = engine
+        self.config = scheduler or SchedulerConfig()
+        for name in ("max_active_requests", "max_queued_requests", "token_budget_per_cycle",
+                     "prefill_quantum_tokens"):
+            if getattr(self.config, name) <= 0:
+                raise ValueError(f"scheduler {name} must be greater than zero")
+        self.capacity = CapacityScheduler(self.config.max_active_requests)
+        self.micro = MicrobatchScheduler()
+        self.queued: Deque[_WorkItem] = collections.deque()
+        self.active: List[_WorkItem] = []
+        self.finished: Dict[int, InferenceResponse] = {}
+        self._next_id = 0
+        self.cycles = 0
+        self.preemptions = 0
+        self.last_batch = None
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def create(cls, model: str, dtype="bfloat16", scheduler: Optional[SchedulerConfig] = None,
+               max_tokens: int = 65536, device: str = "cuda:0") -> "InferenceService":
+        """Loads the model folder and makes its cache for `max_tokens` tokens."""
+        from .engine import Engine, EngineConfig, parse_dtype
+        scheduler = scheduler or SchedulerConfig()
+        engine = Engine.from_folder(model, EngineConfig(
+            dtype=parse_dtype(dtype), page_tokens=scheduler.kv_page_tokens, max_tokens=max_tokens,
+            max_requests=scheduler.max_active_requests, device=device))
+        return cls(engine, scheduler)
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, prompt_tokens: Sequence[int], generation: Optional[GenerationConfig] = None) -> int:
+        generation = generation or GenerationConfig()
+        generation.sampling.validate()
+        spec = self.engine.model.spec
+        prompt = [int(t) for t in prompt_tokens]
+        if not prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if any(not (0 <= t < spec.vocab_size) for t in prompt):
+            raise ValueError("input token is outside model vocabulary")
+        if len(prompt) + generation.max_new_tokens > spec.max_positions:
+            raise ValueError("prompt plus max_new_tokens exceeds the model context length")
+        if len(self.queued) >= self.config.max_queued_requests:
+            raise QueueFull("inference submission queue is full")
+        item = _WorkItem(self._next_id, prompt, len(prompt), generation, HostSampler(generation.sampling),
+                         submitted=time.perf_counter())
+        self._next_id += 1
+        self.queued.append(item)
+        return item.request_id
+
+    def restore(self, request: Hashable, last_token: int, generation: Optional[GenerationConfig] = None) -> int:
+        """Takes over a request that the engine already holds (its tokens are in the cache) as an
+        active, decoding request whose next input is `last_token`
+        (AIR: PreparedModel::restore_sequence, src/runtime/backend.hpp:97-145)."""
+        generation = generation or GenerationConfig()
+        length = self.engine.cache.length(request)
+        item = _WorkItem(request, [0] * length, length, generation, HostSampler(generation.sampling),
+                         submitted=time.perf_counter())
+        item.prompt_position = length
+        item.generated = [int(last_token)]
+        item.generation = GenerationConfig(generation.max_new_tokens + 1, generation.sampling,
+                                           generation.stop_on_eos)
+        item.admitted = item.first_token = item.submitted
+        item.reservation_pages = self.engine.cache.pages_needed(length + generation.max_new_tokens)
+        self.active.append(item)
+        return item.request_id
+
+    def generate(self, prompt_tokens: Sequence[int], generation: Optional[GenerationConfig] = None
+                 ) -> InferenceResponse:
+        return self.generate_cohort([(prompt_tokens, generation)])[0]
+
+    def generate_cohort(self, requests) -> List[InferenceResponse]:
+        """Submits the requests together and runs cycles until all of them are finished."""
+        ids = []
+        for r in requests:
+            prompt, generation = r if isinstance(r, tuple) else (r, None)
+            ids.append(self.submit(prompt, generation))
+        while any(i not in self.finished for i in ids):
+            if not self.run_cycle() and not self.active and not self.queued:
+                break
+        return [self.finished.pop(i) for i in ids]
+
+    # ------------------------------------------------------------------ one cycle
+    def _admit(self) -> None:
+        cache = self.engine.cache
+        while self.queued:
+            item = self.queued[0]
+            worst = len(item.prompt) + max(0, item.generation.max_new_tokens - len(item.generated))
+            if self.config.reserve_worst_case:
+                reserved = sum(i.reservation_pages for i in self.active)
+                decision = self.capacity.evaluate(len(self.active), reserved, cache.num_pages,
+                                                  cache.page_tokens, worst)
+            else:
+                first = min(len(item.prompt), self.config.prefill_quantum_tokens)
+                decision = self.capacity.evaluate(len(self.active), cache.num_pages - cache.free_pages(),
+                                                  cache.num_pages, cache.page_tokens, first)
+                if decision.admit and cache.pages_needed(worst) > cache.num_pages:
+                    decision.admit, decision.reason = False, "device-capacity"
+            if not decision.admit:
+                never = decision.reason == "device-capacity" and (
+                    not self.active or cache.pages_needed(worst) > cache.num_pages)
+                if never:
+                    self.queued.popleft()
+                    self._finish(item, error="insufficient KV pages for one sequence")
+                    continue
+                break
+            self.queued.popleft()
+            item.reservation_pages = decision.reservation_pages if self.config.reserve_worst_case else 0
+            item.admitted = time.perf_counter()
+            self.active.append(item)
+
+    def _entries(self, batch) -> List[Entry]:
+        by_id = {i.request_id: i for i in self.active}
+        entries = []
+        for s in batch.slices:
+            item = by_id[s.slot]
+            if s.phase == WorkPhase.prefill:
+                tokens = item.prompt[item.prompt_position:item.prompt_position + s.token_count]
+                last = item.prompt_position + s.token_count >= len(item.prompt)
+                wants_token = last and len(item.generated) < item.generation.max_new_tokens
+                entries.append(Entry(item.request_id, tokens, [len(tokens) - 1] if wants_token else []))
+            else:
+                entries.append(Entry(item.request_id, [item.generated[-1]], [0]))
+        return entries
+
+    def run_cycle(self) -> bool:
+        """Admission, one micro-batch, one engine step, sampling, finishing.  Returns False when
+        there was nothing to run."""
+        self._admit()
+        if not self.active:
+            return False
+        candidates = []
+        for item in self.active:
+            if item.phase == WorkPhase.prefill:
+                limit = min(len(item.prompt) - item.prompt_position, self.config.prefill_quantum_tokens)
+                candidates.append(SchedulableSequence(item.request_id, WorkPhase.prefill, limit))
+            else:
+                candidates.append(SchedulableSequence(item.request_id, WorkPhase.decode, 1))
+        batch = self.micro.schedule(candidates, self.config.token_budget_per_cycle)
+        if not batch.slices:
+            return False
+        entries = self._entries(batch)
+        while True:
+            try:
+                logits = self.engine.step(entries)
+                break
+            except OutOfPages:
+                victim = self._preempt_youngest()
+                entries = [e for e in entries if e.request != victim]
+                if not entries:
+                    return True
+        self.last_batch = batch
+        self.cycles += 1
+        self._accept(entries, logits)
+        for item in [i for i in self.active if i.done]:
+            self.active.remove(item)
+            self.engine.finish(item.request_id)
+            self._finish(item)
+        return True
+
+    def _preempt_youngest(self) -> int:
+        """Takes the active request that was admitted last out of the engine and puts it back
+        at the head of the queue; it will be computed again from its prompt and its tokens."""
+        if len(self.active) <= 1:
+            item = self.active.pop()
+            if item.request_id in self.engine.cache.sequences:
+                self.engine.finish(item.request_id)
+            self._finish(item, error="insufficient KV pages for one sequence")
+            return item.request_id
+        item = max(self.active, key=lambda i: i.admitted)
+        self.active.remove(item)
+        if item.request_id in self.engine.cache.sequences:
+            self.engine.finish(item.request_id)
+        item.prompt = item.prompt[:item.prompt_tokens] + item.generated
+        item.prompt_position = 0
+        item.metrics.preemptions += 1
+        self.preemptions += 1
+        self.queued.appendleft(item)
+        return item.request_id
+
+    def _accept(self, entries: Sequence[Entry], logits) -> None:
+        by_id = {i.request_id: i for i in self.active}
+        rows = [by_id[e.request] for e in entries if e.want]
+        chosen: List[Optional[int]] = [None] * len(rows)
+        if rows:
+            if all(i.generation.sampling.on_device for i in rows):
+                temps = [float(i.generation.sampling.temperature) for i in rows]
+                if any(t > 0.0 for t in temps):
+                    uniforms = [i.sampler.next_uniform() if t > 0.0 else 0.0 for i, t in zip(rows, temps)]
+                    ids = self.engine.sample(logits, temps, uniforms)
+                else:
+                    ids = self.engine.sample(logits)
+                chosen = [int(t) for t in ids.tolist()]
+            else:
+                host = logits.float().cpu().numpy()
+                chosen = [i.sampler.sample(host[r]) for r, i in enumerate(rows)]
+        now = time.perf_counter()
+        r = 0
+        for e in entries:
+            item = by_id[e.request]
+            if item.phase == WorkPhase.prefill:
+                item.prompt_position += len(e.tokens)
+            if e.want:
+                self._accept_token(item, chosen[r], now)
+                r += 1
+            elif item.phase == WorkPhase.decode and len(item.generated) >= item.generation.max_new_tokens:
+                item.done = True  # max_new_tokens == 0, or a recomputed request that had finished
+
+    def _accept_token(self, item: _WorkItem, token: int, now: float) -> None:
+        """src/runtime/serving.cpp:687-700."""
+        if not item.generated:
+            item.first_token = now
+        item.generated.append(token)
+        eos = self.engine.model.spec.eos_token_id
+        if item.generation.stop_on_eos and eos is not None and token == eos:
+            item.hit_eos = True
+            item.done = True
+        if len(item.generated) >= item.generation.max_new_tokens:
+            item.done = True
+
+    def _finish(self, item: _WorkItem, error: Optional[str] = None) -> None:
+        now = time.perf_counter()
+        m = item.metrics
+        m.prompt_tokens, m.generated_tokens = item.prompt_tokens, len(item.generated)
+        if item.admitted:
+            m.queue_ms = (item.admitted - item.submitted) * 1e3
+        if item.first_token:
+            m.ttft_ms = (item.first_token - item.submitted) * 1e3
+            m.prefill_ms = (item.first_token - item.admitted) * 1e3
+            m.decode_ms = (now - item.first_token) * 1e3
+        m.total_ms = (now - item.submitted) * 1e3
+        self.finished[item.request_id] = InferenceResponse(item.request_id, list(item.generated), item.hit_eos,
+                                                           error, m)
+
+    # ------------------------------------------------------------------ figures
+    def snapshot(self) -> dict:
+        """A few of the gauges of AIR's ServiceSnapshot (include/air/serving.hpp:131-208)."""
+        cache = self.engine.cache
+        return {"queued_requests": len(self.queued), "active_requests": len(self.active),
+                "reserved_pages": sum(i.reservation_pages for i in self.active),
+                "kv_pages_total": cache.num_pages, "kv_pages_free": cache.free_pages(),
+                "cycles": self.cycles, "preemptions": self.preemptions}
