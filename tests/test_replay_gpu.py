@@ -1,0 +1,108 @@
+"""Trace replay on the GPU against the plain implementation: the same requests whole, with
+the last 32 tokens one by one, in portions of changing size down to two tokens, and mixed with
+other requests in a pool so small that pages are used again; in float32 and in bfloat16; for
+the tiny configurations A and B (which differ in every size and option) and W (a window)."""
+import json
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+import util
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": (1, 7, 33, 97, 150), "B": (5, 40, 97, 131, 64, 18), "W": (3, 50, 97, 140)}
+
+
+def streams_for(name):
+    return {f"{name}{i}": util.tokens_for(name, n, i) for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "W"])
+def test_whole(name, dtype):
+    folder, streams = util.model_folder(name), streams_for(name)
+    steps = util.trace_whole(streams)
+    got, _ = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps))
+    util.check_against_plain(got, folder, streams, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "W"])
+def test_bulk_then_last_32_one_by_one(name, dtype):
+    folder, streams = util.model_folder(name), streams_for(name)
+    steps = util.trace_bulk_tail(streams, tail=32)
+    got, _ = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps))
+    util.check_against_plain(got, folder, streams, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "W"])
+def test_portions_of_changing_size(name, dtype):
+    folder, streams = util.model_folder(name), streams_for(name)
+    steps = util.trace_portions(streams)
+    got, _ = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps))
+    util.check_against_plain(got, folder, streams, dtype)
+
+
+@pytest.mark.parametrize("page", [16, 64])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "W"])
+def test_mixed_with_pages_used_again(name, dtype, page):
+    folder, streams = util.model_folder(name), streams_for(name)
+    steps = util.trace_mixed(streams, seed=3, live=4)
+    peak = util.peak_tokens(steps, page=64)
+    got, engine = util.replay(folder, dtype, steps, max_tokens=peak, page_tokens=page)
+    util.check_against_plain(got, folder, streams, dtype)
+    pool = engine.cache.groups[0].pool
+    total = sum(-(-len(t) // page) for t in streams.values())
+    assert total > pool.num_pages, "the pool is smaller than what all requests need: pages were used again"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "W"])
+def test_float32_does_not_depend_on_the_cut(name):
+    """In float32 every kernel reduces in an order that depends only on the position, so the
+    four ways of cutting give the same bits."""
+    folder, streams = util.model_folder(name), streams_for(name)
+    a, _ = util.replay(folder, "float32", util.trace_whole(streams), 1024)
+    b, _ = util.replay(folder, "float32", util.trace_portions(streams), 1024)
+    c, _ = util.replay(folder, "float32", util.trace_mixed(streams, seed=5), 1024, page_tokens=32)
+    assert a.keys() == b.keys() == c.keys()
+    for k in a:
+        assert np.array_equal(a[k], b[k]) and np.array_equal(a[k], c[k]), k
+
+
+def test_trace_run_program_writes_files_and_done_lines():
+    folder = util.model_folder("B")
+    streams = {"x": util.tokens_for("B", 70, 11), "y": util.tokens_for("B", 45, 12)}
+    steps = [
+        util.step_line(0, [("x", streams["x"][:40], [0, 39])]),
+        util.step_line(1, [("x", streams["x"][40:42], []), ("y", streams["y"][:45], [44])]),   # nothing wanted of x
+        util.step_line(2, [("x", streams["x"][42:70], [27])], end=["x", "y"]),
+        util.step_line(3, [], end=[]),
+    ]
+    with tempfile.TemporaryDirectory() as out:
+        util.run_trace_program(folder, "float32", steps, 128, out)
+        assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "2.f32"]
+        got = util.collect(steps, out, util.TINY_B["vocab_size"])
+    assert sorted(got) == [("x", 0), ("x", 39), ("x", 69), ("y", 44)]
+    util.check_against_plain(got, folder, streams, "float32")
+
+
+def test_out_of_pages_is_an_error_that_changes_nothing():
+    from air_b200.cache.manager import OutOfPages
+    from air_b200.engine.batch import Entry
+    from air_b200.engine.engine import Engine, EngineConfig
+    folder = util.model_folder("A")
+    engine = Engine.from_folder(folder, EngineConfig(dtype="float32", page_tokens=16, max_tokens=64))
+    toks = util.tokens_for("A", 80, 1)
+    engine.step([Entry("a", toks[:40], [39])])
+    with pytest.raises(OutOfPages):
+        engine.step([Entry("a", toks[40:45], [4]), Entry("b", toks[:30], [29])])
+    assert engine.cache.length("a") == 40 and "b" not in engine.cache.sequences
+    engine.cache.check()
+    got = engine.step([Entry("a", toks[40:45], [4])]).cpu().numpy()
+    ref = util.plain_logits(folder, toks[:45])
+    assert np.abs(got[0] - ref[44]).max() < util.FP32_TOL * max(1, np.abs(ref).max())

@@ -1,0 +1,230 @@
+"""Helpers of the tests: the tiny configurations, model folders in temporary places, traces
+and their replay, and the comparison with the plain implementation."""
+import functools
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+BASE = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu"}
+
+# Two tiny configurations that differ in every size and option, and a third with a window.
+TINY_A = dict(BASE, num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=128, vocab_size=256, max_position_embeddings=512, rope_theta=10000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=True, use_sliding_window=False)
+TINY_B = dict(BASE, num_hidden_layers=3, hidden_size=192, num_attention_heads=6, num_key_value_heads=1,
+              intermediate_size=352, vocab_size=387, max_position_embeddings=640, rope_theta=1e6,
+              rms_norm_eps=1e-5, tie_word_embeddings=False, use_sliding_window=False, sliding_window=4096)
+TINY_W = dict(BASE, num_hidden_layers=3, hidden_size=96, num_attention_heads=3, num_key_value_heads=3,
+              intermediate_size=208, vocab_size=301, max_position_embeddings=512, rope_theta=50000.0,
+              rms_norm_eps=3e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=40,
+              max_window_layers=1)
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "W": (TINY_W, 2)}
+
+_folders = {}
+_tmp = []
+
+
+def model_folder(name, dtype="bfloat16", scale=None):
+    """A folder with config.json and model.safetensors for a tiny configuration, made once per
+    session in a temporary place.  Weights are stored as bfloat16 values (also for the float32
+    tests, so that both precisions and the plain implementation read the same numbers)."""
+    key = (name, dtype)
+    if key not in _folders:
+        from air_b200.engine.engine import write_random_model
+        cfg, seed = CONFIGS[name]
+        d = tempfile.TemporaryDirectory(prefix=f"air_b200_{name}_")
+        _tmp.append(d)
+        write_random_model(d.name, cfg, seed, dtype)
+        _folders[key] = d.name
+    return _folders[key]
+
+
+@functools.lru_cache(maxsize=None)
+def plain_model(folder):
+    from plain import qwen2_plain as plain
+    return plain.read_model(folder)
+
+
+_plain_cache = {}
+
+
+def plain_logits(folder, tokens):
+    """Logits [len(tokens), vocab] of the plain implementation (cached per token list)."""
+    from plain import qwen2_plain as plain
+    key = (folder, tuple(tokens))
+    if key not in _plain_cache:
+        cfg, tensors = plain_model(folder)
+        _plain_cache[key] = plain.forward(cfg, tensors, list(tokens))
+    return _plain_cache[key]
+
+
+def tokens_for(name, n, seed):
+    cfg, _ = CONFIGS[name]
+    return np.random.default_rng(1000 + seed).integers(0, cfg["vocab_size"], size=n).tolist()
+
+
+# ------------------------------------------------------------------ traces
+def step_line(step, entries, end=()):
+    return {"step": step, "entries": [{"id": i, "tokens": list(t), "want": list(w)} for i, t, w in entries],
+            "end": list(end)}
+
+
+def trace_whole(streams):
+    """Each request alone and whole, all logits wanted."""
+    return [step_line(n, [(rid, toks, range(len(toks)))], end=[rid]) for n, (rid, toks) in enumerate(streams.items())]
+
+
+def trace_bulk_tail(streams, tail=32):
+    steps, n = [], 0
+    for rid, toks in streams.items():
+        cut = max(1, len(toks) - tail)
+        steps.append(step_line(n, [(rid, toks[:cut], range(cut))]))
+        n += 1
+        for i in range(cut, len(toks)):
+            steps.append(step_line(n, [(rid, [toks[i]], [0])], end=[rid] if i == len(toks) - 1 else []))
+            n += 1
+        if cut == len(toks):
+            steps[-1]["end"] = [rid]
+    return steps
+
+
+def trace_portions(streams, sizes=(33, 2, 17, 5, 2, 64, 3, 2, 31, 16, 1, 47, 2)):
+    steps, n = [], 0
+    for rid, toks in streams.items():
+        i, k = 0, 0
+        while i < len(toks):
+            m = min(sizes[k % len(sizes)], len(toks) - i)
+            steps.append(step_line(n, [(rid, toks[i:i + m], range(m))], end=[rid] if i + m == len(toks) else []))
+            i += m
+            k += 1
+            n += 1
+    return steps
+
+
+def trace_mixed(streams, seed=0, live=4, tail=12, portions=(2, 5, 9, 16, 23, 31, 40)):
+    """Up to `live` requests at a time: each is fed in portions of changing size, then its last
+    `tail` tokens one by one, beside whatever the others are doing; a request that ends makes
+    room for the next one, so pages are used again.  All logits are wanted."""
+    rng = np.random.default_rng(seed)
+    waiting = list(streams.items())
+    active = {}
+    steps, n = [], 0
+    while waiting or active:
+        while waiting and len(active) < live:
+            rid, toks = waiting.pop(0)
+            active[rid] = [toks, 0]
+        entries, end = [], []
+        for rid in list(active):
+            toks, pos = active[rid]
+            if rng.random() < 0.2 and len(active) > 1:
+                continue  # left out of this step, goes on later
+            rest = len(toks) - pos
+            m = 1 if rest <= tail else min(int(rng.choice(portions)), rest - tail)
+            entries.append((rid, toks[pos:pos + m], range(m)))
+            active[rid][1] = pos + m
+            if pos + m == len(toks):
+                end.append(rid)
+                del active[rid]
+        if entries:
+            steps.append(step_line(n, entries, end))
+            n += 1
+    return steps
+
+
+def peak_tokens(steps, page=64):
+    """The most tokens live requests hold at any time, each rounded up to whole pages."""
+    held, peak = {}, 0
+    for s in steps:
+        for e in s["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        peak = max(peak, sum(-(-v // page) * page for v in held.values()))
+        for r in s["end"]:
+            held.pop(r, None)
+    return peak
+
+
+def replay(folder, dtype, steps, max_tokens, page_tokens=16, max_requests=8):
+    """Runs the steps through Engine.step (in process) and returns {(request, position): logits}."""
+    import torch
+    from air_b200.engine.engine import Engine, EngineConfig
+    from air_b200.engine.replay import run_trace
+    engine = Engine.from_folder(folder, EngineConfig(dtype=dtype, page_tokens=page_tokens, max_tokens=max_tokens,
+                                                     max_requests=max_requests))
+    with tempfile.TemporaryDirectory() as out:
+        run_trace(engine, [json.dumps(s) for s in steps], out)
+        engine.cache.check()
+        assert not engine.cache.sequences, "every request of the trace was ended"
+        assert engine.cache.free_pages() == engine.cache.num_pages
+        return collect(steps, out, engine.model.spec.vocab_size), engine
+
+
+def collect(steps, out_dir, vocab):
+    got, pos = {}, {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        path = os.path.join(out_dir, f"{s['step']}.f32")
+        if wanted == 0:
+            assert not os.path.exists(path)
+        else:
+            data = np.fromfile(path, dtype="<f4").reshape(wanted, vocab)
+        r = 0
+        for e in s["entries"]:
+            base = pos.get(e["id"], 0)
+            for w in e["want"]:
+                got[(e["id"], base + w)] = data[r]
+                r += 1
+            pos[e["id"]] = base + len(e["tokens"])
+        for rid in s["end"]:
+            pos.pop(rid, None)
+    return got
+
+
+def run_trace_program(folder, dtype, steps, max_tokens, out_dir, extra=()):
+    """Runs bin/trace_run as a program; checks the `done` lines."""
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+           "--out", out_dir, "--max-tokens", str(max_tokens)] + list(extra)
+    p = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                       timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
+    assert done == [f"done {s['step']}" for s in steps]
+    return p
+
+
+# ------------------------------------------------------------------ comparison
+# Tolerances are set once, from the arithmetic: float32 differs from the 64-bit-accumulating
+# plain implementation by a few units of 1e-7 per operation; bfloat16 rounds activations to 8
+# bits of mantissa (2^-9 relative per rounding) at each of a few dozen places.
+FP32_TOL = 2e-5     # of the largest |logit|
+BF16_MAX_TOL = 4e-2
+BF16_MEAN_TOL = 6e-3
+
+
+def check_against_plain(got, folder, streams, dtype):
+    worst = 0.0
+    for rid, toks in streams.items():
+        ref = plain_logits(folder, toks)
+        scale = max(1.0, float(np.abs(ref).max()))
+        rows = sorted(p for (r, p) in got if r == rid)
+        assert rows, f"no logits for request {rid}"
+        for p in rows:
+            out = got[(rid, p)]
+            assert np.isfinite(out).all()
+            diff = np.abs(out - ref[p])
+            if dtype == "float32":
+                assert diff.max() <= FP32_TOL * scale, (rid, p, float(diff.max()))
+                assert out.argmax() == ref[p].argmax() or np.sort(ref[p])[-1] - np.sort(ref[p])[-2] < 2 * FP32_TOL * scale
+            else:
+                assert diff.max() <= BF16_MAX_TOL * scale, (rid, p, float(diff.max()))
+                assert diff.mean() <= BF16_MEAN_TOL * scale, (rid, p, float(diff.mean()))
+                top2 = np.sort(ref[p])[-2:]
+                if top2[1] - top2[0] > 2 * BF16_MAX_TOL * scale:
+                    assert out.argmax() == ref[p].argmax()
+            worst = max(worst, float(diff.max()) / scale)
+    return worst
