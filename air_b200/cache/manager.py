@@ -43,6 +43,7 @@ class PagePool:
         self._free: List[int] = list(range(num_pages - 1, -1, -1))
         self._owner: List[Optional[Hashable]] = [None] * num_pages
         self.peak_used = 0
+        self.takes = 0      # pages handed out so far; more than num_pages means pages were used again
 
     @property
     def free_pages(self) -> int:
@@ -61,6 +62,7 @@ class PagePool:
         if self._owner[page] is not None:
             raise CacheError(f"page {page} was on the free stack while owned by {self._owner[page]!r}")
         self._owner[page] = owner
+        self.takes += 1
         self.peak_used = max(self.peak_used, self.used_pages)
         return page
 

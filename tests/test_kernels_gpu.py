@@ -1,0 +1,295 @@
+"""Each CUDA kernel alone against a plain float32/float64 torch or numpy reference of the same
+operation, at sizes other than the engine's (widths and vocabularies that are no power of two,
+head sizes in steps of 16, odd numbers of heads and groups)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(x, dtype=None):
+    t = torch.as_tensor(x)
+    return t.to("cuda", dtype=dtype) if dtype is not None else t.to("cuda")
+
+
+def ops():
+    from air_b200.csrc import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_gathers_rows_and_feeds_back_sampled_tokens(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1000, 200, generator=g).to(DT[dtype])
+    ids = torch.tensor([0, 999, 5, -3, 17, -1], dtype=torch.int32)
+    last = torch.tensor([42, 7, 500], dtype=torch.int32)
+    out = torch.empty(6, 200, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().embedding(dev(table), dev(ids), out, status=status, last_token=dev(last))
+    want = table[[0, 999, 5, 500, 17, 42]].float()
+    assert torch.equal(out.cpu(), want) and status.item() == 0
+    ops().embedding(dev(table), dev(torch.tensor([1000], dtype=torch.int32)), out[:1], status=status)
+    assert status.item() == 1 and float(out[0].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("E", [200, 1000, 3584, 5120])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_add_rmsnorm(E, dtype):
+    g = torch.Generator().manual_seed(E)
+    h = torch.randn(37, E, generator=g) * 3
+    delta = torch.randn(37, E, generator=g).to(DT[dtype])
+    w = (1 + 0.1 * torch.randn(E, generator=g)).to(DT[dtype])
+    eps = 1e-5
+    x = h + delta.float()
+    want = plain.rms_norm(x.numpy(), w.float().numpy(), eps)
+    hd = dev(h.clone())
+    out = torch.empty(37, E, dtype=DT[dtype], device="cuda")
+    ops().add_rmsnorm(hd, dev(delta), dev(w), eps, out)
+    assert torch.equal(hd.cpu(), x), "the residual stream is updated in float32"
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    assert np.abs(out.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+    # without delta, and on chosen rows only (h stays as it is)
+    rows = torch.tensor([36, 0, 5], dtype=torch.int32)
+    out2 = torch.empty(3, E, dtype=DT[dtype], device="cuda")
+    before = hd.clone()
+    ops().add_rmsnorm(hd, None, dev(w), eps, out2, rows=dev(rows))
+    assert torch.equal(hd, before)
+    assert torch.equal(out2.cpu(), out.cpu()[rows.long()])
+    out3 = torch.empty(3, E, dtype=DT[dtype], device="cuda")
+    ops().add_rmsnorm(dev(h.clone()), dev(delta), dev(w), eps, out3, rows=dev(rows))
+    assert torch.equal(out3.cpu(), out.cpu()[rows.long()])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 130, 75), (37, 130, 75), (64, 64, 16), (65, 257, 1000), (3, 9, 3584)])
+def test_gemm_f32_is_true_32_bit_and_rows_do_not_depend_on_the_batch(M, N, K):
+    g = torch.Generator().manual_seed(M * N)
+    a, w, b = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(N, generator=g)
+    out = torch.empty(M, N, device="cuda")
+    ops().gemm_f32(dev(a), dev(w), dev(b), out)
+    want = (a.double() @ w.double().T + b.double())
+    err = (out.cpu().double() - want).abs().max() / want.abs().max()
+    assert err < 5e-7 * math.sqrt(K), "an error of TF32 size (1e-3) would show a reduced-precision mode"
+    one = torch.empty(1, N, device="cuda")
+    ops().gemm_f32(dev(a[M // 2:M // 2 + 1].contiguous()), dev(w), dev(b), one)
+    assert torch.equal(one[0], out[M // 2]), "a row alone gives the same bits as in the batch"
+    nobias = torch.empty(M, N, device="cuda")
+    ops().gemm_f32(dev(a), dev(w), None, nobias)
+    assert torch.allclose(nobias.cpu() + b, out.cpu(), atol=1e-5)
+
+
+def rope_reference(x, positions, theta, rot):
+    """x [T, heads, d]: rotate the first `rot` elements of every head (plain formula)."""
+    y = x.copy()
+    y[..., :rot] = plain.rope(x[..., :rot], positions, theta)
+    return y
+
+
+@pytest.mark.parametrize("H,K,d,rot", [(5, 1, 48, 48), (6, 3, 80, 80), (4, 2, 128, 64), (3, 3, 16, 16)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_qkv_rope_store(H, K, d, rot, dtype):
+    from air_b200.parts.rope import RopeHalf
+    from air_b200.parts.spec import PartSpec
+    from air_b200.parts.base import Runtime
+    P, T, theta = 16, 23, 12345.0
+    rng = np.random.default_rng(d)
+    qkv = rng.standard_normal((T, (H + 2 * K) * d)).astype(np.float32)
+    bias = rng.standard_normal((H + 2 * K) * d).astype(np.float32)
+    # two requests: tokens 0..13 of request 0 at positions 30..43, tokens 14..22 of request 1 at 0..8
+    positions = np.array(list(range(30, 44)) + list(range(9)), dtype=np.int32)
+    token_seq = np.array([0] * 14 + [1] * 9, dtype=np.int32)
+    block_table = np.array([[7, 2, 9], [4, -1, -1]], dtype=np.int32)
+    pe = RopeHalf(PartSpec("rope_half", {"rotary_dim": rot, "theta": theta, "max_positions": 64}))
+    pe.load({}, Runtime(torch.device("cuda"), DT[dtype], P))
+    q_out = torch.zeros(T, H, d, dtype=DT[dtype], device="cuda")
+    cache = torch.zeros(10, 2, K, P, d, dtype=DT[dtype], device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().qkv_rope_store(dev(qkv), dev(bias), pe.table(), dev(positions), dev(token_seq), dev(block_table),
+                         q_out, cache, H, K, d, status=status)
+    x = (qkv + bias).reshape(T, H + 2 * K, d)
+    q_want = rope_reference(x[:, :H], positions, theta, rot)
+    k_want = rope_reference(x[:, H:H + K], positions, theta, rot)
+    v_want = x[:, H + K:]
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    assert np.abs(q_out.float().cpu().numpy() - q_want).max() < tol * np.abs(q_want).max()
+    c = cache.float().cpu().numpy()
+    touched = np.zeros(c.shape[:1] + c.shape[3:4], dtype=bool)
+    for t in range(T):
+        page = block_table[token_seq[t], positions[t] // P]
+        off = positions[t] % P
+        touched[page, off] = True
+        assert np.abs(c[page, 0, :, off] - k_want[t]).max() < tol * np.abs(k_want).max()
+        assert np.abs(c[page, 1, :, off] - v_want[t]).max() < tol * np.abs(v_want).max()
+    assert np.abs(c[~touched.repeat(1, 0)[:, None, None, :].repeat(2, 1).repeat(K, 2)]).sum() == 0, \
+        "no other place of any page is written"
+    assert status.item() == 0
+    # a run that reads another run's cache writes q only
+    cache2 = torch.zeros_like(cache)
+    ops().qkv_rope_store(dev(qkv), dev(bias), pe.table(), dev(positions), dev(token_seq), dev(block_table),
+                         q_out, cache2, H, K, d, write_kv=False)
+    assert float(cache2.abs().sum()) == 0.0
+
+
+def attention_reference(q, k_all, v_all, positions, seq_of, window):
+    """q [T, H, d]; k_all/v_all: per request [len, K, d] (float64 softmax, plain formula)."""
+    T, H, d = q.shape
+    out = np.zeros_like(q)
+    for t in range(T):
+        p = positions[t]
+        lo = 0 if not window else max(0, p - window + 1)
+        k, v = k_all[seq_of[t]][lo:p + 1], v_all[seq_of[t]][lo:p + 1]
+        for h in range(H):
+            g = h * k.shape[1] // H
+            s = (k[:, g].astype(np.float64) @ q[t, h].astype(np.float64)) / math.sqrt(d)
+            e = np.exp(s - s.max())
+            out[t, h] = ((e / e.sum()).astype(np.float32)[:, None] * v[:, g]).sum(0)
+    return out
+
+
+def paged_case(H, K, d, P, lens, q_lens, dtype, seed, num_pages=40):
+    """Requests with `lens` tokens in the cache in shuffled pages; the last q_lens are queries."""
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(num_pages)
+    cache = np.zeros((num_pages, 2, K, P, d), dtype=np.float32)
+    width = max(-(-n // P) for n in lens)
+    bt = -np.ones((len(lens), width), dtype=np.int32)
+    ks, vs, used = [], [], 0
+    for s, n in enumerate(lens):
+        k = rng.standard_normal((n, K, d)).astype(np.float32)
+        v = rng.standard_normal((n, K, d)).astype(np.float32)
+        if dtype == "bfloat16":
+            k, v = plain.round_bf16(k), plain.round_bf16(v)
+        ks.append(k); vs.append(v)
+        for b in range(-(-n // P)):
+            bt[s, b] = perm[used]; used += 1
+            m = min(P, n - b * P)
+            cache[bt[s, b], 0, :, :m] = k[b * P:b * P + m].transpose(1, 0, 2)
+            cache[bt[s, b], 1, :, :m] = v[b * P:b * P + m].transpose(1, 0, 2)
+    positions = np.concatenate([np.arange(n - ql, n) for n, ql in zip(lens, q_lens)]).astype(np.int32)
+    seq_of = np.concatenate([[s] * ql for s, ql in enumerate(q_lens)]).astype(np.int32)
+    q = rng.standard_normal((len(positions), H, d)).astype(np.float32)
+    if dtype == "bfloat16":
+        q = plain.round_bf16(q)
+    return q, cache, bt, positions, seq_of, ks, vs
+
+
+@pytest.mark.parametrize("H,K,d,P", [(6, 2, 48, 16), (7, 1, 80, 32), (4, 4, 128, 64), (2, 1, 256, 16), (3, 3, 16, 16)])
+@pytest.mark.parametrize("window", [0, 21])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_paged_attention_ref(H, K, d, P, window, dtype):
+    lens, q_lens = [150, 1, 64, 33], [37, 1, 1, 33]
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, lens, q_lens, dtype, seed=d + window)
+    out = torch.empty(q.shape, dtype=DT[dtype], device="cuda")
+    ops().paged_attention_ref(dev(q, DT[dtype]), dev(cache, DT[dtype]), dev(bt), dev(seq_of), dev(positions), out,
+                              window, 1.0 / math.sqrt(d))
+    want = attention_reference(q, ks, vs, positions, seq_of, window)
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    assert np.abs(out.float().cpu().numpy() - want).max() < tol * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 17, 63, 64, 300, 447])
+def test_attention_finds_one_far_key_among_hundreds(far):
+    """One key is made to match the query so that its score stands out: the output must be that
+    key's value, wherever in the pages the key lies (a page's first or last place, a far page)."""
+    H, K, d, P, n = 4, 2, 64, 16, 448
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [1], "float32", seed=far)
+    q[:] = 0
+    q[0, :, :] = 0.5
+    page, off = bt[0, far // P], far % P
+    cache[page, 0, :, off, :] = 40.0          # score 0.5*40*64/8 = 160 against |score| < 20 elsewhere
+    ks[0][far] = 40.0
+    out = torch.empty(q.shape, device="cuda")
+    ops().paged_attention_ref(dev(q), dev(cache), dev(bt), dev(seq_of), dev(positions), out, 0, 1.0 / math.sqrt(d))
+    got = out.cpu().numpy()[0]
+    for h in range(H):
+        assert np.abs(got[h] - vs[0][far, h * K // H]).max() < 1e-4
+
+
+def test_window_edge_is_exact():
+    """With a window of w the key at distance w - 1 counts and the key at distance w does not."""
+    H, K, d, P, n, w = 2, 1, 32, 16, 100, 37
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [1], "float32", seed=1)
+    q[:] = 0.5
+    for key, visible in ((n - w, True), (n - w - 1, False)):
+        c = cache.copy()
+        c[bt[0, key // P], 0, :, key % P, :] = 40.0
+        out = torch.empty(q.shape, device="cuda")
+        ops().paged_attention_ref(dev(q), dev(c), dev(bt), dev(seq_of), dev(positions), out, w, 1.0 / math.sqrt(d))
+        hit = np.abs(out.cpu().numpy()[0, 0] - vs[0][key, 0]).max() < 1e-4
+        assert hit == visible
+
+
+@pytest.mark.parametrize("T,I", [(1, 352), (37, 1000), (5, 18944)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul(T, I, dtype):
+    g = torch.Generator().manual_seed(I)
+    x = (torch.randn(T, 2 * I, generator=g) * 3).to(DT[dtype])
+    out = torch.empty(T, I, dtype=DT[dtype], device="cuda")
+    ops().silu_mul(dev(x), out)
+    xf = x.float().numpy()
+    want = plain.silu(xf[:, :I]) * xf[:, I:]
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    assert np.abs(out.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+
+
+def test_argmax_takes_the_lowest_index_of_the_maximum():
+    V = 50001
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(5, V, generator=g)
+    logits[0, 40000] = logits[0, 123] = 9.0
+    logits[1, V - 1] = 11.0
+    logits[2, 0] = 11.0
+    logits[3] = -3.0                      # all equal: index 0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    slots = torch.tensor([2, 0, 1, 4, 3], dtype=torch.int32, device="cuda")
+    last = torch.zeros(6, dtype=torch.int32, device="cuda")
+    ops().sample(dev(logits), None, None, out, status=status, slots=slots, last_token=last)
+    assert out.tolist() == [123, V - 1, 0, 0, int(logits[4].argmax())] and status.item() == 0
+    assert last.tolist() == [V - 1, 0, 123, out[4].item(), 0, 0]
+    logits[4, 77] = float("nan")
+    ops().sample(dev(logits), None, None, out, status=status)
+    assert status.item() == 3
+
+
+def test_temperature_sampling_follows_the_distribution_and_the_uniform_number():
+    V, R = 1003, 4000
+    g = torch.Generator().manual_seed(1)
+    row = torch.randn(V, generator=g) * 2
+    temp = 0.7
+    p = torch.softmax(row.double() / temp, 0)
+    cdf = torch.cumsum(p, 0)
+    u = torch.rand(R, generator=g)
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops().sample(dev(row.repeat(R, 1)), dev(torch.full((R,), temp)), dev(u), out)
+    got = out.cpu().long()
+    want = torch.searchsorted(cdf, u.double()).clamp(max=V - 1)
+    # the walk is in index order: the drawn index is where the cumulative sum passes u (up to rounding)
+    near = (got - want).abs() <= 1
+    assert near.float().mean() > 0.995
+    agree = (got == want).float().mean()
+    assert agree > 0.97
+    # rows with temperature 0 among them are greedy
+    t = torch.tensor([0.0, 0.7, 0.0])
+    out3 = torch.empty(3, dtype=torch.int32, device="cuda")
+    ops().sample(dev(row.repeat(3, 1)), dev(t), dev(torch.tensor([0.3, 0.999999, 0.5])), out3)
+    assert out3[0].item() == out3[2].item() == int(row.argmax())
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    o = ops()
+    q = torch.zeros(2, 2, 24, device="cuda")
+    with pytest.raises(o.KernelError, match="multiples of 16"):
+        o.paged_attention_ref(q, torch.zeros(1, 2, 1, 16, 24, device="cuda"), torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
+                              torch.zeros(2, dtype=torch.int32, device="cuda"), torch.zeros(2, dtype=torch.int32, device="cuda"),
+                              torch.empty_like(q), 0, 1.0)
+    with pytest.raises(o.KernelError, match="CUDA tensor"):
+        o.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
+    with pytest.raises(o.KernelError, match="shape"):
+        o.gemm_f32(torch.zeros(2, 8, device="cuda"), torch.zeros(3, 9, device="cuda"), None, torch.zeros(2, 3, device="cuda"))

@@ -1,0 +1,179 @@
+"""The scheduler's decisions (no GPU): admission by reservation, decode first, the token budget,
+rotation, finishing, and what happens when pages run out.  The engine is a fake that keeps the
+real cache manager's books and returns logits that make the next token predictable."""
+import numpy as np
+import pytest
+import torch
+
+from air_b200.cache.manager import CacheManager, OutOfPages
+from air_b200.engine.scheduler import (CapacityScheduler, MicrobatchScheduler, SchedulableSequence as Seq,
+                                       WorkPhase)
+from air_b200.engine.service import InferenceService, QueueFull, SchedulerConfig
+from air_b200.parts.base import PagedKV
+from air_b200.sampling.sampler import GenerationConfig, SamplingConfig
+
+P, D = WorkPhase.prefill, WorkPhase.decode
+
+
+def test_capacity_arithmetic():
+    c = CapacityScheduler(max_active_requests=2)
+    assert c.evaluate(0, 0, 10, 16, 160).admit                      # exact fit
+    assert c.evaluate(0, 0, 10, 16, 161).reason == "device-capacity"
+    assert c.evaluate(1, 6, 10, 16, 64).admit and not c.evaluate(1, 7, 10, 16, 64).admit
+    assert c.evaluate(2, 0, 10, 16, 1).reason == "max-active-requests"
+    assert c.evaluate(0, 0, 10, 16, 17).reservation_pages == 2
+
+
+def test_decode_first_then_prompts_under_the_budget():
+    s = MicrobatchScheduler()
+    batch = s.schedule([Seq("p1", P, 4), Seq("d1", D, 1), Seq("p2", P, 4), Seq("d2", D, 1)], 5)
+    assert [(x.slot, x.token_count) for x in batch.slices] == [("d1", 1), ("d2", 1), ("p1", 3)]
+    assert (batch.token_count, batch.decode_tokens, batch.prefill_tokens, batch.prefill_sequences) == (5, 2, 3, 1)
+
+
+def test_per_sequence_caps_and_zero_limits():
+    s = MicrobatchScheduler()
+    batch = s.schedule([Seq("a", P, 4), Seq("z", P, 0), Seq("b", P, 4), Seq("c", P, 4)], 9)
+    assert [(x.slot, x.token_count) for x in batch.slices] == [("a", 4), ("b", 4), ("c", 1)]
+    assert s.schedule([Seq("a", P, 4)], 0).slices == [] and s.schedule([], 9).slices == []
+
+
+def test_rotation_under_a_budget_of_one():
+    s = MicrobatchScheduler()
+    cands = [Seq("a", D, 1), Seq("b", D, 1), Seq("c", D, 1)]
+    assert [s.schedule(cands, 1).slices[0].slot for _ in range(6)] == ["a", "b", "c", "a", "b", "c"]
+    s = MicrobatchScheduler()
+    cands = [Seq("x", P, 8), Seq("y", P, 8)]
+    assert [s.schedule(cands, 8).slices[0].slot for _ in range(4)] == ["x", "y", "x", "y"]
+
+
+# ------------------------------------------------------------------ the service over a fake engine
+class FakeSpec:
+    vocab_size, max_positions, eos_token_id = 50, 4096, 49
+
+
+class FakeModel:
+    spec = FakeSpec()
+
+
+class FakeEngine:
+    """The next token after t is (t + 1) % 49 at the request's first logits, and so on; token 48
+    is followed by 49 = eos."""
+
+    def __init__(self, pages, page=16, slots=8):
+        self.cache = CacheManager([(PagedKV(1, 16, None),)], page, pages, slots, allocate=False)
+        self.model = FakeModel()
+        self.steps = []
+
+    def step(self, entries):
+        opened = [e.request for e in entries if e.request not in self.cache.sequences]
+        for r in opened:
+            self.cache.open(r)
+        try:
+            self.cache.reserve([(e.request, len(e.tokens)) for e in entries])
+        except OutOfPages:
+            for r in opened:
+                self.cache.close(r)
+            raise
+        rows = []
+        for e in entries:
+            self.cache.commit(e.request, len(e.tokens))
+            for w in e.want:
+                row = np.zeros(50, dtype=np.float32)
+                row[(e.tokens[w] + 1) % 50] = 5.0
+                rows.append(row)
+        self.steps.append([(e.request, len(e.tokens), list(e.want)) for e in entries])
+        self._rows = len(rows)
+        return torch.tensor(np.array(rows).reshape(len(rows), 50))
+
+    def sample(self, logits, temperature=None, uniform=None):
+        return logits.argmax(-1).to(torch.int32)
+
+    def finish(self, request):
+        self.cache.close(request)
+
+
+def test_prompt_in_portions_then_decode_and_pages_back():
+    eng = FakeEngine(pages=8)
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=4, token_budget_per_cycle=16,
+                                                prefill_quantum_tokens=6))
+    r = svc.generate([1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 20], GenerationConfig(max_new_tokens=4))
+    assert r.tokens == [21, 22, 23, 24] and not r.hit_eos and r.error is None
+    # 14 prompt tokens in portions of 6, 6, 2 (the last one wants logits), then 3 decode steps
+    assert eng.steps == [[(0, 6, [])], [(0, 6, [])], [(0, 2, [1])], [(0, 1, [0])], [(0, 1, [0])], [(0, 1, [0])]]
+    assert eng.cache.free_pages() == 8 and not eng.cache.sequences
+    assert r.metrics.prompt_tokens == 14 and r.metrics.generated_tokens == 4
+
+
+def test_eos_stops_and_zero_new_tokens():
+    eng = FakeEngine(pages=8)
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=4))
+    r = svc.generate([46], GenerationConfig(max_new_tokens=10))
+    assert r.tokens == [47, 48, 49] and r.hit_eos
+    r = svc.generate([46], GenerationConfig(max_new_tokens=10, stop_on_eos=False))
+    assert r.tokens == [47, 48, 49, 0, 1, 2, 3, 4, 5, 6]
+    r = svc.generate([5, 6], GenerationConfig(max_new_tokens=0))
+    assert r.tokens == [] and eng.cache.free_pages() == 8
+
+
+def test_decode_beside_prompt_portions_in_one_step():
+    eng = FakeEngine(pages=32)
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=4, token_budget_per_cycle=8,
+                                                prefill_quantum_tokens=4))
+    out = svc.generate_cohort([([1, 2], GenerationConfig(max_new_tokens=6)),
+                               (list(range(10, 22)), GenerationConfig(max_new_tokens=2))])
+    assert out[0].tokens == [3, 4, 5, 6, 7, 8] and out[1].tokens == [22, 23]
+    mixed = [s for s in eng.steps if len(s) == 2 and {n for _, n, _ in s} != {1}]
+    assert mixed, "a decoded token of one request ran beside a prompt portion of the other"
+    assert all(sum(n for _, n, _ in s) <= 8 for s in eng.steps)
+
+
+def test_admission_waits_for_reserved_pages_and_fails_what_never_fits():
+    eng = FakeEngine(pages=4)                                    # 64 tokens
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=4))
+    a = svc.submit(list(range(30)), GenerationConfig(max_new_tokens=10))     # 40 tokens -> 3 pages
+    b = svc.submit(list(range(20)), GenerationConfig(max_new_tokens=10))     # 30 tokens -> 2 pages: must wait
+    c = svc.submit(list(range(40)), GenerationConfig(max_new_tokens=40))     # 80 tokens -> 5 pages: never fits
+    svc.run_cycle()
+    assert [i.request_id for i in svc.active] == [a] and [i.request_id for i in svc.queued] == [b, c]
+    assert svc.snapshot()["reserved_pages"] == 3
+    while svc.active or svc.queued:
+        svc.run_cycle()
+    assert svc.finished[a].tokens == list(range(30, 40)) and svc.finished[b].tokens == list(range(20, 30))
+    assert svc.finished[c].error == "insufficient KV pages for one sequence" and svc.finished[c].tokens == []
+    assert eng.cache.free_pages() == 4
+
+
+def test_queue_is_bounded_and_requests_are_checked():
+    svc = InferenceService(FakeEngine(pages=4), SchedulerConfig(max_queued_requests=2))
+    svc.submit([1]); svc.submit([2])
+    with pytest.raises(QueueFull):
+        svc.submit([3])
+    with pytest.raises(ValueError, match="vocabulary"):
+        InferenceService(FakeEngine(4)).submit([50])
+    with pytest.raises(ValueError, match="context"):
+        InferenceService(FakeEngine(4)).submit([1] * 4000, GenerationConfig(max_new_tokens=200))
+    with pytest.raises(ValueError, match="top_p"):
+        InferenceService(FakeEngine(4)).submit([1], GenerationConfig(sampling=SamplingConfig(0.5, 0, 1.5, 0)))
+
+
+def test_when_pages_run_out_the_youngest_is_put_back_and_computed_again():
+    eng = FakeEngine(pages=4)                                    # 64 tokens in all
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=4, reserve_worst_case=False,
+                                                prefill_quantum_tokens=16, token_budget_per_cycle=64))
+    out = svc.generate_cohort([(list(range(1, 25)), GenerationConfig(max_new_tokens=20, stop_on_eos=False)),
+                               (list(range(2, 22)), GenerationConfig(max_new_tokens=20, stop_on_eos=False))])
+    # both need 44 and 40 tokens: together more than the pool holds, so one was pre-empted
+    assert svc.preemptions >= 1 and out[1].metrics.preemptions >= 1
+    assert out[0].tokens == [(24 + i) % 50 for i in range(1, 21)]
+    assert out[1].tokens == [(21 + i) % 50 for i in range(1, 21)]
+    assert eng.cache.free_pages() == 4 and not eng.cache.sequences
+    eng.cache.check()
+
+
+def test_a_single_request_that_outgrows_the_pool_fails():
+    eng = FakeEngine(pages=2)
+    svc = InferenceService(eng, SchedulerConfig(reserve_worst_case=False))
+    r = svc.generate(list(range(10)), GenerationConfig(max_new_tokens=30, stop_on_eos=False))
+    assert r.error == "insufficient KV pages for one sequence"
+    assert eng.cache.free_pages() == 2
