@@ -1,0 +1,159 @@
+"""Generation through the Python entry point and the command line against the plain
+implementation: greedy tokens, the first tokens of a sequence, long decoding, temperature
+sampling, several requests at once."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import util
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def service(name, dtype, **kw):
+    from air_b200.engine.engine import Engine, EngineConfig
+    from air_b200.engine.service import InferenceService, SchedulerConfig
+    engine = Engine.from_folder(util.model_folder(name), EngineConfig(
+        dtype=dtype, page_tokens=kw.pop("page_tokens", 16), max_tokens=kw.pop("max_tokens", 1024),
+        max_requests=kw.get("max_active_requests", 8)))
+    return InferenceService(engine, SchedulerConfig(**{"max_active_requests": 8, **kw}))
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain(name):
+    from air_b200 import GenerationConfig
+    folder = util.model_folder(name)
+    cfg, tensors = util.plain_model(folder)
+    svc = service(name, "float32", prefill_quantum_tokens=5, token_budget_per_cycle=12)
+    prompts = [util.tokens_for(name, n, 20 + n) for n in (1, 7, 33)]
+    want = [plain.greedy_generate(cfg, tensors, p, 16) for p in prompts]
+    got = svc.generate_cohort([(p, GenerationConfig(max_new_tokens=16, stop_on_eos=False)) for p in prompts])
+    assert [r.tokens for r in got] == want
+    assert svc.engine.cache.free_pages() == svc.engine.cache.num_pages
+    svc.engine.check_status()
+
+
+def test_first_tokens_of_a_sequence():
+    """Positions 0, 1, 2: one key, two keys, three keys; decoded one by one from the very start."""
+    from air_b200.engine.batch import Entry
+    folder = util.model_folder("B")
+    toks = util.tokens_for("B", 4, 77)
+    want = util.plain_logits(folder, toks)
+    for dtype, tol in (("float32", util.FP32_TOL), ("bfloat16", util.BF16_MAX_TOL)):
+        svc = service("B", dtype)
+        got = np.concatenate([svc.engine.step([Entry("r", [t], [0])]).cpu().numpy() for t in toks])
+        assert np.abs(got - want).max() < tol * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_stays_on_the_plain_logits(dtype):
+    """300 tokens decoded one by one after a short prompt (teacher-forced with the plain
+    implementation's greedy tokens), across many pages."""
+    from air_b200.engine.batch import Entry
+    folder = util.model_folder("A")
+    cfg, tensors = util.plain_model(folder)
+    prompt = util.tokens_for("A", 5, 9)
+    tokens = prompt + plain.greedy_generate(cfg, tensors, prompt, 40)
+    tokens = (tokens * 8)[:320]                      # teacher-forced stream
+    want = util.plain_logits(folder, tokens)
+    svc = service("A", dtype, max_tokens=384)
+    eng = svc.engine
+    got = [eng.step([Entry("r", tokens[:5], range(5))]).cpu().numpy()]
+    got += [eng.step([Entry("r", [t], [0])]).cpu().numpy() for t in tokens[5:]]
+    got = np.concatenate(got)
+    scale = max(1.0, np.abs(want).max())
+    if dtype == "float32":
+        assert np.abs(got - want).max() < util.FP32_TOL * scale
+    else:
+        assert np.abs(got - want).max() < util.BF16_MAX_TOL * scale
+        assert np.abs(got - want).mean() < util.BF16_MEAN_TOL * scale
+
+
+def test_device_feedback_of_sampled_tokens_equals_host_feedback():
+    from air_b200.engine.batch import Entry, LAST_SAMPLED
+    svc = service("B", "float32")
+    eng = svc.engine
+    prompt = util.tokens_for("B", 9, 5)
+    ids = [int(eng.sample(eng.step([Entry("dev", prompt, [8])])).item())]
+    for _ in range(10):
+        ids.append(int(eng.sample(eng.step([Entry("dev", [LAST_SAMPLED], [0])])).item()))
+    cfg, tensors = util.plain_model(util.model_folder("B"))
+    assert ids == plain.greedy_generate(cfg, tensors, prompt, 11)
+
+
+def test_temperature_sampling_mixed_batch_of_config_b():
+    """Prompts of 5, 40 and 97 tokens in portions of 32 beside three requests that decode at
+    temperature 0.8: tokens are reproducible per seed, differ between seeds, and every sampled
+    token has a plausible probability under the plain implementation's distribution."""
+    from air_b200 import GenerationConfig, SamplingConfig
+    folder = util.model_folder("B")
+    cfg, tensors = util.plain_model(folder)
+
+    def run(seed):
+        svc = service("B", "float32", prefill_quantum_tokens=32, token_budget_per_cycle=70)
+        reqs = [(util.tokens_for("B", n, n), GenerationConfig(max_new_tokens=4, stop_on_eos=False)) for n in (5, 40, 97)]
+        reqs += [(util.tokens_for("B", 3, 200 + i), GenerationConfig(
+            max_new_tokens=12, stop_on_eos=False, sampling=SamplingConfig(temperature=0.8, seed=seed + i)))
+            for i in range(3)]
+        return reqs, svc.generate_cohort(reqs)
+
+    reqs, first = run(100)
+    _, again = run(100)
+    _, other = run(500)
+    assert [r.tokens for r in first] == [r.tokens for r in again]
+    assert [r.tokens for r in first[3:]] != [r.tokens for r in other[3:]]
+    for (prompt, g), r in zip(reqs[:3], first[:3]):
+        assert r.tokens == plain.greedy_generate(cfg, tensors, prompt, 4)
+    for (prompt, g), r in zip(reqs[3:], first[3:]):
+        logits = plain.forward(cfg, tensors, prompt + r.tokens)[len(prompt) - 1:-1]
+        p = torch.softmax(torch.tensor(logits).double() / 0.8, -1)
+        chosen = p[torch.arange(len(r.tokens)), torch.tensor(r.tokens)]
+        assert float(chosen.min()) > 1e-5
+
+
+def test_host_sampler_path_with_top_k_and_top_p():
+    from air_b200 import GenerationConfig, SamplingConfig
+    folder = util.model_folder("A")
+    cfg, tensors = util.plain_model(folder)
+    svc = service("A", "float32")
+    prompt = util.tokens_for("A", 6, 1)
+    sampling = SamplingConfig(temperature=0.9, top_k=7, top_p=0.8, seed=11)
+    got = svc.generate(prompt, GenerationConfig(max_new_tokens=8, stop_on_eos=False, sampling=sampling)).tokens
+    s = plain.PlainSampler(0.9, 7, 0.8, 11)
+    toks = list(prompt)
+    for t in got:
+        logits = plain.forward(cfg, tensors, toks)[-1]
+        assert s.sample(logits) == t
+        toks.append(t)
+
+
+def test_command_line(tmp_path):
+    folder = util.model_folder("A")
+    cfg, tensors = util.plain_model(folder)
+    prompt = util.tokens_for("A", 7, 3)
+    exe = [sys.executable, os.path.join(util.ROOT, "bin", "air-b200")]
+    p = subprocess.run(exe + ["cuda", folder, ",".join(map(str, prompt)), "--tokens", "5", "--dtype", "float32",
+                              "--no-stop-on-eos"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr
+    assert [int(t) for t in p.stdout.strip().split(",")] == plain.greedy_generate(cfg, tensors, prompt, 5)
+    p = subprocess.run(exe + ["cuda-compare", folder, ",".join(map(str, prompt))], capture_output=True, text=True,
+                       timeout=300)
+    assert p.returncode == 0, p.stderr
+    report = json.loads(p.stdout)
+    assert report["top1_parity"] and report["float32_whole_vs_token_by_token_max_abs"] <= 1e-5
+    assert subprocess.run(exe + ["cuda", str(tmp_path), "1,2"], capture_output=True).returncode == 3
+    assert subprocess.run(exe + ["cuda"], capture_output=True).returncode == 2
+    p = subprocess.run(exe + ["cuda-info"], capture_output=True, text=True)
+    assert p.returncode == 0 and "B200" in p.stdout
+
+
+def test_smoke_entry():
+    sys.path.insert(0, util.ROOT)
+    import __graft_entry__
+    __graft_entry__.smoke()
