@@ -126,7 +126,8 @@ class CacheManager:
     (for tests of the bookkeeping)."""
 
     def __init__(self, needs_per_run: Sequence[Sequence[object]], page_tokens: int, num_pages: int,
-                 max_requests: int, dtype: torch.dtype = torch.float32, device="cpu", allocate: bool = True):
+                 max_requests: int, dtype: torch.dtype = torch.float32, device="cpu", allocate: bool = True,
+                 max_blocks: Optional[int] = None):
         if page_tokens <= 0 or page_tokens % 16:
             raise CacheError(f"page size {page_tokens} must be a positive multiple of 16")
         if num_pages <= 0:
@@ -159,6 +160,16 @@ class CacheManager:
             self._views.append(tuple(views))
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.sequences: Dict[Hashable, Sequence_] = {}
+        # Block tables on the device, one per group: row = the request's slot, column = block of
+        # page_tokens positions, value = page (or -1).  They are kept up to date by small updates
+        # (slot, block, page) that `flush_tables` sends before a step, so a step copies no tables.
+        self.max_blocks = max_blocks if max_blocks is not None else num_pages
+        self.tables: List[Optional[torch.Tensor]] = []
+        self._updates: List[List[int]] = []
+        for _ in self.groups:
+            self.tables.append(torch.full((max_requests, self.max_blocks), -1, dtype=torch.int32, device=device)
+                               if allocate else None)
+            self._updates.append([])
 
     def _group_of(self, need: PagedKV) -> int:
         for i, g in enumerate(self.groups):
@@ -212,13 +223,17 @@ class CacheManager:
                 want = self.pages_needed(seq.length + n)
                 for gi, g in enumerate(self.groups):
                     pages = seq.pages[gi]
+                    if want > self.max_blocks:
+                        raise CacheError(f"request {request!r} would need {want} blocks, tables have {self.max_blocks}")
                     while len(pages) < want:
                         pages.append(g.pool.take(request))
                         taken.append((gi, request, 1))
+                        self._updates[gi] += [seq.slot, len(pages) - 1, pages[-1]]
         except OutOfPages:
             for gi, request, _ in reversed(taken):
                 page = self.sequences[request].pages[gi].pop()
                 self.groups[gi].pool.give(page, request)
+                del self._updates[gi][-3:]
             raise
 
     def commit(self, request: Hashable, n: int) -> None:
@@ -234,6 +249,20 @@ class CacheManager:
                 if pages[b] >= 0:
                     g.pool.give(pages[b], request)
                     pages[b] = -1
+                    self._updates[gi] += [seq.slot, b, -1]
+
+    def flush_tables(self) -> None:
+        """Sends the pending updates of the block tables to the device."""
+        for gi, upd in enumerate(self._updates):
+            if upd and self.tables[gi] is not None:
+                from ..csrc import ops
+                host = torch.tensor(upd, dtype=torch.int32)
+                if self.tables[gi].is_cuda:
+                    ops.table_update(self.tables[gi], host.pin_memory().to(self.tables[gi].device, non_blocking=True))
+                else:
+                    u = host.view(-1, 3).long()
+                    self.tables[gi][u[:, 0], u[:, 1]] = u[:, 2].int()
+            upd.clear()
 
     def trim(self, request: Hashable) -> None:
         """Gives back pages beyond the committed length (after a step that failed)."""

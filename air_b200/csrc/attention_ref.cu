@@ -9,7 +9,8 @@
 // position and on the cache's contents, not on how the tokens were cut into steps or on
 // what else is in the batch.
 //
-// q, out: [T, H, d].  cache: [page, 2, K, P, d] (keys then values).  block_table: [S, max_blocks].
+// q, out: [T, H, d].  cache: [page, 2, K, P, d] (keys then values).  block_table: [slots, max_blocks],
+// row token_seq[t] for token t (negative: padding, skipped).
 // A query at position p sees keys max(0, p - window + 1) .. p (window 0: all keys).
 #include "common.cuh"
 
@@ -29,6 +30,7 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
     __shared__ float sacc[ATT_WARPS][ATT_MAX_D];
     const int t = blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (token_seq[t] < 0) return;  // padding
     const int pos = positions[t];
     const int kvh = (int)(((long long)h * K) / H);
     const int* bt = block_table + (size_t)token_seq[t] * max_blocks;

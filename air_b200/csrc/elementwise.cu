@@ -54,7 +54,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
 // qkv [T, (H + 2K) d] is the output of the fused projection.  For every token: add the
 // bias, rotate the heads of q and k with the table's cos/sin of the token's position
 // (pairs (i, i + rot/2) of the first `rot` elements of a head), store q to q_out [T, H, d]
-// and k, v into the token's place in the pages: cache [page, 2, K, P, d].
+// and k, v into the token's place in the pages: cache [page, 2, K, P, d].  token_seq[t] is the
+// slot of the token's request = its row of block_table; a negative slot marks padding.
 // table [positions, rot]: cos in the first rot/2 columns, sin in the second.
 template <typename TI, typename TB, typename TO>
 __global__ void qkv_rope_store_kernel(const TI* __restrict__ qkv, const TB* __restrict__ bias,
@@ -64,6 +65,8 @@ __global__ void qkv_rope_store_kernel(const TI* __restrict__ qkv, const TB* __re
                                       TO* __restrict__ q_out, TO* __restrict__ cache,
                                       int H, int K, int d, int P, int write_kv, int* status) {
     const int t = blockIdx.x;
+    const int slot = token_seq[t];
+    if (slot < 0) return;  // padding
     const int pos = positions[t];
     const int width = (H + 2 * K) * d;
     const TI* in = qkv + (size_t)t * width;
@@ -71,7 +74,7 @@ __global__ void qkv_rope_store_kernel(const TI* __restrict__ qkv, const TB* __re
     TO* kdst = nullptr;
     TO* vdst = nullptr;
     if (write_kv) {
-        const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / P];
+        const int page = block_table[(size_t)slot * max_blocks + pos / P];
         if (page < 0) {
             if (threadIdx.x == 0 && status) atomicExch(status, 2);
         } else {
@@ -143,6 +146,13 @@ __global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out,
     }
 }
 
+// ---------------------------------------------------------------- block table updates
+// updates [n, 3]: (slot, block, page) -> table[slot, block] = page
+__global__ void table_update_kernel(int* __restrict__ table, const int* __restrict__ updates, int n, int W) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) table[(size_t)updates[3 * i] * W + updates[3 * i + 1]] = updates[3 * i + 2];
+}
+
 // ---------------------------------------------------------------- conversions
 template <typename TI, typename TO>
 __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
@@ -210,5 +220,11 @@ AIR_API int air_convert(const void* in, int in_dtype, void* out, int out_dtype, 
     AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(out_dtype, TO, {
         convert_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, (size_t)n);
     }));
+    return (int)cudaGetLastError();
+}
+
+AIR_API int air_table_update(int* table, const int* updates, int n, int W, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    table_update_kernel<<<(n + 127) / 128, 128, 0, stream>>>(table, updates, n, W);
     return (int)cudaGetLastError();
 }

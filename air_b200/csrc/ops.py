@@ -26,6 +26,7 @@ _SIGNATURES = {
     "air_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "air_table_update": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -206,3 +207,12 @@ def sample(logits, temperature, uniform, out, status=None, slots=None, last_toke
     _check(_get("air_sample")(logits.data_ptr(), _ptr(temperature), _ptr(uniform), out.data_ptr(), _ptr(slots),
                               _ptr(last_token), R, V, _ptr(status), _stream()), "sample")
     return out
+
+
+def table_update(table, updates):
+    """table[slot, block] = page for every (slot, block, page) of updates (flat int32 [3n])."""
+    _req(table, "table", _I32)
+    _req(updates, "updates", _I32)
+    _check(_get("air_table_update")(table.data_ptr(), updates.data_ptr(), updates.numel() // 3, table.shape[1],
+                                    _stream()), "table_update")
+    return table

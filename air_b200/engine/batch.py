@@ -4,9 +4,10 @@ AIR runs prompt chunks and decoded tokens through different entry points and nev
 launch (src/runtime/serving.cpp:1821-1941; src/cuda/cuda_backend.cu:2890, 3072, 3249).  Here a
 step is one flat list of tokens: any number of requests, each with one or more next tokens.
 The context carries, per token, its id, its position and the index of its request in the
-batch; per request, where its tokens start, its length after the step, its state slot and
-one row of each group's block table.  All of it is packed into one pinned int32 buffer and
-copied to the device once.
+batch; per request, where its tokens start, its length after the step and its state slot.  All of
+it is packed into one pinned int32 buffer and copied to the device once.  The block tables
+stay on the device (one row per slot, kept by the cache manager); kernels find a token's
+pages through its slot.
 """
 from __future__ import annotations
 
@@ -32,13 +33,13 @@ class StepContext:
     num_seqs: int
     token_ids: torch.Tensor        # [T] int32
     positions: torch.Tensor        # [T] int32
-    token_seq: torch.Tensor        # [T] int32: index of the token's request in this batch
+    token_seq: torch.Tensor        # [T] int32: state slot of the token's request (-1: padding, skipped)
     q_start: torch.Tensor          # [S+1] int32
     kv_len: torch.Tensor           # [S] int32: length of the request after this step
     slots: torch.Tensor            # [S] int32: state slot of the request
     logit_rows: torch.Tensor       # [R] int32: flat indices of the tokens whose logits are wanted
     row_slots: torch.Tensor        # [R] int32: state slot of the request of each wanted row
-    block_tables: List[torch.Tensor]   # per group: [S, max_blocks] int32, -1 where no page is held
+    block_tables: List[torch.Tensor]   # per group: [slots, max_blocks] int32 (row = slot), -1 where no page
     status: Optional[torch.Tensor]     # [1] int32, set by kernels that meet an impossible index
     # host copies, for parts that plan on the host
     q_start_host: List[int] = field(default_factory=list)
@@ -67,7 +68,7 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
         n = len(e.tokens)
         ids.extend(int(t) if int(t) >= 0 else -(seq.slot + 1) for t in e.tokens)
         pos.extend(range(seq.length, seq.length + n))
-        tseq.extend([s] * n)
+        tseq.extend([seq.slot] * n)
         for w in e.want:
             if not (0 <= w < n):
                 raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
@@ -77,16 +78,8 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
         kv_len.append(seq.length + n)
         slots.append(seq.slot)
     T, S = len(ids), len(entries)
-    tables = []
-    for gi in range(len(cache.groups)):
-        width = max(1, max((len(cache.sequences[e.request].pages[gi]) for e in entries), default=1))
-        flat = []
-        for e in entries:
-            pages = cache.sequences[e.request].pages[gi]
-            flat.extend(pages)
-            flat.extend([-1] * (width - len(pages)))
-        tables.append((width, flat))
-    sections = [ids, pos, tseq, q_start, kv_len, slots, rows, row_slots] + [t[1] for t in tables]
+    cache.flush_tables()
+    sections = [ids, pos, tseq, q_start, kv_len, slots, rows, row_slots]
     total = sum(len(x) for x in sections)
     host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
     offset = 0
@@ -105,7 +98,7 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
     return StepContext(
         num_tokens=T, num_seqs=S, token_ids=cut(0), positions=cut(1), token_seq=cut(2), q_start=cut(3),
         kv_len=cut(4), slots=cut(5), logit_rows=cut(6), row_slots=cut(7),
-        block_tables=[cut(8 + i).view(S, tables[i][0]) for i in range(len(tables))],
+        block_tables=list(cache.tables),
         status=status, q_start_host=q_start, kv_len_host=kv_len, slots_host=slots,
         max_q_len=max((len(e.tokens) for e in entries), default=0), max_kv_len=max(kv_len, default=0),
         all_decode=all(len(e.tokens) == 1 for e in entries))

@@ -45,6 +45,57 @@ class EngineConfig:
     max_tokens: int = 8192
     max_requests: int = 8
     device: str = "cuda:0"
+    cuda_graphs: bool = True      # decode-only steps replay a captured graph
+
+
+_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class DecodeGraph:
+    """A decode step (every request brings one token) captured as a CUDA graph for a fixed
+    number of tokens.  The batch lives in static device buffers; a step copies 4 ints per token
+    from pinned host memory and replays the graph.  Fewer requests than the graph's size are
+    padded with slot -1, which every kernel skips."""
+    RING = 8
+
+    def __init__(self, engine: "Engine", size: int):
+        dev = engine.rt.device
+        self.size, self.engine = size, engine
+        self.ints = torch.zeros(4 * size, dtype=torch.int32, device=dev)
+        self.ints[2 * size:3 * size] = -1
+        self.fixed = torch.arange(size + 1, dtype=torch.int32, device=dev)
+        self.host = [torch.zeros(4 * size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.turn = 0
+        ids, pos, slot, kvl = (self.ints[i * size:(i + 1) * size] for i in range(4))
+        self.ctx = StepContext(
+            num_tokens=size, num_seqs=size, token_ids=ids, positions=pos, token_seq=slot, q_start=self.fixed,
+            kv_len=kvl, slots=slot, logit_rows=self.fixed[:size], row_slots=slot,
+            block_tables=list(engine.cache.tables), status=engine.status, max_q_len=1, all_decode=True,
+            last_token=engine.last_token)
+        # once eagerly on padding (so that every lazy set-up is done), then captured
+        engine.model.forward(self.ctx, engine.cache)
+        torch.cuda.synchronize()
+        before = ops.launches
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = engine.model.forward(self.ctx, engine.cache)
+        self.kernels = ops.launches - before
+
+    def run(self, ids, positions, slots) -> torch.Tensor:
+        n, size = len(ids), self.size
+        i = self.turn = (self.turn + 1) % self.RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        pad = size - n
+        self.host[i].copy_(torch.tensor(ids + [0] * pad + positions + [0] * pad + slots + [-1] * pad +
+                                        [p + 1 for p in positions] + [0] * pad, dtype=torch.int32))
+        self.ints.copy_(self.host[i], non_blocking=True)
+        ev = self.events[i] = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.graph.replay()
+        self.engine.graph_kernel_launches += self.kernels
+        return self.logits[:n]
 
 
 class Engine:
@@ -52,13 +103,17 @@ class Engine:
         self.model, self.config, self.model_config = model, config, model_config
         self.rt = model.rt
         num_pages = max(1, -(-config.max_tokens // config.page_tokens))
+        max_blocks = -(-min(model.spec.max_positions, num_pages * config.page_tokens) // config.page_tokens)
         self.cache = CacheManager(model.cache_needs(), config.page_tokens, num_pages, config.max_requests,
-                                  dtype=self.rt.dtype, device=self.rt.device)
+                                  dtype=self.rt.dtype, device=self.rt.device, max_blocks=max_blocks)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
         self.last_token = torch.zeros(config.max_requests, dtype=torch.int32, device=self.rt.device)
         self.last_context: Optional[StepContext] = None
         self.steps = 0
         self.graph_kernel_launches = 0
+        self.graphs = {}
+        self.use_graphs = config.cuda_graphs and all(
+            getattr(b.mixer, "graph_safe", False) for b in model.blocks)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -92,7 +147,8 @@ class Engine:
         one decoded token, any mix).  Returns float32 logits [wanted places, vocab] on the
         device, in the order of the entries and of their `want`.  A request is opened at its
         first tokens.  On failure (OutOfPages, a token outside the vocabulary) nothing is
-        committed and pages taken for the step are given back."""
+        committed and pages taken for the step are given back.  The returned logits may live in
+        a buffer that the next step overwrites: use them (or copy them) before stepping again."""
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
         vocab, limit = self.model.spec.vocab_size, self.model.spec.max_positions
         seen = set()
@@ -121,9 +177,13 @@ class Engine:
                 self.cache.close(r)
             raise
         try:
-            ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
-            ctx.last_token = self.last_token
-            logits = self.model.forward(ctx, self.cache)
+            if self.use_graphs and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries) \
+                    and len(entries) <= _BUCKETS[-1]:
+                logits, ctx = self._decode_step(entries)
+            else:
+                ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+                ctx.last_token = self.last_token
+                logits = self.model.forward(ctx, self.cache)
         except Exception:
             for e in entries:
                 if e.request in opened:
@@ -136,6 +196,26 @@ class Engine:
         self.steps += 1
         self.last_context = ctx
         return logits
+
+    def _decode_step(self, entries):
+        seqs = [self.cache.sequences[e.request] for e in entries]
+        size = next(b for b in _BUCKETS if b >= len(entries))
+        graph = self.graphs.get(size)
+        if graph is None:
+            graph = self.graphs[size] = DecodeGraph(self, size)
+        self.cache.flush_tables()
+        ids = [int(e.tokens[0]) if int(e.tokens[0]) >= 0 else -(s.slot + 1) for e, s in zip(entries, seqs)]
+        logits = graph.run(ids, [s.length for s in seqs], [s.slot for s in seqs])
+        n = len(entries)
+        c = graph.ctx
+        ctx = StepContext(
+            num_tokens=n, num_seqs=n, token_ids=c.token_ids[:n], positions=c.positions[:n], token_seq=c.token_seq[:n],
+            q_start=c.q_start[:n + 1], kv_len=c.kv_len[:n], slots=c.slots[:n], logit_rows=c.logit_rows[:n],
+            row_slots=c.row_slots[:n], block_tables=c.block_tables, status=self.status,
+            q_start_host=list(range(n + 1)), kv_len_host=[s.length + 1 for s in seqs],
+            slots_host=[s.slot for s in seqs], max_q_len=1, max_kv_len=max(s.length + 1 for s in seqs),
+            all_decode=True, last_token=self.last_token)
+        return logits, ctx
 
     def sample(self, logits: torch.Tensor, temperature=None, uniform=None) -> torch.Tensor:
         """Chooses a token for every row of the last step's logits on the device: the lowest

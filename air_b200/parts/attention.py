@@ -30,6 +30,8 @@ class Attention(Mixer):
     attention kernel reads keys and values only from the pages, for prompt portions and
     decoded tokens alike."""
 
+    graph_safe = True
+
     def __init__(self, spec, prefix=""):
         super().__init__(spec, prefix)
         p = spec.params

@@ -86,6 +86,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward() only launches work on the current stream from device data (no host
+    # reads of the batch), so that a decode step can be captured in a CUDA graph.
+    graph_safe: bool = False
+
     def cache_needs(self) -> Tuple[CacheNeed, ...]:
         return ()
 
