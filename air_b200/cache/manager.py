@@ -163,13 +163,15 @@ class CacheManager:
         # Block tables on the device, one per group: row = the request's slot, column = block of
         # page_tokens positions, value = page (or -1).  They are kept up to date by small updates
         # (slot, block, page) that `flush_tables` sends before a step, so a step copies no tables.
-        self.max_blocks = max_blocks if max_blocks is not None else num_pages
+        # max_blocks bounds a request's length (in a group with a window a request may be longer
+        # than the whole pool, since it gives old pages back).
+        self.max_blocks = max_blocks if max_blocks is not None else (num_pages if allocate else 1 << 30)
         self.tables: List[Optional[torch.Tensor]] = []
-        self._updates: List[List[int]] = []
+        self._updates: List[Dict[Tuple[int, int], int]] = []   # (slot, block) -> page: the last write wins
         for _ in self.groups:
             self.tables.append(torch.full((max_requests, self.max_blocks), -1, dtype=torch.int32, device=device)
                                if allocate else None)
-            self._updates.append([])
+            self._updates.append({})
 
     def _group_of(self, need: PagedKV) -> int:
         for i, g in enumerate(self.groups):
@@ -217,23 +219,26 @@ class CacheManager:
     def reserve(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
         """Makes room for `n` more tokens of each request in the batch: all of it or none."""
         taken: List[Tuple[int, Hashable, int]] = []  # (group, request, blocks appended)
+        for request, n in batch:
+            want = self.pages_needed(self.sequences[request].length + n)
+            if want > self.max_blocks:
+                raise CacheError(f"request {request!r} would need {want} blocks, tables have {self.max_blocks}")
         try:
             for request, n in batch:
                 seq = self.sequences[request]
                 want = self.pages_needed(seq.length + n)
                 for gi, g in enumerate(self.groups):
                     pages = seq.pages[gi]
-                    if want > self.max_blocks:
-                        raise CacheError(f"request {request!r} would need {want} blocks, tables have {self.max_blocks}")
                     while len(pages) < want:
                         pages.append(g.pool.take(request))
                         taken.append((gi, request, 1))
-                        self._updates[gi] += [seq.slot, len(pages) - 1, pages[-1]]
+                        self._updates[gi][(seq.slot, len(pages) - 1)] = pages[-1]
         except OutOfPages:
             for gi, request, _ in reversed(taken):
                 page = self.sequences[request].pages[gi].pop()
                 self.groups[gi].pool.give(page, request)
-                del self._updates[gi][-3:]
+                seq = self.sequences[request]
+                self._updates[gi].pop((seq.slot, len(seq.pages[gi])), None)
             raise
 
     def commit(self, request: Hashable, n: int) -> None:
@@ -249,14 +254,15 @@ class CacheManager:
                 if pages[b] >= 0:
                     g.pool.give(pages[b], request)
                     pages[b] = -1
-                    self._updates[gi] += [seq.slot, b, -1]
+                    self._updates[gi][(seq.slot, b)] = -1
 
     def flush_tables(self) -> None:
         """Sends the pending updates of the block tables to the device."""
         for gi, upd in enumerate(self._updates):
             if upd and self.tables[gi] is not None:
                 from ..csrc import ops
-                host = torch.tensor(upd, dtype=torch.int32)
+                host = torch.tensor([x for (slot, block), page in upd.items() for x in (slot, block, page)],
+                                    dtype=torch.int32)
                 if self.tables[gi].is_cuda:
                     ops.table_update(self.tables[gi], host.pin_memory().to(self.tables[gi].device, non_blocking=True))
                 else:

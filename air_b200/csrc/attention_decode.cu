@@ -1,0 +1,304 @@
+// Decode attention over the paged cache for bfloat16: one query token per request, grouped
+// query heads, keys split over several blocks (split-KV) and merged by a second kernel.
+//
+// Decoding reads every key and value of the request once and does little arithmetic on them,
+// so the kernel is built around the memory system: each warp streams its own 16-key tiles
+// straight from global memory into registers with 16-byte loads and feeds them to the tensor
+// cores (mma.sync m16n8k16, bf16 in, fp32 out) with the query heads of the group as the M
+// dimension, so the G query heads that share a kv head share every byte that is loaded.
+// Nothing is staged in shared memory and nothing is transposed by ldmatrix:
+//
+//  * S = Q K^T: the k index of the MMA is the head dimension.  A dot product does not care in
+//    which order its terms are added, so the k slots of an MMA are mapped to the head dimension
+//    such that a thread's slots are 8 consecutive elements of a row of K (one 16-byte load)
+//    and the same 8 elements of a row of Q.
+//  * O = P V: the MMA's B operand wants, per register, the same column of two consecutive keys.
+//    A thread loads 8 consecutive columns of the four keys it is responsible for and builds
+//    those registers with one byte-permute each; the n index of the MMA is mapped to the head
+//    dimension accordingly and mapped back when O is written.
+//
+// grid = (splits, kv_heads * head_blocks, tokens), 4 warps.  Block (s, ., t) takes the s-th share
+// of the token's 16-key tiles; its warps take tiles round-robin, each with its own running
+// maximum, sum and output (online softmax in 32-bit), merged through shared memory.  With one
+// split the block writes the output; otherwise it writes (max, sum, unnormalised output) to
+// scratch memory and `decode_combine_kernel` merges the splits.
+//
+// q, out: [T, H, D] bf16.  cache: [page, 2, K, P, D] bf16.  block_table [slots, max_blocks].
+// token_seq[t]: slot (negative: padding, skipped).  A query at position p sees keys
+// max(0, p - window + 1) .. p (window 0: all).
+#include "common.cuh"
+
+namespace air {
+
+constexpr int DEC_WARPS = 4;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint4 ldg16(const void* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                        const int* __restrict__ block_table, int max_blocks,
+                        const int* __restrict__ token_seq, const int* __restrict__ positions,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int H, int K, int P, int window, float scale_log2) {
+    constexpr int KC = D / 32;   // 32-element chunks of the head dimension (QK^T)
+    constexpr int NT = D / 8;    // 8-column tiles of the output (PV)
+    constexpr int NG = D / 64;   // 64-column groups
+    extern __shared__ float smem[];
+    float* sm_o = smem;                          // [warps][16][D]
+    float* sm_m = smem + DEC_WARPS * 16 * D;     // [warps][16]
+    float* sm_l = sm_m + DEC_WARPS * 16;         // [warps][16]
+
+    const int t = blockIdx.z;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int G = H / K;
+    const int head_blocks = (G + 15) / 16;
+    const int kvh = blockIdx.y / head_blocks, hb = blockIdx.y % head_blocks;
+    const int split = blockIdx.x, splits = gridDim.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tq = lane & 3;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* bt = block_table + (size_t)slot * max_blocks;
+
+    // this block's tiles
+    const int tile0 = lo / 16, tile1 = pos / 16 + 1;
+    const int per = (tile1 - tile0 + splits - 1) / splits;
+    const int begin = tile0 + split * per, end = min(tile1, begin + per);
+
+    // query fragments: rows g and g + 8 of the block of 16 heads
+    const int r0 = hb * 16 + g, r1 = r0 + 8;
+    uint4 qa[KC], qb[KC];
+#pragma unroll
+    for (int c = 0; c < KC; ++c) {
+        qa[c] = r0 < G ? ldg16(q + ((size_t)t * H + kvh * G + r0) * D + 32 * c + 8 * tq) : make_uint4(0, 0, 0, 0);
+        qb[c] = r1 < G ? ldg16(q + ((size_t)t * H + kvh * G + r1) * D + 32 * c + 8 * tq) : make_uint4(0, 0, 0, 0);
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const size_t page_stride = (size_t)2 * K * P * D;
+    const size_t v_offset = (size_t)K * P * D;
+    for (int tile = begin + warp; tile < end; tile += DEC_WARPS) {
+        const int kbase = tile * 16;
+        const int page = bt[kbase / P];
+        const __nv_bfloat16* kp = cache + (size_t)page * page_stride + ((size_t)kvh * P + (kbase % P)) * D;
+        const __nv_bfloat16* vp = kp + v_offset;
+        // K: rows g and 8 + g of the tile; V: rows 2tq, 2tq+1, 8+2tq, 9+2tq
+        uint4 kf[2][KC];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < KC; ++c) kf[j][c] = ldg16(kp + (size_t)(8 * j + g) * D + 32 * c + 8 * tq);
+        uint4 vf[4][NG];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int n = 0; n < NG; ++n)
+                vf[i][n] = ldg16(vp + (size_t)(2 * tq + (i & 1) + 8 * (i >> 1)) * D + 64 * n + 8 * g);
+
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int c = 0; c < KC; ++c) {
+                mma_bf16_16816(s[j], qa[c].x, qb[c].x, qa[c].y, qb[c].y, kf[j][c].x, kf[j][c].y);
+                mma_bf16_16816(s[j], qa[c].z, qb[c].z, qa[c].w, qb[c].w, kf[j][c].z, kf[j][c].w);
+            }
+        }
+        // mask and scale (scores in units of log2 e)
+        float tm0 = -INFINITY, tm1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = kbase + 8 * j + 2 * tq + e;
+                const bool ok = key >= lo && key <= pos;
+                s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+                s[j][2 + e] = ok ? s[j][2 + e] * scale_log2 : -INFINITY;
+                tm0 = fmaxf(tm0, s[j][e]);
+                tm1 = fmaxf(tm1, s[j][2 + e]);
+            }
+        tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1));
+        tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
+        tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1));
+        tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
+        const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);
+        if (n0 == -INFINITY) continue;   // no visible key yet (same for both rows and all lanes)
+        const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);
+        m0 = n0;
+        m1 = n1;
+        float p[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            p[j][0] = exp2f(s[j][0] - n0);
+            p[j][1] = exp2f(s[j][1] - n0);
+            p[j][2] = exp2f(s[j][2] - n1);
+            p[j][3] = exp2f(s[j][3] - n1);
+        }
+        l0 = l0 * c0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
+        l1 = l1 * c1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+        const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa1 = pack_bf16(p[0][2], p[0][3]);
+        const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]), pa3 = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            o[n][0] *= c0;
+            o[n][1] *= c0;
+            o[n][2] *= c1;
+            o[n][3] *= c1;
+        }
+#pragma unroll
+        for (int n = 0; n < NG; ++n) {
+            const uint32_t a[4] = {vf[0][n].x, vf[0][n].y, vf[0][n].z, vf[0][n].w};   // key 2tq
+            const uint32_t b[4] = {vf[1][n].x, vf[1][n].y, vf[1][n].z, vf[1][n].w};   // key 2tq + 1
+            const uint32_t c[4] = {vf[2][n].x, vf[2][n].y, vf[2][n].z, vf[2][n].w};   // key 8 + 2tq
+            const uint32_t d[4] = {vf[3][n].x, vf[3][n].y, vf[3][n].z, vf[3][n].w};   // key 9 + 2tq
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                mma_bf16_16816(o[8 * n + 2 * w], pa0, pa1, pa2, pa3, __byte_perm(a[w], b[w], 0x5410),
+                               __byte_perm(c[w], d[w], 0x5410));
+                mma_bf16_16816(o[8 * n + 2 * w + 1], pa0, pa1, pa2, pa3, __byte_perm(a[w], b[w], 0x7632),
+                               __byte_perm(c[w], d[w], 0x7632));
+            }
+        }
+    }
+    // sums over the four threads of a row
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // merge the warps.  Output tile n, accumulator e holds column (n/8)*64 + 8*(2tq + (e&1)) + n%8.
+    if (tq == 0) {
+        sm_m[warp * 16 + g] = m0;
+        sm_m[warp * 16 + g + 8] = m1;
+        sm_l[warp * 16 + g] = l0;
+        sm_l[warp * 16 + g + 8] = l1;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int col = (n / 8) * 64 + 8 * (2 * tq + (e & 1)) + (n % 8);
+            sm_o[(warp * 16 + g + 8 * (e >> 1)) * D + col] = o[n][e];
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * D; idx += blockDim.x) {
+        const int r = idx / D, col = idx % D;
+        if (hb * 16 + r >= G) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, sm_m[w * 16 + r]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float wgt = sm_m[w * 16 + r] == -INFINITY ? 0.f : exp2f(sm_m[w * 16 + r] - mm);
+            acc += sm_o[(w * 16 + r) * D + col] * wgt;
+            ll += sm_l[w * 16 + r] * wgt;
+        }
+        const int h = kvh * G + hb * 16 + r;
+        if (splits == 1) {
+            out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll);
+        } else {
+            const size_t pi = ((size_t)t * H + h) * splits + split;
+            part_o[pi * D + col] = acc;
+            if (col == 0) {
+                part_ml[pi * 2] = mm;
+                part_ml[pi * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+// Merges the splits of one (token, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+template <int D>
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      const int* __restrict__ token_seq, __nv_bfloat16* __restrict__ out, int H,
+                                      int splits) {
+    const int t = blockIdx.y, h = blockIdx.x;
+    if (token_seq[t] < 0) return;
+    const size_t base = ((size_t)t * H + h) * splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    float ll = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = part_ml[(base + s) * 2];
+        ll += m == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(m - mm);
+    }
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float m = part_ml[(base + s) * 2];
+            if (m != -INFINITY) acc += part_o[(base + s) * D + col] * exp2f(m - mm);
+        }
+        out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll);
+    }
+}
+
+template <int D>
+int launch_decode(const void* q, const void* cache, const int* block_table, int max_blocks, const int* token_seq,
+                  const int* positions, void* out, float* part_o, float* part_ml, int T, int H, int K, int P,
+                  int window, float scale, int splits, cudaStream_t stream) {
+    const int G = H / K;
+    const int head_blocks = (G + 15) / 16;
+    const size_t smem = (size_t)(DEC_WARPS * 16 * D + 2 * DEC_WARPS * 16) * sizeof(float);
+    auto kernel = decode_attention_kernel<D>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(splits, K * head_blocks, T);
+    kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, max_blocks, token_seq, positions,
+        (__nv_bfloat16*)out, part_o, part_ml, H, K, P, window, scale * 1.4426950408889634f);
+    if (splits > 1) {
+        decode_combine_kernel<D><<<dim3(H, T), D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, token_seq,
+                                                                              (__nv_bfloat16*)out, H, splits);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace air
+
+// Scratch: part_o needs T*H*splits*D floats and part_ml T*H*splits*2 floats when splits > 1.
+AIR_API int air_decode_attention(const void* q, const void* cache, const int* block_table, int max_blocks,
+                                 const int* token_seq, const int* positions, void* out, float* part_o,
+                                 float* part_ml, int T, int H, int K, int D, int P, int window, float scale,
+                                 int splits, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || K <= 0 || H % K || P % 16 || splits < 1 || T > 65535 || (splits > 1 && (!part_o || !part_ml)))
+        return AIR_ERR_BAD_ARGUMENT;
+    switch (D) {
+        case 64:
+            return air::launch_decode<64>(q, cache, block_table, max_blocks, token_seq, positions, out, part_o, part_ml,
+                                          T, H, K, P, window, scale, splits, stream);
+        case 128:
+            return air::launch_decode<128>(q, cache, block_table, max_blocks, token_seq, positions, out, part_o,
+                                           part_ml, T, H, K, P, window, scale, splits, stream);
+        case 256:
+            return air::launch_decode<256>(q, cache, block_table, max_blocks, token_seq, positions, out, part_o,
+                                           part_ml, T, H, K, P, window, scale, splits, stream);
+        default:
+            return AIR_ERR_BAD_ARGUMENT;
+    }
+}

@@ -27,6 +27,8 @@ _SIGNATURES = {
     "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "air_table_update": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "air_decode_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -216,3 +218,47 @@ def table_update(table, updates):
     _check(_get("air_table_update")(table.data_ptr(), updates.data_ptr(), updates.numel() // 3, table.shape[1],
                                     _stream()), "table_update")
     return table
+
+
+DECODE_HEAD_DIMS = (64, 128, 256)
+
+
+def decode_splits(tokens: int, heads: int, kv_heads: int) -> int:
+    """How many blocks share the keys of one (token, kv head): enough to fill the GPU."""
+    per_split = tokens * kv_heads * (-(-(heads // kv_heads) // 16))
+    return max(1, min(32, -(-444 // per_split)))
+
+
+def decode_attention(q, cache, block_table, token_seq, positions, out, window, scale, splits=None, scratch=None):
+    """bfloat16 attention for one query token per request (see attention_decode.cu).  scratch:
+    (float32 [T*H*splits*D], float32 [T*H*splits*2]) or None to allocate."""
+    T, H, d = q.shape
+    K, P = cache.shape[2], cache.shape[3]
+    _req(q, "q", (torch.bfloat16,))
+    _req(cache, "cache", (torch.bfloat16,), (None, 2, None, None, d))
+    _req(block_table, "block_table", _I32)
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(positions, "positions", _I32, (T,))
+    _req(out, "out", (torch.bfloat16,), (T, H, d))
+    if d not in DECODE_HEAD_DIMS:
+        raise KernelError(f"decode_attention takes head sizes {DECODE_HEAD_DIMS}, not {d}")
+    if splits is None:
+        splits = decode_splits(T, H, K)
+    po = pm = None
+    if splits > 1:
+        if scratch is None:
+            scratch = (torch.empty(T * H * splits * d, dtype=torch.float32, device=q.device),
+                       torch.empty(T * H * splits * 2, dtype=torch.float32, device=q.device))
+        po, pm = scratch
+        _req(po, "scratch[0]", (torch.float32,))
+        _req(pm, "scratch[1]", (torch.float32,))
+        if po.numel() < T * H * splits * d or pm.numel() < T * H * splits * 2:
+            raise KernelError("decode_attention: scratch is too small")
+    global launches
+    _check(_get("air_decode_attention")(
+        q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
+        positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P, int(window or 0), float(scale),
+        splits, _stream()), "decode_attention")
+    if splits > 1:
+        launches += 1
+    return out

@@ -103,7 +103,7 @@ class Engine:
         self.model, self.config, self.model_config = model, config, model_config
         self.rt = model.rt
         num_pages = max(1, -(-config.max_tokens // config.page_tokens))
-        max_blocks = -(-min(model.spec.max_positions, num_pages * config.page_tokens) // config.page_tokens)
+        max_blocks = -(-model.spec.max_positions // config.page_tokens)
         self.cache = CacheManager(model.cache_needs(), config.page_tokens, num_pages, config.max_requests,
                                   dtype=self.rt.dtype, device=self.rt.device, max_blocks=max_blocks)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)

@@ -293,3 +293,40 @@ def test_kernels_refuse_what_they_cannot_take():
         o.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
     with pytest.raises(o.KernelError, match="shape"):
         o.gemm_f32(torch.zeros(2, 8, device="cuda"), torch.zeros(3, 9, device="cuda"), None, torch.zeros(2, 3, device="cuda"))
+
+
+@pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (4, 4, 128, 16), (40, 2, 64, 32), (8, 1, 256, 16)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_decode_attention(H, K, d, P, window, splits):
+    """One query per request, groups of 1 to 20 query heads per kv head, contexts from one key
+    to several pages, any number of splits (also more splits than tiles)."""
+    lens = [700, 1, 16, 17, 333, 64]
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, lens, [1] * len(lens), "bfloat16", seed=H + splits,
+                                                         num_pages=80)
+    # a padded token in the middle is skipped
+    q = np.insert(q, 2, 0, axis=0)
+    positions = np.insert(positions, 2, 0).astype(np.int32)
+    seq_of = np.insert(seq_of, 2, -1).astype(np.int32)
+    out = torch.full(q.shape, 7.0, dtype=torch.bfloat16, device="cuda")
+    ops().decode_attention(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(seq_of), dev(positions), out,
+                           window, 1.0 / math.sqrt(d), splits=splits)
+    keep = seq_of >= 0
+    want = attention_reference(q[keep], ks, vs, positions[keep], seq_of[keep], window)
+    got = out.float().cpu().numpy()
+    assert np.abs(got[keep] - want).max() < 1e-2 * max(1.0, np.abs(want).max())
+    assert (got[~keep] == 7.0).all()
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 1000, 2047])
+def test_decode_attention_finds_one_far_key(far):
+    H, K, d, P, n = 14, 2, 128, 64, 2048
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [1], "bfloat16", seed=far, num_pages=40)
+    q[:] = 0.5
+    cache[bt[0, far // P], 0, :, far % P, :] = 8.0       # score 0.5*8*128/sqrt(128) = 45 against |score| < 6
+    out = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
+    ops().decode_attention(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(seq_of), dev(positions), out,
+                           0, 1.0 / math.sqrt(d))
+    got = out.float().cpu().numpy()[0]
+    for h in range(H):
+        assert np.abs(got[h] - vs[0][far, h * K // H]).max() < 2e-2
