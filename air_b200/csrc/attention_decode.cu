@@ -302,3 +302,76 @@ AIR_API int air_decode_attention(const void* q, const void* cache, const int* bl
             return AIR_ERR_BAD_ARGUMENT;
     }
 }
+
+// ---------------------------------------------------------------------------------------------
+// air_decode_attention_static: the same attention for callers that must not allocate.
+// Declared and described in no_alloc.h.
+#include <mutex>
+
+#include "no_alloc.h"
+
+// The split-KV partial results live here instead of in memory that the caller allocates.  Every
+// GPU that loads this library holds these AIR_STATIC_SCRATCH_FLOATS * 4 bytes until the process
+// exits.  In host code this name is only a handle for cudaGetSymbolAddress, not a device address.
+static __device__ __align__(256) float g_static_scratch[AIR_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_address[kMaxDevices] = {};
+std::mutex g_scratch_mutex;
+
+// The device address of g_static_scratch on the current device, looked up once per device.
+int static_scratch(float** address) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= kMaxDevices) return AIR_ERR_BAD_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_address[device] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_scratch_address[device] = static_cast<float*>(p);
+    }
+    *address = g_scratch_address[device];
+    return 0;
+}
+}  // namespace
+
+AIR_API long long air_decode_attention_static_capacity(void) { return AIR_STATIC_SCRATCH_FLOATS; }
+
+AIR_API long long air_decode_attention_static_need(int T, int H, int D, int splits) {
+    if (splits <= 1) return 0;
+    return (long long)T * H * splits * (D + 2);
+}
+
+AIR_API const char* air_decode_attention_static_error(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case AIR_ERR_BAD_ARGUMENT: return "a size that the decode attention kernel does not take";
+        case AIR_ERR_STATIC_SCRATCH: return "tokens * heads * splits * (head_dim + 2) exceeds the built-in scratch "
+                                            "(air_decode_attention_static_capacity floats): use fewer splits or "
+                                            "fewer tokens per call";
+        default: return "a CUDA error (the code is a cudaError_t)";
+    }
+}
+
+AIR_API int air_decode_attention_static(const void* q, const void* cache, const int* block_table, int max_blocks,
+                                        const int* token_seq, const int* positions, void* out, int T, int H, int K,
+                                        int D, int P, int window, float scale, int splits, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (splits < 1 || H <= 0 || D <= 0) return AIR_ERR_BAD_ARGUMENT;
+    const long long need = air_decode_attention_static_need(T, H, D, splits);
+    if (need > AIR_STATIC_SCRATCH_FLOATS) return AIR_ERR_STATIC_SCRATCH;
+    float* scratch = nullptr;
+    if (splits > 1) {
+        const int rc = static_scratch(&scratch);
+        if (rc != 0) return rc;
+    }
+    // Layout in the scratch: outputs [T*H*splits*D], then (max, sum) pairs [T*H*splits*2].  Nothing
+    // has to be cleared: every entry that the merge reads is written by this call's first kernel.
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)T * H * splits * D : nullptr;
+    return air_decode_attention(q, cache, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
+                                K, D, P, window, scale, splits, stream);
+}
