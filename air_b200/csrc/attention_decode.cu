@@ -27,27 +27,11 @@
 // token_seq[t]: slot (negative: padding, skipped).  A query at position p sees keys
 // max(0, p - window + 1) .. p (window 0: all).
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace air {
 
 constexpr int DEC_WARPS = 4;
-
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-__device__ __forceinline__ uint4 ldg16(const void* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
-}
 
 template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)

@@ -29,6 +29,8 @@ _SIGNATURES = {
     "air_table_update": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_decode_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "air_prefill_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                              c_int, c_int, c_float, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -261,4 +263,22 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
         splits, _stream()), "decode_attention")
     if splits > 1:
         launches += 1
+    return out
+
+
+def prefill_attention(q, cache, block_table, tiles, out, window, scale):
+    """bfloat16 causal attention for tiles of up to 16 consecutive tokens of a request (see
+    attention_prefill.cu).  tiles [n, 4] int32: (slot, first token, its position, rows)."""
+    T, H, d = q.shape
+    K, P = cache.shape[2], cache.shape[3]
+    _req(q, "q", (torch.bfloat16,))
+    _req(cache, "cache", (torch.bfloat16,), (None, 2, None, None, d))
+    _req(block_table, "block_table", _I32)
+    _req(tiles, "tiles", _I32, (None, 4))
+    _req(out, "out", (torch.bfloat16,), (T, H, d))
+    if d not in DECODE_HEAD_DIMS:
+        raise KernelError(f"prefill_attention takes head sizes {DECODE_HEAD_DIMS}, not {d}")
+    _check(_get("air_prefill_attention")(
+        q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(),
+        tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _stream()), "prefill_attention")
     return out

@@ -49,6 +49,7 @@ class StepContext:
     max_kv_len: int = 0
     all_decode: bool = False
     last_token: Optional[torch.Tensor] = None   # [slots] int32: the device's last choice per request
+    tiles: Optional[torch.Tensor] = None        # [n, 4] int32: (slot, first token, its position, rows <= 16)
 
 
 def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepContext:
@@ -63,12 +64,15 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
     slots: List[int] = []
     rows: List[int] = []
     row_slots: List[int] = []
+    tiles: List[int] = []
     for s, e in enumerate(entries):
         seq = cache.sequences[e.request]
         n = len(e.tokens)
         ids.extend(int(t) if int(t) >= 0 else -(seq.slot + 1) for t in e.tokens)
         pos.extend(range(seq.length, seq.length + n))
         tseq.extend([seq.slot] * n)
+        for i in range(0, n, 16):
+            tiles += [seq.slot, q_start[-1] + i, seq.length + i, min(16, n - i)]
         for w in e.want:
             if not (0 <= w < n):
                 raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
@@ -79,7 +83,7 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
         slots.append(seq.slot)
     T, S = len(ids), len(entries)
     cache.flush_tables()
-    sections = [ids, pos, tseq, q_start, kv_len, slots, rows, row_slots]
+    sections = [ids, pos, tseq, q_start, kv_len, slots, rows, row_slots, tiles]
     total = sum(len(x) for x in sections)
     host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
     offset = 0
@@ -98,7 +102,7 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
     return StepContext(
         num_tokens=T, num_seqs=S, token_ids=cut(0), positions=cut(1), token_seq=cut(2), q_start=cut(3),
         kv_len=cut(4), slots=cut(5), logit_rows=cut(6), row_slots=cut(7),
-        block_tables=list(cache.tables),
+        block_tables=list(cache.tables), tiles=cut(8).view(-1, 4),
         status=status, q_start_host=q_start, kv_len_host=kv_len, slots_host=slots,
         max_q_len=max((len(e.tokens) for e in entries), default=0), max_kv_len=max(kv_len, default=0),
         all_decode=all(len(e.tokens) == 1 for e in entries))

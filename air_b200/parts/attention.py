@@ -96,8 +96,10 @@ class Attention(Mixer):
         ops.qkv_rope_store(qkv, self.bias, self.position.table(), ctx.positions, ctx.token_seq, bt, q, pages.kv,
                            H, K, d, write_kv=owns_cache, status=ctx.status)
         out = torch.empty_like(q)
-        if rt.dtype == torch.bfloat16 and ctx.all_decode and d in ops.DECODE_HEAD_DIMS:
+        if rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.all_decode:
             ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
+        elif rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.tiles is not None:
+            ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale)
         else:
             ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         return self.o(out.view(T, H * d), torch.float32)

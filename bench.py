@@ -150,9 +150,10 @@ def decode_e2e(engine, requests, steps, warmup, torch):
     torch.cuda.synchronize()
     sec = time.perf_counter() - t0
     ctx = engine.last_context
-    h2d = sum(t.numel() * 4 for t in (ctx.token_ids, ctx.positions, ctx.token_seq, ctx.q_start, ctx.kv_len,
-                                      ctx.slots, ctx.logit_rows, ctx.row_slots)) + \
-        sum(b.numel() * 4 for b in ctx.block_tables)
+    # per step: 4 ints per token of the decode graph's batch from pinned memory; sampled ids back
+    size = next(iter(engine.graphs.values())).size if engine.graphs else len(requests)
+    sizes = [g.size for g in engine.graphs.values() if g.size >= len(requests)]
+    h2d = 16 * (min(sizes) if sizes else len(requests))
     return sec / steps, h2d, 4 * len(requests)
 
 
@@ -172,7 +173,9 @@ def main():
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=QWEN25_7B["num_hidden_layers"])
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
+    ap.add_argument("--skip-prefill", action="store_true", help="for profiling the decode step alone")
+    ap.add_argument("--skip-e2e", action="store_true", help="for profiling the decode step alone")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -208,7 +211,7 @@ def main():
         ms, clocks, launches = decode_device(engine, requests, args.steps, args.warmup, torch, Entry, LAST_SAMPLED)
         results[b] = {"ms": ms, "clocks": clocks, "launches": launches}
         release(engine, requests)
-        if b == args.batch:
+        if b == args.batch and not args.skip_e2e:
             fill_cache(engine, requests, start_len, torch)
             sec, h2d, d2h = decode_e2e(engine, requests, args.steps, args.warmup, torch)
             results[b]["e2e"] = {"value": b / sec, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -220,7 +223,7 @@ def main():
     g = torch.Generator().manual_seed(7)
     prompt = torch.randint(0, mc.vocab_size, (T,), generator=g).tolist()
     times = []
-    for i in range(3):
+    for i in range(0 if args.skip_prefill else 3):
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
@@ -229,7 +232,7 @@ def main():
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e))
         engine.finish("p")
-    pre_ms = min(times[1:])
+    pre_ms = min(times[1:]) if times else float("nan")
     L, E, I, V = len(engine.model.spec.order), mc.hidden_size, mc.intermediate_size, mc.vocab_size
     H, K, d = mc.num_attention_heads, mc.num_key_value_heads, mc.head_dim
     gemm_params = L * (E * (H + 2 * K) * d + H * d * E + 3 * E * I)
