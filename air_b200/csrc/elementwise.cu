@@ -50,6 +50,43 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     }
 }
 
+// The same with four elements per access, for E % 4 == 0.  `parts` tensors of delta's shape,
+// one after the other, are summed in order (the partial sums of a split product).
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restrict__ delta, int parts,
+                                        size_t part_stride, const TW* __restrict__ w, TO* __restrict__ out,
+                                        const int* __restrict__ rows, int E, float eps) {
+    __shared__ float scratch[32];
+    extern __shared__ float xrow[];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+        float x[4];
+        load4(h + src + i, x);
+        for (int p = 0; p < parts; ++p) {
+            float d[4];
+            load4(delta + p * part_stride + src + i, d);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] += d[j];
+        }
+        store4(xrow + i, x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
+    }
+    const float total = block_sum(ss, scratch);
+    const float scale = rsqrtf(total / (float)E + eps);
+    for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+        float x[4], wv[4], y[4];
+        load4(xrow + i, x);
+        load4(w + i, wv);
+        if (!rows && parts > 0) store4(h + src + i, x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[j] = x[j] * scale * wv[j];
+        store4(out + (size_t)r * E + i, y);
+    }
+}
+
 // ---------------------------------------------------------------- bias + rotary + cache write
 // qkv [T, (H + 2K) d] is the output of the fused projection.  For every token: add the
 // bias, rotate the heads of q and k with the table's cos/sin of the token's position
@@ -132,6 +169,76 @@ __global__ void qkv_rope_store_kernel(const TI* __restrict__ qkv, const TB* __re
     }
 }
 
+// The same for full rotation (rot == d) with four pairs per thread.  `parts` tensors of qkv's
+// shape are summed in order (the partial sums of a split product).
+template <typename TI, typename TB, typename TO>
+__global__ void qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts, size_t part_stride,
+                                           const TB* __restrict__ bias, const float* __restrict__ table,
+                                           const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                           const int* __restrict__ block_table, int max_blocks,
+                                           TO* __restrict__ q_out, TO* __restrict__ cache,
+                                           int H, int K, int d, int P, int write_kv, int* status) {
+    const int t = blockIdx.x;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    const int width = (H + 2 * K) * d, half = d / 2;
+    const TI* in = qkv + (size_t)t * width;
+    TO* kdst = nullptr;
+    TO* vdst = nullptr;
+    if (write_kv) {
+        const int page = block_table[(size_t)slot * max_blocks + pos / P];
+        if (page < 0) {
+            if (threadIdx.x == 0 && status) atomicExch(status, 2);
+        } else {
+            kdst = cache + ((size_t)page * 2 * K * P + (size_t)(pos % P)) * d;
+            vdst = kdst + (size_t)K * P * d;
+        }
+    }
+    const int per_head = half / 4;
+    const int heads = write_kv ? H + 2 * K : H;
+    const float* cs = table + (size_t)pos * d;
+    for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
+        const int head = idx / per_head, j = (idx % per_head) * 4;
+        const int base = head * d;
+        float a[4], b[4];
+        load4(in + base + j, a);
+        load4(in + base + half + j, b);
+        for (int p = 1; p < parts; ++p) {
+            float x[4], y[4];
+            load4(in + p * part_stride + base + j, x);
+            load4(in + p * part_stride + base + half + j, y);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
+        }
+        if (bias) {
+            float x[4], y[4];
+            load4(bias + base + j, x);
+            load4(bias + base + half + j, y);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
+        }
+        const bool is_v = head >= H + K;
+        if (!is_v) {
+            float c[4], sn[4];
+            load4(cs + j, c);
+            load4(cs + half + j, sn);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float ra = a[e] * c[e] - b[e] * sn[e], rb = a[e] * sn[e] + b[e] * c[e];
+                a[e] = ra;
+                b[e] = rb;
+            }
+        }
+        TO* dst;
+        if (head < H) dst = q_out + ((size_t)t * H + head) * d;
+        else if (!kdst) continue;
+        else dst = (is_v ? vdst + (size_t)(head - H - K) * P * d : kdst + (size_t)(head - H) * P * d);
+        store4(dst + j, a);
+        store4(dst + half + j, b);
+    }
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 // in [T, 2I]: gate in the first I columns, up in the second.  out [T, I].
 template <typename TI, typename TO>
@@ -143,6 +250,22 @@ __global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out,
         const float g = to_float(in[t * 2 * I + i]);
         const float u = to_float(in[t * 2 * I + I + i]);
         out[idx] = from_float<TO>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+template <typename TI, typename TO>
+__global__ void silu_mul_vec4_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, size_t total4) {
+    const int I4 = I / 4;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I4;
+        const int i = (int)(idx % I4) * 4;
+        float g[4], u[4], y[4];
+        load4(in + t * 2 * I + i, g);
+        load4(in + t * 2 * I + I + i, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+        store4(out + t * I + i, y);
     }
 }
 
@@ -172,32 +295,52 @@ AIR_API int air_embedding(const void* table, int table_dtype, const int* ids, co
     return (int)cudaGetLastError();
 }
 
-AIR_API int air_add_rmsnorm(float* h, const void* delta, int delta_dtype, const void* w, int w_dtype,
-                            void* out, int out_dtype, const int* rows, int R, int E, float eps,
+// delta: `parts` tensors [rows of h, E] one after the other (parts = 0 or delta = null: none).
+AIR_API int air_add_rmsnorm(float* h, const void* delta, int delta_dtype, int parts, const void* w, int w_dtype,
+                            void* out, int out_dtype, const int* rows, int R, int E, long long h_rows, float eps,
                             cudaStream_t stream) {
     if (R <= 0) return 0;
     const size_t smem = (size_t)E * sizeof(float);
-    if (smem > 200 * 1024) return AIR_ERR_BAD_ARGUMENT;
+    if (smem > 200 * 1024 || parts < 0) return AIR_ERR_BAD_ARGUMENT;
+    if (!delta) parts = 0;
     const int threads = E >= 2048 ? 512 : 256;
     AIR_DISPATCH(delta_dtype, TD, AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
-        auto kernel = add_rmsnorm_kernel<TD, TW, TO>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<R, threads, smem, stream>>>(h, (const TD*)delta, (const TW*)w, (TO*)out, rows, E, eps);
+        if (E % 4 == 0) {
+            auto kernel = add_rmsnorm_vec4_kernel<TD, TW, TO>;
+            if (smem > 48 * 1024)
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<R, threads, smem, stream>>>(h, (const TD*)delta, parts, (size_t)h_rows * E, (const TW*)w,
+                                                 (TO*)out, rows, E, eps);
+        } else {
+            if (parts > 1) return AIR_ERR_BAD_ARGUMENT;
+            auto kernel = add_rmsnorm_kernel<TD, TW, TO>;
+            if (smem > 48 * 1024)
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<R, threads, smem, stream>>>(h, parts ? (const TD*)delta : nullptr, (const TW*)w, (TO*)out, rows,
+                                                 E, eps);
+        }
     })));
     return (int)cudaGetLastError();
 }
 
-AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, const void* bias, int bias_dtype,
+AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, int parts, const void* bias, int bias_dtype,
                                const float* table, int rot, const int* positions, const int* token_seq,
                                const int* block_table, int max_blocks, void* q_out, void* cache,
                                int out_dtype, int T, int H, int K, int d, int P, int write_kv,
                                int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (rot < 0 || rot > d || (rot & 1)) return AIR_ERR_BAD_ARGUMENT;
+    if (rot < 0 || rot > d || (rot & 1) || parts < 1) return AIR_ERR_BAD_ARGUMENT;
     AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(bias_dtype, TB, AIR_DISPATCH(out_dtype, TO, {
-        qkv_rope_store_kernel<TI, TB, TO><<<T, 256, 0, stream>>>(
-            (const TI*)qkv, (const TB*)bias, table, rot, positions, token_seq, block_table, max_blocks,
-            (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
+        if (rot == d && d % 8 == 0) {
+            qkv_rope_store_vec4_kernel<TI, TB, TO><<<T, 256, 0, stream>>>(
+                (const TI*)qkv, parts, (size_t)T * (H + 2 * K) * d, (const TB*)bias, table, positions, token_seq,
+                block_table, max_blocks, (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
+        } else {
+            if (parts != 1) return AIR_ERR_BAD_ARGUMENT;
+            qkv_rope_store_kernel<TI, TB, TO><<<T, 256, 0, stream>>>(
+                (const TI*)qkv, (const TB*)bias, table, rot, positions, token_seq, block_table, max_blocks,
+                (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
+        }
     })));
     return (int)cudaGetLastError();
 }
@@ -206,9 +349,15 @@ AIR_API int air_silu_mul(const void* in, int in_dtype, void* out, int out_dtype,
                          cudaStream_t stream) {
     const size_t total = (size_t)T * I;
     if (total == 0) return 0;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(out_dtype, TO, {
-        silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, total);
+        if (I % 4 == 0) {
+            const size_t n = total / 4;
+            const int blocks = (int)((n + 255) / 256 < 148 * 32 ? (n + 255) / 256 : 148 * 32);
+            silu_mul_vec4_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, n);
+        } else {
+            const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+            silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, total);
+        }
     }));
     return (int)cudaGetLastError();
 }

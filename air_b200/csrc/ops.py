@@ -17,9 +17,9 @@ c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_vo
 
 _SIGNATURES = {
     "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
-    "air_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
-                        c_float, c_void_p],
-    "air_qkv_rope_store": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+    "air_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                        c_longlong, c_float, c_void_p],
+    "air_qkv_rope_store": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "air_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "air_convert": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
@@ -105,16 +105,19 @@ def add_rmsnorm(h, delta, weight, eps, out, rows=None):
     With rows: out[r] = rmsnorm(h[rows[r]] + delta[rows[r]]) * weight, h unchanged."""
     E = h.shape[-1]
     _req(h, "h", (torch.float32,), (None, E))
+    parts = 0
     if delta is not None:
-        _req(delta, "delta", _FLOATS, tuple(h.shape))
+        # [rows, E], or [parts, rows, E]: partial sums that are added in order
+        parts = 1 if delta.dim() == 2 else delta.shape[0]
+        _req(delta, "delta", _FLOATS, tuple(h.shape) if delta.dim() == 2 else (parts,) + tuple(h.shape))
     _req(weight, "weight", _FLOATS, (E,))
     R = h.shape[0] if rows is None else rows.shape[0]
     if rows is not None:
         _req(rows, "rows", _I32)
     _req(out, "out", _FLOATS, (R, E))
-    _check(_get("air_add_rmsnorm")(h.data_ptr(), _ptr(delta), _DT[delta.dtype] if delta is not None else 0,
+    _check(_get("air_add_rmsnorm")(h.data_ptr(), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, parts,
                                    weight.data_ptr(), _DT[weight.dtype], out.data_ptr(), _DT[out.dtype],
-                                   _ptr(rows), R, E, float(eps), _stream()), "add_rmsnorm")
+                                   _ptr(rows), R, E, h.shape[0], float(eps), _stream()), "add_rmsnorm")
     return out
 
 
@@ -122,9 +125,10 @@ def qkv_rope_store(qkv, bias, table, positions, token_seq, block_table, q_out, c
                    head_dim, write_kv=True, status=None):
     """Adds the bias, rotates q and k by the table's cos/sin of each token's position, writes
     q to q_out [T, H, d] and k, v into the pages (cache [page, 2, K, P, d])."""
-    T = qkv.shape[0]
+    T = qkv.shape[-2]
     width = (heads + 2 * kv_heads) * head_dim
-    _req(qkv, "qkv", _FLOATS, (T, width))
+    parts = 1 if qkv.dim() == 2 else qkv.shape[0]     # [T, width], or [parts, T, width] partial sums
+    _req(qkv, "qkv", _FLOATS, (T, width) if qkv.dim() == 2 else (parts, T, width))
     if bias is not None:
         _req(bias, "bias", _FLOATS, (width,))
     rot = 0
@@ -139,7 +143,7 @@ def qkv_rope_store(qkv, bias, table, positions, token_seq, block_table, q_out, c
     _req(q_out, "q_out", _FLOATS, (T, heads, head_dim))
     _req(cache, "cache", (q_out.dtype,), (None, 2, kv_heads, None, head_dim))
     _check(_get("air_qkv_rope_store")(
-        qkv.data_ptr(), _DT[qkv.dtype], _ptr(bias), _DT[bias.dtype] if bias is not None else 0,
+        qkv.data_ptr(), _DT[qkv.dtype], parts, _ptr(bias), _DT[bias.dtype] if bias is not None else 0,
         _ptr(table), rot, positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], q_out.data_ptr(), cache.data_ptr(), _DT[q_out.dtype], T, heads, kv_heads,
         head_dim, cache.shape[3], 1 if write_kv else 0, _ptr(status), _stream()), "qkv_rope_store")

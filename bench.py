@@ -176,6 +176,7 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling the decode step alone")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling the decode step alone")
+    ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -204,6 +205,9 @@ def main():
     kv_bytes_per_token = 2 * mc.num_key_value_heads * mc.head_dim * 2 * len(engine.model.spec.order)
 
     results = {}
+    if args.skip_decode:
+        batches, args.skip_e2e = [], True
+        results[args.batch] = {"ms": float("nan"), "clocks": None, "launches": 0}
     for b in batches:
         requests = [f"r{i}" for i in range(b)]
         start_len = args.context - (args.steps + args.warmup + 2)
