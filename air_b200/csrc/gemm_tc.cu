@@ -1,0 +1,406 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T with
+// float32 accumulation in tensor memory, for prefill (M in the thousands) and decode (M of a
+// few tokens) alike, with the epilogues that the decoder wants fused in.
+//
+// One persistent block per SM, 192 threads:
+//   warp 0   one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//            of a 128 x 64 tile of A and a BN x 64 tile of W per stage into a ring of stages;
+//   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M = 128, N = BN, K = 16, four per
+//            stage) into one of two accumulators and commits the stage's "empty" barrier;
+//   warps 2-5  read a finished accumulator with tcgen05.ld (each thread one row = one token, 32
+//            columns at a time) and write the result, while the next tile is being multiplied.
+// A thread of the epilogue holds a whole row of the tile, so what the decoder does per token and
+// output column pair is done in registers:
+//   EPI_F32 / EPI_BF16  store C
+//   EPI_SILU            W holds, per tile, BN/2 rows of the gate projection followed by the BN/2 rows
+//                       of the up projection for the same outputs: out = silu(gate) * up as bfloat16
+//   EPI_PARTIAL         the k range is split over `splits` blocks; each writes its partial sums to
+//                       C[split][M][N] (float32), which the consumer (norm or rotary kernel) adds up
+//                       in a fixed order.  This keeps all 148 SMs streaming weights when M is small.
+// Rows of A beyond M are not loaded (the box of A is only as tall as needed); the accumulator rows
+// they would feed hold garbage that is never read.  Rows of W beyond N are zero-filled by TMA.
+//
+// Every wait on an mbarrier is bounded: when a wait gives up, the block sets a flag, every role
+// leaves its loop, outstanding copies are given time to land, tensor memory is freed and *status
+// is set to 4.  The host reads *status with the step's other error codes.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace air {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
+
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for the phase with the given parity; gives up after TC_SPIN_LIMIT tries or when another
+// role has given up.  Returns false on giving up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct TcArgs {
+    void* out;          // EPI_F32/PARTIAL: float [splits][M][N]; EPI_BF16: bf16 [M][N]; EPI_SILU: bf16 [M][N/2]
+    int M, N, K;
+    int a_rows;         // height of A's TMA box: 16, 32, 64 or 128
+    int splits;         // parts of the k range (1 unless EPI_PARTIAL)
+    int* status;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const TcArgs args) {
+    constexpr int STAGE_A = TC_BM * TC_BK * 2;                 // 16 KB (only a_rows rows are filled)
+    constexpr int STAGE_W = BN * TC_BK * 2;
+    constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; a power of two
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sa = smem;
+    uint8_t* sw = smem + STAGES * STAGE_A;
+    uint64_t* bars = (uint64_t*)(sw + STAGES * STAGE_W);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* acc_full = bars + 2 * STAGES;
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (args.M + TC_BM - 1) / TC_BM;
+    const int n_tiles = (args.N + BN - 1) / BN;
+    const int k_tiles = (args.K + TC_BK - 1) / TC_BK;
+    const int k_per = (k_tiles + args.splits - 1) / args.splits;
+    const int total = m_tiles * n_tiles * args.splits;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ------------------------------------------------ producer
+            const uint32_t bytes = (uint32_t)(args.a_rows * TC_BK * 2 + STAGE_W);
+            uint32_t stage = 0, phase = 0;
+            for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x) {
+                const int split = tile % args.splits;
+                const int mn = tile / args.splits;
+                const int m0 = (mn % m_tiles) * TC_BM, n0 = (mn / m_tiles) * BN;
+                const int k_begin = split * k_per, k_end = min(k_tiles, k_begin + k_per);
+                for (int kt = k_begin; kt < k_end; ++kt) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) break;
+                    mbar_expect_tx(&full[stage], bytes);
+                    tma_load_2d(sa + stage * STAGE_A, &map_a, kt * TC_BK, m0, &full[stage]);
+                    tma_load_2d(sw + stage * STAGE_W, &map_w, kt * TC_BK, n0, &full[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ------------------------------------------------ MMA issuer
+            constexpr uint32_t idesc = umma_idesc(BN);
+            uint32_t stage = 0, phase = 0, it = 0;
+            for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++it) {
+                const int split = tile % args.splits;
+                const int k_begin = split * k_per, k_end = min(k_tiles, k_begin + k_per);
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kt = k_begin; kt < k_end; ++kt) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = umma_desc(smem_u32(sa + stage * STAGE_A));
+                    const uint64_t dw = umma_desc(smem_u32(sw + stage * STAGE_W));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16(d, da + 2 * k, dw + 2 * k, idesc, (kt > k_begin || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ---------------------------------------------------- epilogue: warps 2..5
+        const int quarter = warp & 3;                     // the 32 lanes of tensor memory this warp may read
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++it) {
+            const int split = tile % args.splits;
+            const int mn = tile / args.splits;
+            const int m0 = (mn % m_tiles) * TC_BM, n0 = (mn / m_tiles) * BN;
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
+            const bool warp_has_rows = m0 + quarter * 32 < args.M;
+            if (warp_has_rows) {
+                const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+                if (EPI == EPI_SILU) {
+                    __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)row * (args.N / 2) + n0 / 2;
+#pragma unroll 1
+                    for (int c = 0; c < BN / 2; c += 32) {
+                        uint32_t gate[32], up[32];
+                        tmem_ld32(taddr + c, gate);
+                        tmem_ld32(taddr + BN / 2 + c, up);
+                        if (row < args.M) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                if (n0 / 2 + c + j >= args.N / 2) break;
+                                float y[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const float g = __uint_as_float(gate[j + e]), u = __uint_as_float(up[j + e]);
+                                    y[e] = g / (1.f + expf(-g)) * u;
+                                }
+                                store4(out + c + j, *(const float(*)[4])&y[0]);
+                                store4(out + c + j + 4, *(const float(*)[4])&y[4]);
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(taddr + c, v);
+                        if (row < args.M) {
+                            if (EPI == EPI_BF16) {
+                                __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)row * args.N + n0 + c;
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) {
+                                    if (n0 + c + j >= args.N) break;
+                                    const float y[4] = {__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                        __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])};
+                                    store4(out + j, y);
+                                }
+                            } else {
+                                float* out = (float*)args.out + ((size_t)split * args.M + row) * args.N + n0 + c;
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) {
+                                    if (n0 + c + j >= args.N) break;
+                                    *reinterpret_cast<float4*>(out + j) =
+                                        make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                    __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+    }
+
+    // ---------------------------------------------------------- leaving
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        // copies that were issued may still be on their way: give them time before the block ends
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+        if (threadIdx.x == 0 && args.status) atomicExch(args.status, 4);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A tensor map of a row-major bf16 matrix [rows, cols] with boxes of box_rows x 64 and 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return AIR_ERR_BAD_ARGUMENT;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 200000 + (int)r;
+}
+
+template <int BN, int EPI>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcArgs& args, int blocks, cudaStream_t stream) {
+    constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    // always more than half of an SM's shared memory, so that two blocks never share an SM (and its
+    // 512 columns of tensor memory)
+    const size_t smem = 1024 + (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 256;
+    const size_t request = smem < 120 * 1024 ? 120 * 1024 : smem;
+    auto kernel = gemm_tc_kernel<BN, EPI>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)request);
+    if (e != cudaSuccess) return (int)e;
+    kernel<<<blocks, TC_THREADS, request, stream>>>(ma, mw, args);
+    return (int)cudaGetLastError();
+}
+
+template <int BN>
+static int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const TcArgs& args, int blocks,
+                        cudaStream_t stream) {
+    switch (epi) {
+        case EPI_F32: return launch_tc<BN, EPI_F32>(ma, mw, args, blocks, stream);
+        case EPI_BF16: return launch_tc<BN, EPI_BF16>(ma, mw, args, blocks, stream);
+        case EPI_SILU: return launch_tc<BN, EPI_SILU>(ma, mw, args, blocks, stream);
+        case EPI_PARTIAL: return launch_tc<BN, EPI_PARTIAL>(ma, mw, args, blocks, stream);
+        default: return AIR_ERR_BAD_ARGUMENT;
+    }
+}
+
+}  // namespace air
+
+// a [M, K] bf16, w [N, K] bf16 (for epi 2: gate and up rows interleaved in blocks of bn / 2), K % 8 == 0.
+// out as TcArgs.out.  bn: 32, 64, 128 or 256.  max_blocks: the number of SMs to use (0: all).
+AIR_API int air_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, int bn, int epi, int splits,
+                        int max_blocks, int* status, cudaStream_t stream) {
+    using namespace air;
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || splits < 1 || (splits > 1 && epi != EPI_PARTIAL) || ((uintptr_t)a & 15) ||
+        ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
+        return AIR_ERR_BAD_ARGUMENT;
+    if (epi == EPI_SILU && (bn < 64 || N % bn || (N / 2) % 8)) return AIR_ERR_BAD_ARGUMENT;
+    if (epi != EPI_SILU && N % 4) return AIR_ERR_BAD_ARGUMENT;
+    const int k_tiles = (K + TC_BK - 1) / TC_BK;
+    if (splits > k_tiles) return AIR_ERR_BAD_ARGUMENT;
+    const int a_rows = M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16));
+    CUtensorMap ma, mw;
+    int rc = make_map(&ma, a, M, K, a_rows);
+    if (rc) return rc;
+    rc = make_map(&mw, w, N, K, bn);
+    if (rc) return rc;
+    TcArgs args{out, M, N, K, a_rows, splits, status};
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (max_blocks > 0 && max_blocks < sms) sms = max_blocks;
+    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn) * splits;
+    const int blocks = (int)(tiles < sms ? tiles : sms);
+    switch (bn) {
+        case 32: return dispatch_epi<32>(epi, ma, mw, args, blocks, stream);
+        case 64: return dispatch_epi<64>(epi, ma, mw, args, blocks, stream);
+        case 128: return dispatch_epi<128>(epi, ma, mw, args, blocks, stream);
+        case 256: return dispatch_epi<256>(epi, ma, mw, args, blocks, stream);
+        default: return AIR_ERR_BAD_ARGUMENT;
+    }
+}

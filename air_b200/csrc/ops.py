@@ -31,6 +31,7 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "air_prefill_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_float, c_void_p],
+    "air_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -285,4 +286,39 @@ def prefill_attention(q, cache, block_table, tiles, out, window, scale):
     _check(_get("air_prefill_attention")(
         q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(),
         tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _stream()), "prefill_attention")
+    return out
+
+
+EPI_F32, EPI_BF16, EPI_SILU, EPI_PARTIAL = 0, 1, 2, 3
+
+
+def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0):
+    """bfloat16 product a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (see gemm_tc.cu).
+    epi EPI_F32: out float32 [M,N]; EPI_BF16: out bfloat16 [M,N]; EPI_SILU: w holds gate and up rows
+    interleaved in blocks of bn/2, out bfloat16 [M,N/2] = silu(gate)*up; EPI_PARTIAL: out float32
+    [splits,M,N] partial sums over parts of k."""
+    M, K = a.shape
+    N = w.shape[0]
+    _req(a, "a", (torch.bfloat16,))
+    _req(w, "w", (torch.bfloat16,), (N, K))
+    if K % 8:
+        raise KernelError(f"gemm_tc: K = {K} must be a multiple of 8 (TMA rows are multiples of 16 bytes)")
+    if bn not in (32, 64, 128, 256):
+        raise KernelError(f"gemm_tc: tile width {bn}")
+    if epi == EPI_F32:
+        _req(out, "out", (torch.float32,), (M, N))
+    elif epi == EPI_BF16:
+        _req(out, "out", (torch.bfloat16,), (M, N))
+    elif epi == EPI_SILU:
+        _req(out, "out", (torch.bfloat16,), (M, N // 2))
+        if bn < 64 or N % bn:
+            raise KernelError(f"gemm_tc: silu epilogue needs N = {N} to be a multiple of the tile width {bn} >= 64")
+    elif epi == EPI_PARTIAL:
+        _req(out, "out", (torch.float32,), (splits, M, N))
+    else:
+        raise KernelError(f"gemm_tc: epilogue {epi}")
+    if epi != EPI_SILU and N % 4:
+        raise KernelError(f"gemm_tc: N = {N} must be a multiple of 4")
+    _check(_get("air_gemm_tc")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits, max_blocks,
+                               _ptr(status), _stream()), "gemm_tc")
     return out

@@ -1,0 +1,92 @@
+"""The tcgen05 matrix product against a float64 product of the same bfloat16 inputs: every
+tile width, every epilogue, sizes with tails in M, N and K, one token to thousands."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def ops():
+    from air_b200.csrc import ops as o
+    return o
+
+
+def inputs(M, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = (torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    return a.cuda(), w.cuda(), a.double() @ w.double().T
+
+
+def close(got, want, K):
+    tol = 2e-6 * K ** 0.5 + 1e-6
+    return float((got.double().cpu() - want).abs().max()) <= tol * float(want.abs().max()) + 1e-5
+
+
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+@pytest.mark.parametrize("M,N,K", [(8, 64, 64), (1, 256, 128), (16, 512, 192), (37, 388, 352), (128, 256, 256),
+                                   (200, 1000, 1000), (64, 4608, 3584)])
+def test_float32_output(bn, M, N, K):
+    o = ops()
+    a, w, want = inputs(M, N, K, M + N)
+    out = torch.full((M, N), 9.0, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o.gemm_tc(a, w, out, bn, o.EPI_F32, status=status)
+    assert status.item() == 0
+    assert close(out, want, K)
+
+
+@pytest.mark.parametrize("bn,splits", [(32, 2), (64, 3), (128, 5), (64, 1)])
+def test_partial_sums_over_k(bn, splits):
+    o = ops()
+    M, N, K = 8, 3584, 18944 // 8
+    a, w, want = inputs(M, N, K, splits)
+    out = torch.zeros(splits, M, N, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o.gemm_tc(a, w, out, bn, o.EPI_PARTIAL, splits=splits, status=status)
+    assert status.item() == 0
+    assert close(out.sum(0), want, K)
+    if splits > 1:
+        assert float(out[1].abs().max()) > 0
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("M", [3, 130])
+def test_silu_epilogue_with_interleaved_gate_and_up(bn, M):
+    o = ops()
+    I, K = 3 * bn, 320
+    g = torch.Generator().manual_seed(bn + M)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16)
+    up = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16)
+    half = bn // 2
+    w = torch.cat([torch.cat([gate[i:i + half], up[i:i + half]]) for i in range(0, I, half)])
+    out = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+    o.gemm_tc(a.cuda(), w.cuda(), out, bn, o.EPI_SILU)
+    gd, ud = a.double() @ gate.double().T, a.double() @ up.double().T
+    want = gd / (1 + torch.exp(-gd)) * ud
+    assert float((out.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+
+
+def test_bfloat16_output_and_many_tiles():
+    o = ops()
+    M, N, K = 2048, 1536, 512
+    a, w, want = inputs(M, N, K, 5)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o.gemm_tc(a, w, out, 256, o.EPI_BF16, status=status)
+    assert status.item() == 0
+    assert float((out.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+    # fewer blocks than tiles: every block walks several tiles, both accumulators in turn
+    out2 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    o.gemm_tc(a, w, out2, 128, o.EPI_BF16, status=status, max_blocks=7)
+    assert status.item() == 0 and torch.equal(out2, out)
+
+
+def test_refusals():
+    o = ops()
+    a = torch.zeros(4, 36, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, 36, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(o.KernelError, match="multiple of 8"):
+        o.gemm_tc(a, w, torch.zeros(4, 8, device="cuda"), 32, o.EPI_F32)
