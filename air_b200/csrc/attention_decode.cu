@@ -6,7 +6,7 @@
 // straight from global memory into registers with 16-byte loads and feeds them to the tensor
 // cores (mma.sync m16n8k16, bf16 in, fp32 out) with the query heads of the group as the M
 // dimension, so the G query heads that share a kv head share every byte that is loaded.
-// Nothing is staged in shared memory and nothing is transposed by ldmatrix:
+// Nothing is transposed by ldmatrix and no tile is shared between threads through shared memory:
 //
 //  * S = Q K^T: the k index of the MMA is the head dimension.  A dot product does not care in
 //    which order its terms are added, so the k slots of an MMA are mapped to the head dimension
@@ -32,6 +32,12 @@
 namespace air {
 
 constexpr int DEC_WARPS = 4;
+constexpr int DEC_STAGES = 3;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
+                 : "memory");
+}
 
 template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -80,25 +86,53 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
+    // Keys and values are fetched two tiles ahead with cp.async into a ring in shared memory in which
+    // every thread has places of its own: it copies exactly the 16-byte pieces that it will later
+    // load into its own registers, so the ring needs no barrier; it only extends the registers.
+    constexpr int PIECES = 2 * KC + 4 * NG;
+    uint4* ring = reinterpret_cast<uint4*>(smem);
     const size_t page_stride = (size_t)2 * K * P * D;
     const size_t v_offset = (size_t)K * P * D;
-    for (int tile = begin + warp; tile < end; tile += DEC_WARPS) {
-        const int kbase = tile * 16;
-        const int page = bt[kbase / P];
-        const __nv_bfloat16* kp = cache + (size_t)page * page_stride + ((size_t)kvh * P + (kbase % P)) * D;
-        const __nv_bfloat16* vp = kp + v_offset;
+    const int my_tiles = begin + warp < end ? (end - begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
+    auto issue = [&](int i) {
+        if (i < my_tiles) {
+            const int kbase = (begin + warp + i * DEC_WARPS) * 16;
+            const int page = bt[kbase / P];
+            const __nv_bfloat16* kp = cache + (size_t)page * page_stride + ((size_t)kvh * P + (kbase % P)) * D;
+            const __nv_bfloat16* vp = kp + v_offset;
+            uint4* dst = ring + (size_t)(i % DEC_STAGES) * PIECES * (DEC_WARPS * 32) + threadIdx.x;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < KC; ++c)
+                    cp_async16(dst + (j * KC + c) * (DEC_WARPS * 32), kp + (size_t)(8 * j + g) * D + 32 * c + 8 * tq);
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4)
+#pragma unroll
+                for (int n = 0; n < NG; ++n)
+                    cp_async16(dst + (2 * KC + i4 * NG + n) * (DEC_WARPS * 32),
+                               vp + (size_t)(2 * tq + (i4 & 1) + 8 * (i4 >> 1)) * D + 64 * n + 8 * g);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i) issue(i);
+    for (int it = 0; it < my_tiles; ++it) {
+        const int kbase = (begin + warp + it * DEC_WARPS) * 16;
+        issue(it + DEC_STAGES - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(DEC_STAGES - 1) : "memory");
+        const uint4* src = ring + (size_t)(it % DEC_STAGES) * PIECES * (DEC_WARPS * 32) + threadIdx.x;
         // K: rows g and 8 + g of the tile; V: rows 2tq, 2tq+1, 8+2tq, 9+2tq
         uint4 kf[2][KC];
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int c = 0; c < KC; ++c) kf[j][c] = ldg16(kp + (size_t)(8 * j + g) * D + 32 * c + 8 * tq);
+            for (int c = 0; c < KC; ++c) kf[j][c] = src[(j * KC + c) * (DEC_WARPS * 32)];
         uint4 vf[4][NG];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int n = 0; n < NG; ++n)
-                vf[i][n] = ldg16(vp + (size_t)(2 * tq + (i & 1) + 8 * (i >> 1)) * D + 64 * n + 8 * g);
+            for (int n = 0; n < NG; ++n) vf[i][n] = src[(2 * KC + i * NG + n) * (DEC_WARPS * 32)];
 
         float s[2][4];
 #pragma unroll
@@ -172,7 +206,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
-    // merge the warps.  Output tile n, accumulator e holds column (n/8)*64 + 8*(2tq + (e&1)) + n%8.
+    // merge the warps (the ring is done with: its memory is used again).
+    // Output tile n, accumulator e holds column (n/8)*64 + 8*(2tq + (e&1)) + n%8.
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
     if (tq == 0) {
         sm_m[warp * 16 + g] = m0;
         sm_m[warp * 16 + g + 8] = m1;
@@ -245,7 +282,9 @@ int launch_decode(const void* q, const void* cache, const int* block_table, int 
                   int window, float scale, int splits, cudaStream_t stream) {
     const int G = H / K;
     const int head_blocks = (G + 15) / 16;
-    const size_t smem = (size_t)(DEC_WARPS * 16 * D + 2 * DEC_WARPS * 16) * sizeof(float);
+    const size_t merge = (size_t)(DEC_WARPS * 16 * D + 2 * DEC_WARPS * 16) * sizeof(float);
+    const size_t ring = (size_t)DEC_STAGES * (2 * (D / 32) + 4 * (D / 64)) * DEC_WARPS * 32 * 16;
+    const size_t smem = merge > ring ? merge : ring;
     auto kernel = decode_attention_kernel<D>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -240,29 +240,33 @@ __global__ void qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// in [T, 2I]: gate in the first I columns, up in the second.  out [T, I].
+// in [T, 2I]: blocks of `block` gate columns and `block` up columns in turn (block = I: all gate
+// columns, then all up columns).  out [T, I].
 template <typename TI, typename TO>
-__global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, int block, size_t total) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
         const int i = (int)(idx % I);
-        const float g = to_float(in[t * 2 * I + i]);
-        const float u = to_float(in[t * 2 * I + I + i]);
+        const size_t at = t * 2 * I + (size_t)(i / block) * 2 * block + i % block;
+        const float g = to_float(in[at]);
+        const float u = to_float(in[at + block]);
         out[idx] = from_float<TO>(g / (1.f + expf(-g)) * u);
     }
 }
 
 template <typename TI, typename TO>
-__global__ void silu_mul_vec4_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, size_t total4) {
+__global__ void silu_mul_vec4_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, int block,
+                                     size_t total4) {
     const int I4 = I / 4;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I4;
         const int i = (int)(idx % I4) * 4;
+        const size_t at = t * 2 * I + (size_t)(i / block) * 2 * block + i % block;
         float g[4], u[4], y[4];
-        load4(in + t * 2 * I + i, g);
-        load4(in + t * 2 * I + I + i, u);
+        load4(in + at, g);
+        load4(in + at + block, u);
 #pragma unroll
         for (int e = 0; e < 4; ++e) y[e] = g[e] / (1.f + expf(-g[e])) * u[e];
         store4(out + t * I + i, y);
@@ -345,18 +349,19 @@ AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, int parts, const v
     return (int)cudaGetLastError();
 }
 
-AIR_API int air_silu_mul(const void* in, int in_dtype, void* out, int out_dtype, int T, int I,
+AIR_API int air_silu_mul(const void* in, int in_dtype, void* out, int out_dtype, int T, int I, int block,
                          cudaStream_t stream) {
     const size_t total = (size_t)T * I;
     if (total == 0) return 0;
+    if (block <= 0 || I % block) return AIR_ERR_BAD_ARGUMENT;
     AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(out_dtype, TO, {
-        if (I % 4 == 0) {
+        if (I % 4 == 0 && block % 4 == 0) {
             const size_t n = total / 4;
             const int blocks = (int)((n + 255) / 256 < 148 * 32 ? (n + 255) / 256 : 148 * 32);
-            silu_mul_vec4_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, n);
+            silu_mul_vec4_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, block, n);
         } else {
             const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-            silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, total);
+            silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, block, total);
         }
     }));
     return (int)cudaGetLastError();

@@ -21,7 +21,7 @@ _SIGNATURES = {
                         c_longlong, c_float, c_void_p],
     "air_qkv_rope_store": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "air_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "air_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "air_convert": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
     "air_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -151,13 +151,17 @@ def qkv_rope_store(qkv, bias, table, positions, token_seq, block_table, q_out, c
     return q_out
 
 
-def silu_mul(gate_up, out):
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def silu_mul(gate_up, out, block=None):
+    """out[t, i] = silu(gate[t, i]) * up[t, i], where gate_up [T, 2I] holds blocks of `block` gate
+    columns and `block` up columns in turn (default: all gate columns, then all up columns)."""
     T, I = out.shape
+    block = I if block is None else block
+    if block <= 0 or I % block:
+        raise KernelError(f"silu_mul: block {block} does not divide {I}")
     _req(gate_up, "gate_up", _FLOATS, (T, 2 * I))
     _req(out, "out", _FLOATS)
     _check(_get("air_silu_mul")(gate_up.data_ptr(), _DT[gate_up.dtype], out.data_ptr(), _DT[out.dtype], T, I,
-                                _stream()), "silu_mul")
+                                block, _stream()), "silu_mul")
     return out
 
 
@@ -231,9 +235,10 @@ DECODE_HEAD_DIMS = (64, 128, 256)
 
 
 def decode_splits(tokens: int, heads: int, kv_heads: int) -> int:
-    """How many blocks share the keys of one (token, kv head): enough to fill the GPU."""
+    """How many blocks share the keys of one (token, kv head): as many as fit on the GPU at once
+    (two blocks per SM), so that no block waits for a second round."""
     per_split = tokens * kv_heads * (-(-(heads // kv_heads) // 16))
-    return max(1, min(32, -(-444 // per_split)))
+    return max(1, min(32, 296 // per_split))
 
 
 def decode_attention(q, cache, block_table, token_seq, positions, out, window, scale, splits=None, scratch=None):

@@ -106,7 +106,8 @@ class Engine:
         max_blocks = -(-model.spec.max_positions // config.page_tokens)
         self.cache = CacheManager(model.cache_needs(), config.page_tokens, num_pages, config.max_requests,
                                   dtype=self.rt.dtype, device=self.rt.device, max_blocks=max_blocks)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        self.status = self.rt.status if self.rt.status is not None else \
+            torch.zeros(1, dtype=torch.int32, device=self.rt.device)
         self.last_token = torch.zeros(config.max_requests, dtype=torch.int32, device=self.rt.device)
         self.last_context: Optional[StepContext] = None
         self.steps = 0
@@ -123,7 +124,8 @@ class Engine:
         arch = registry.architecture(model_config.architecture)
         model = Model(arch.build_spec(model_config))
         device = _device(config.device)
-        rt = Runtime(device=device, dtype=parse_dtype(config.dtype), page_tokens=config.page_tokens)
+        rt = Runtime(device=device, dtype=parse_dtype(config.dtype), page_tokens=config.page_tokens,
+                     status=torch.zeros(1, dtype=torch.int32, device=device))
         tensors = load_tensors(folder, model.tensor_specs(), rt.dtype, device)
         model.load(tensors, rt)
         return cls(model, config, model_config)
@@ -137,7 +139,8 @@ class Engine:
         arch = registry.architecture(model_config.architecture)
         model = Model(arch.build_spec(model_config))
         device = _device(config.device)
-        rt = Runtime(device=device, dtype=parse_dtype(config.dtype), page_tokens=config.page_tokens)
+        rt = Runtime(device=device, dtype=parse_dtype(config.dtype), page_tokens=config.page_tokens,
+                     status=torch.zeros(1, dtype=torch.int32, device=device))
         model.load(random_tensors(model.tensor_specs(), seed, rt.dtype, device=device), rt)
         return cls(model, config, model_config)
 
@@ -254,7 +257,8 @@ class Engine:
             self.status.zero_()
             raise StepError({1: "a token outside the vocabulary reached the embedding kernel",
                              2: "a token was to be written to a page that its request does not hold",
-                             3: "non-finite logits"}.get(code, f"device status {code}"))
+                             3: "non-finite logits",
+                             4: "a wait inside the matrix-product kernel ran out"}.get(code, f"device status {code}"))
 
 
 def _device(name) -> torch.device:

@@ -47,7 +47,7 @@ class Model:
             b.load(tensors, rt)
         self.final_norm.load(tensors, rt)
         out = self.embedding if self.spec.output_name is None else tensors[self.spec.output_name]
-        self.output = Linear(out)
+        self.output = Linear(out, rt.status)
 
     def cache_needs(self):
         """Per run of the order list: the needs of the layer's mixer, or nothing for a run that
@@ -93,4 +93,4 @@ class Model:
         if R == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         y = self.final_norm.forward(h, pending, rows=ctx.logit_rows)
-        return self.output(y, torch.float32)
+        return self.output.full(y) if self.output.small(y) else self.output(y, torch.float32)

@@ -66,9 +66,9 @@ class Attention(Mixer):
         ws = [tensors[p + f"{n}_proj.weight"] for n in "qkv"]
         if len({w.dtype for w in ws}) != 1:
             raise ValueError(f"{p}: q, k and v projections are stored in different precisions")
-        self.qkv = Linear(torch.cat(ws, dim=0).contiguous())
+        self.qkv = Linear(torch.cat(ws, dim=0).contiguous(), rt.status)
         self.q_only = self.qkv.rows(0, self.heads * self.head_dim)
-        self.o = Linear(tensors[p + "o_proj.weight"])
+        self.o = Linear(tensors[p + "o_proj.weight"], rt.status)
         self.bias = None
         if any((p + f"{n}_proj.bias") in tensors for n in "qkv"):
             parts = []
@@ -86,7 +86,7 @@ class Attention(Mixer):
         H, K, d = self.heads, self.kv_heads, self.head_dim
         rt = self.rt
         if owns_cache:
-            qkv = self.qkv(x, torch.float32)
+            qkv = self.qkv.partial(x) if self.qkv.small(x) else self.qkv(x, torch.float32)
         else:
             # this run reads another run's keys and values: only q is computed
             qkv = torch.zeros((T, (H + 2 * K) * d), dtype=torch.float32, device=x.device)
@@ -102,4 +102,5 @@ class Attention(Mixer):
             ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale)
         else:
             ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
-        return self.o(out.view(T, H * d), torch.float32)
+        out = out.view(T, H * d)
+        return self.o.partial(out) if self.o.small(out) else self.o(out, torch.float32)

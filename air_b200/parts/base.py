@@ -10,8 +10,9 @@ other parts of its block are.
   PositionEncoding  table() -> float32 [positions, rotary width] cos|sin, consumed by mixers
   Mixer             cache_needs() -> what it keeps per request (pages of keys and values, a
                     state of fixed size, both, or nothing);
-                    forward(x, ctx, cache, owns_cache) -> [T, hidden]
-  FeedForward       forward(x, ctx) -> [T, hidden]
+                    forward(x, ctx, cache, owns_cache) -> [T, hidden], or float32 [parts, T, hidden]
+                    partial sums that the next norm adds up in order
+  FeedForward       forward(x, ctx) -> [T, hidden] (or partial sums, as above)
   Block             forward(h, pending, ctx, cache, owns_cache) -> (h, pending): the arrangement
                     of two norms, a mixer and a feed-forward around the residual stream
 """
@@ -33,6 +34,7 @@ class Runtime:
     device: torch.device
     dtype: torch.dtype
     page_tokens: int = 64
+    status: Optional[torch.Tensor] = None    # [1] int32 on the device: kernels report impossible states here
 
     @property
     def is_fp32(self) -> bool:

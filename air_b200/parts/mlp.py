@@ -16,7 +16,11 @@ class SwiGLU(FeedForward):
     (AIR: src/reference/reference_executor.cpp:33-35, 394-408).
     params: hidden, intermediate.  Tensors: <prefix>{gate,up}_proj.weight [intermediate, hidden],
     <prefix>down_proj.weight [hidden, intermediate].  gate and up become one matrix at load, so
-    the input is read once; the activation kernel reads both halves of its output."""
+    the input is read once: blocks of gate rows and of up rows for the same outputs in turn (the
+    block is the largest of 128, 64, 32 that divides `intermediate`, else all of it), so that a
+    tile of the product holds both factors of its outputs and the tcgen05 kernel can apply the
+    activation in its epilogue; with many rows the library's product is followed by the
+    activation kernel, which reads the same arrangement."""
 
     def tensor_specs(self):
         e, i, p = self.spec["hidden"], self.spec["intermediate"], self.prefix
@@ -29,12 +33,24 @@ class SwiGLU(FeedForward):
         g, u = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
         if g.dtype != u.dtype:
             raise ValueError(f"{p}: gate and up projections are stored in different precisions")
-        self.gate_up = Linear(torch.cat([g, u], dim=0).contiguous())
-        self.down = Linear(tensors[p + "down_proj.weight"])
-        self.intermediate = self.spec["intermediate"]
+        inter = self.intermediate = self.spec["intermediate"]
+        block = next((b for b in (128, 64, 32) if inter % b == 0), inter)
+        if g.dtype != torch.bfloat16:
+            block = inter
+        self.block = block
+        if block == inter:
+            w = torch.cat([g, u], dim=0)
+        else:
+            w = torch.stack([g.view(inter // block, block, -1), u.view(inter // block, block, -1)], dim=1)
+            w = w.reshape(2 * inter, -1)
+        self.gate_up = Linear(w.contiguous(), rt.status, gate_up_block=block if block != inter else 0)
+        self.down = Linear(tensors[p + "down_proj.weight"], rt.status)
 
     def forward(self, x, ctx):
-        gu = self.gate_up(x, torch.float32 if self.rt.is_fp32 else self.rt.dtype)
-        act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
-        ops.silu_mul(gu, act)
-        return self.down(act, torch.float32)
+        if self.gate_up.gate_up_block and self.gate_up.small(x):
+            act = self.gate_up.silu_mul(x)
+        else:
+            gu = self.gate_up(x, torch.float32 if self.rt.is_fp32 else self.rt.dtype)
+            act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
+            ops.silu_mul(gu, act, block=self.block)
+        return self.down.partial(act) if self.down.small(act) else self.down(act, torch.float32)

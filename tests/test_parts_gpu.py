@@ -65,6 +65,7 @@ def test_swiglu_part(dtype):
     part.load({k: v.cuda() for k, v in t.items()}, runtime(dtype))
     x = torch.randn(11, 80, generator=torch.Generator().manual_seed(1)).to(DT[dtype])
     out = part.forward(x.cuda(), None)
+    out = out.sum(0) if out.dim() == 3 else out
     n = as_np(t)
     want = plain.swiglu(x.float().numpy(), n["f.gate_proj.weight"], n["f.up_proj.weight"], n["f.down_proj.weight"])
     assert out.dtype == torch.float32
@@ -92,7 +93,8 @@ def test_attention_part_over_portions(heads, kv, d, window, dtype):
     outs, i = [], 0
     for n in (20, 2, 23):
         ctx, entries = context_for(cache, [("r", [0] * n, [])])
-        outs.append(part.forward(x[i:i + n].cuda(), ctx, cache.views(0), True).cpu())
+        y = part.forward(x[i:i + n].cuda(), ctx, cache.views(0), True)
+        outs.append((y.sum(0) if y.dim() == 3 else y).cpu())        # partial sums over parts of k are allowed
         cache.commit("r", n)
         i += n
     out = torch.cat(outs).numpy()
