@@ -54,6 +54,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     float* sm_m = smem + DEC_WARPS * 16 * D;     // [warps][16]
     float* sm_l = sm_m + DEC_WARPS * 16;         // [warps][16]
 
+    pdl_enter(TR_ATT_DECODE);
     const int t = blockIdx.z;
     const int slot = token_seq[t];
     if (slot < 0) return;
@@ -256,6 +257,7 @@ template <int D>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       const int* __restrict__ token_seq, __nv_bfloat16* __restrict__ out, int H,
                                       int splits) {
+    pdl_enter(TR_ATT_COMBINE);
     const int t = blockIdx.y, h = blockIdx.x;
     if (token_seq[t] < 0) return;
     const size_t base = ((size_t)t * H + h) * splits;
@@ -291,14 +293,13 @@ int launch_decode(const void* q, const void* cache, const int* block_table, int 
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(splits, K * head_blocks, T);
-    kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, max_blocks, token_seq, positions,
-        (__nv_bfloat16*)out, part_o, part_ml, H, K, P, window, scale * 1.4426950408889634f);
-    if (splits > 1) {
-        decode_combine_kernel<D><<<dim3(H, T), D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, token_seq,
-                                                                              (__nv_bfloat16*)out, H, splits);
-    }
-    return (int)cudaGetLastError();
+    int rc = launch(kernel, grid, DEC_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
+                    block_table, max_blocks, token_seq, positions, (__nv_bfloat16*)out, part_o, part_ml, H, K, P,
+                    window, scale * 1.4426950408889634f);
+    if (rc == 0 && splits > 1)
+        rc = launch(decode_combine_kernel<D>, dim3(H, T), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
+                    (const float*)part_ml, token_seq, (__nv_bfloat16*)out, H, splits);
+    return rc;
 }
 
 }  // namespace air
@@ -398,3 +399,5 @@ AIR_API int air_decode_attention_static(const void* q, const void* cache, const 
     return air_decode_attention(q, cache, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
                                 K, D, P, window, scale, splits, stream);
 }
+
+AIR_API int air_trace_set_attention_decode(unsigned long long* buffer) { return air::set_trace_here(buffer); }

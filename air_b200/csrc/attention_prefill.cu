@@ -27,6 +27,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          __nv_bfloat16* __restrict__ out, int H, int K, int P, int window, float scale_log2) {
     constexpr int KC = D / 32, NT = D / 8, NG = D / 64;
     extern __shared__ float smem[];   // [warps][16][D + 4]: the output tile of each warp
+    pdl_enter(TR_ATT_PREFILL);
     const int G = H / K;
     const int head_blocks = (G + PRE_MAX_WARPS - 1) / PRE_MAX_WARPS;
     const int kvh = blockIdx.y / head_blocks, hb = blockIdx.y % head_blocks;
@@ -183,10 +184,8 @@ int launch_prefill(const void* q, const void* cache, const int* block_table, int
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(n_tiles, K * head_blocks);
-    kernel<<<grid, warps * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table,
-                                                max_blocks, tiles, (__nv_bfloat16*)out, H, K, P, window,
-                                                scale * 1.4426950408889634f);
-    return (int)cudaGetLastError();
+    return launch(kernel, grid, warps * 32, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
+                  block_table, max_blocks, tiles, (__nv_bfloat16*)out, H, K, P, window, scale * 1.4426950408889634f);
 }
 
 }  // namespace air
@@ -210,3 +209,5 @@ AIR_API int air_prefill_attention(const void* q, const void* cache, const int* b
             return AIR_ERR_BAD_ARGUMENT;
     }
 }
+
+AIR_API int air_trace_set_attention_prefill(unsigned long long* buffer) { return air::set_trace_here(buffer); }

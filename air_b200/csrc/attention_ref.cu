@@ -28,6 +28,7 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
     __shared__ float sq[ATT_MAX_D];
     __shared__ float sm[ATT_WARPS], sl[ATT_WARPS];
     __shared__ float sacc[ATT_WARPS][ATT_MAX_D];
+    pdl_enter(TR_ATT_REF);
     const int t = blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (token_seq[t] < 0) return;  // padding
@@ -114,9 +115,11 @@ AIR_API int air_paged_attention_ref(const void* q, const void* cache, int dtype,
     if (d <= 0 || d > air::ATT_MAX_D || H <= 0 || K <= 0 || H > 65535) return AIR_ERR_BAD_ARGUMENT;
     dim3 grid(T, H);
     AIR_DISPATCH(dtype, TT, {
-        air::paged_attention_ref_kernel<TT><<<grid, air::ATT_WARPS * 32, 0, stream>>>(
-            (const TT*)q, (const TT*)cache, block_table, max_blocks, token_seq, positions, (TT*)out, H, K, d, P,
-            window, scale);
+        return air::launch(air::paged_attention_ref_kernel<TT>, grid, air::ATT_WARPS * 32, 0, stream, (const TT*)q,
+                           (const TT*)cache, block_table, max_blocks, token_seq, positions, (TT*)out, H, K, d, P,
+                           window, scale);
     });
-    return (int)cudaGetLastError();
+    return 0;
 }
+
+AIR_API int air_trace_set_attention_ref(unsigned long long* buffer) { return air::set_trace_here(buffer); }

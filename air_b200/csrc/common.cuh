@@ -17,6 +17,63 @@
 
 namespace air {
 
+// Programmatic dependent launch.  Every kernel of this library is launched with the attribute
+// that lets it become resident while its predecessor in the stream is still running, and every
+// kernel begins with pdl_enter(): it first tells the scheduler that its own successor may be
+// launched, then waits until its predecessor has completed and its writes are visible.  Whatever
+// a kernel does before pdl_enter() (setting up barriers, fetching weights, which no kernel
+// writes) overlaps the predecessor's tail.  Without the attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Optional timeline: when a trace buffer is set (air_set_trace), block 0 of every kernel appends
+// (kernel id, %globaltimer) once it has passed the wait on its predecessor.  Slot 0 counts entries.
+static __device__ unsigned long long* g_trace = nullptr;
+__device__ __forceinline__ void trace_point(int id) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long* t = g_trace;
+        if (t) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            const unsigned long long i = atomicAdd(t, 1ull);
+            if (i < 16384) {
+                t[1 + 2 * i] = (unsigned long long)id;
+                t[2 + 2 * i] = now;
+            }
+        }
+    }
+}
+enum TraceId { TR_EMBED = 1, TR_NORM, TR_ROPE, TR_SILU, TR_CONVERT, TR_TABLE, TR_ATT_REF, TR_ATT_DECODE, TR_ATT_COMBINE,
+               TR_ATT_PREFILL, TR_GEMM_F32, TR_GEMM_TC, TR_SAMPLE };
+
+__device__ __forceinline__ void pdl_enter(int id = 0) {
+    pdl_trigger();
+    pdl_wait();
+    trace_point(id);
+}
+
+// Every translation unit has its own copy of g_trace; this sets the copy of the unit that calls it.
+inline int set_trace_here(unsigned long long* buffer) {
+    return (int)cudaMemcpyToSymbol(g_trace, &buffer, sizeof(buffer));
+}
+
+// 1: launches carry the programmatic-serialization attribute (set by air_set_pdl).
+int& pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

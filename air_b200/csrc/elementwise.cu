@@ -13,6 +13,7 @@ template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  const int* __restrict__ last_token, float* __restrict__ out, int E, int V,
                                  int* status) {
+    pdl_enter(TR_EMBED);
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 && last_token) id = last_token[-id - 1];
@@ -32,6 +33,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
                                    const int* __restrict__ rows, int E, float eps) {
     __shared__ float scratch[32];
     extern __shared__ float xrow[];
+    pdl_enter(TR_NORM);
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * E;
     float ss = 0.f;
@@ -58,6 +60,7 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restr
                                         const int* __restrict__ rows, int E, float eps) {
     __shared__ float scratch[32];
     extern __shared__ float xrow[];
+    pdl_enter(TR_NORM);
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * E;
     float ss = 0.f;
@@ -101,6 +104,7 @@ __global__ void qkv_rope_store_kernel(const TI* __restrict__ qkv, const TB* __re
                                       const int* __restrict__ block_table, int max_blocks,
                                       TO* __restrict__ q_out, TO* __restrict__ cache,
                                       int H, int K, int d, int P, int write_kv, int* status) {
+    pdl_enter(TR_ROPE);
     const int t = blockIdx.x;
     const int slot = token_seq[t];
     if (slot < 0) return;  // padding
@@ -178,6 +182,7 @@ __global__ void qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts
                                            const int* __restrict__ block_table, int max_blocks,
                                            TO* __restrict__ q_out, TO* __restrict__ cache,
                                            int H, int K, int d, int P, int write_kv, int* status) {
+    pdl_enter(TR_ROPE);
     const int t = blockIdx.x;
     const int slot = token_seq[t];
     if (slot < 0) return;
@@ -244,6 +249,7 @@ __global__ void qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts
 // columns, then all up columns).  out [T, I].
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, int block, size_t total) {
+    pdl_enter(TR_SILU);
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
@@ -258,6 +264,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out,
 template <typename TI, typename TO>
 __global__ void silu_mul_vec4_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, int block,
                                      size_t total4) {
+    pdl_enter(TR_SILU);
     const int I4 = I / 4;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -276,6 +283,7 @@ __global__ void silu_mul_vec4_kernel(const TI* __restrict__ in, TO* __restrict__
 // ---------------------------------------------------------------- block table updates
 // updates [n, 3]: (slot, block, page) -> table[slot, block] = page
 __global__ void table_update_kernel(int* __restrict__ table, const int* __restrict__ updates, int n, int W) {
+    pdl_enter(TR_TABLE);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) table[(size_t)updates[3 * i] * W + updates[3 * i + 1]] = updates[3 * i + 2];
 }
@@ -283,6 +291,7 @@ __global__ void table_update_kernel(int* __restrict__ table, const int* __restri
 // ---------------------------------------------------------------- conversions
 template <typename TI, typename TO>
 __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    pdl_enter(TR_CONVERT);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = from_float<TO>(to_float(in[i]));
 }
@@ -294,9 +303,9 @@ using namespace air;
 AIR_API int air_embedding(const void* table, int table_dtype, const int* ids, const int* last_token, float* out,
                           int T, int E, int V, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
-    AIR_DISPATCH(table_dtype, TT, embedding_kernel<TT><<<T, 256, 0, stream>>>((const TT*)table, ids, last_token,
-                                                                               out, E, V, status));
-    return (int)cudaGetLastError();
+    AIR_DISPATCH(table_dtype, TT, return launch(embedding_kernel<TT>, T, 256, 0, stream, (const TT*)table, ids,
+                                                last_token, out, E, V, status));
+    return 0;
 }
 
 // delta: `parts` tensors [rows of h, E] one after the other (parts = 0 or delta = null: none).
@@ -313,15 +322,15 @@ AIR_API int air_add_rmsnorm(float* h, const void* delta, int delta_dtype, int pa
             auto kernel = add_rmsnorm_vec4_kernel<TD, TW, TO>;
             if (smem > 48 * 1024)
                 cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<R, threads, smem, stream>>>(h, (const TD*)delta, parts, (size_t)h_rows * E, (const TW*)w,
-                                                 (TO*)out, rows, E, eps);
+            return launch(kernel, R, threads, smem, stream, h, (const TD*)delta, parts, (size_t)h_rows * E,
+                          (const TW*)w, (TO*)out, rows, E, eps);
         } else {
             if (parts > 1) return AIR_ERR_BAD_ARGUMENT;
             auto kernel = add_rmsnorm_kernel<TD, TW, TO>;
             if (smem > 48 * 1024)
                 cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<R, threads, smem, stream>>>(h, parts ? (const TD*)delta : nullptr, (const TW*)w, (TO*)out, rows,
-                                                 E, eps);
+            return launch(kernel, R, threads, smem, stream, h, parts ? (const TD*)delta : nullptr, (const TW*)w,
+                          (TO*)out, rows, E, eps);
         }
     })));
     return (int)cudaGetLastError();
@@ -336,14 +345,14 @@ AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, int parts, const v
     if (rot < 0 || rot > d || (rot & 1) || parts < 1) return AIR_ERR_BAD_ARGUMENT;
     AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(bias_dtype, TB, AIR_DISPATCH(out_dtype, TO, {
         if (rot == d && d % 8 == 0) {
-            qkv_rope_store_vec4_kernel<TI, TB, TO><<<T, 256, 0, stream>>>(
-                (const TI*)qkv, parts, (size_t)T * (H + 2 * K) * d, (const TB*)bias, table, positions, token_seq,
-                block_table, max_blocks, (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
+            return launch(qkv_rope_store_vec4_kernel<TI, TB, TO>, T, 256, 0, stream, (const TI*)qkv, parts,
+                          (size_t)T * (H + 2 * K) * d, (const TB*)bias, table, positions, token_seq, block_table,
+                          max_blocks, (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
         } else {
             if (parts != 1) return AIR_ERR_BAD_ARGUMENT;
-            qkv_rope_store_kernel<TI, TB, TO><<<T, 256, 0, stream>>>(
-                (const TI*)qkv, (const TB*)bias, table, rot, positions, token_seq, block_table, max_blocks,
-                (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
+            return launch(qkv_rope_store_kernel<TI, TB, TO>, T, 256, 0, stream, (const TI*)qkv, (const TB*)bias,
+                          table, rot, positions, token_seq, block_table, max_blocks, (TO*)q_out, (TO*)cache, H, K, d,
+                          P, write_kv, status);
         }
     })));
     return (int)cudaGetLastError();
@@ -358,10 +367,10 @@ AIR_API int air_silu_mul(const void* in, int in_dtype, void* out, int out_dtype,
         if (I % 4 == 0 && block % 4 == 0) {
             const size_t n = total / 4;
             const int blocks = (int)((n + 255) / 256 < 148 * 32 ? (n + 255) / 256 : 148 * 32);
-            silu_mul_vec4_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, block, n);
+            return launch(silu_mul_vec4_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, (TO*)out, I, block, n);
         } else {
             const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-            silu_mul_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, I, block, total);
+            return launch(silu_mul_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, (TO*)out, I, block, total);
         }
     }));
     return (int)cudaGetLastError();
@@ -372,13 +381,25 @@ AIR_API int air_convert(const void* in, int in_dtype, void* out, int out_dtype, 
     if (n <= 0) return 0;
     const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(out_dtype, TO, {
-        convert_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, (size_t)n);
+        return launch(convert_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, (TO*)out, (size_t)n);
     }));
     return (int)cudaGetLastError();
 }
 
 AIR_API int air_table_update(int* table, const int* updates, int n, int W, cudaStream_t stream) {
     if (n <= 0) return 0;
-    table_update_kernel<<<(n + 127) / 128, 128, 0, stream>>>(table, updates, n, W);
-    return (int)cudaGetLastError();
+    return launch(table_update_kernel, (n + 127) / 128, 128, 0, stream, table, updates, n, W);
 }
+
+// 1: kernels are launched so that they may overlap the tail of their predecessor (the default);
+// 0: plain stream order.
+AIR_API void air_set_pdl(int on) { air::pdl_enabled() = on ? 1 : 0; }
+
+namespace air {
+int& pdl_enabled() {
+    static int enabled = 1;
+    return enabled;
+}
+}  // namespace air
+
+AIR_API int air_trace_set_elementwise(unsigned long long* buffer) { return air::set_trace_here(buffer); }

@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
                                                        int M, int N, int K) {
     __shared__ float sa[GK][GB + 4];
     __shared__ float sw[GK][GB + 4];
+    pdl_enter(TR_GEMM_F32);
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;          // 16 x 16 threads, 4 x 4 outputs each
     const int m0 = blockIdx.y * GB, n0 = blockIdx.x * GB;
@@ -64,6 +65,7 @@ AIR_API int air_gemm_f32(const float* A, const float* W, const float* bias, floa
     if (K <= 0) return AIR_ERR_BAD_ARGUMENT;
     dim3 grid((N + air::GB - 1) / air::GB, (M + air::GB - 1) / air::GB);
     if (grid.y > 65535) return AIR_ERR_BAD_ARGUMENT;
-    air::gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K);
-    return (int)cudaGetLastError();
+    return air::launch(air::gemm_f32_kernel, grid, 256, 0, stream, A, W, bias, C, M, N, K);
 }
+
+AIR_API int air_trace_set_gemm_f32(unsigned long long* buffer) { return air::set_trace_here(buffer); }

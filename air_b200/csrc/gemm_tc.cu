@@ -4,7 +4,7 @@
 //
 // One persistent block per SM, 192 threads:
 //   warp 0   one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
-//            of a 128 x 64 tile of A and a BN x 64 tile of W per stage into a ring of stages;
+//            of an up to 128 x 64 tile of A and a BN x 64 tile of W per stage into a ring of stages;
 //   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M = 128, N = BN, K = 16, four per
 //            stage) into one of two accumulators and commits the stage's "empty" barrier;
 //   warps 2-5  read a finished accumulator with tcgen05.ld (each thread one row = one token, 32
@@ -69,6 +69,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// Asks for a tile to be brought into L2 (no shared memory, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -123,18 +129,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 struct TcArgs {
     void* out;          // EPI_F32/PARTIAL: float [splits][M][N]; EPI_BF16: bf16 [M][N]; EPI_SILU: bf16 [M][N/2]
     int M, N, K;
-    int a_rows;         // height of A's TMA box: 16, 32, 64 or 128
+    int a_rows;         // height of A's TMA box: 16, 64 or 128
     int splits;         // parts of the k range (1 unless EPI_PARTIAL)
+    int prefetch;       // further k-tiles of W that a block asks into L2 before its predecessor has ended
     int* status;
 };
 
-template <int BN, int EPI>
+// Stages of the ring for a tile width and a height of A's box: what fits in 196 KB, at most 24.
+__host__ __device__ constexpr int tc_stages(int bn, int ar) {
+    return 196 * 1024 / ((ar + bn) * TC_BK * 2) > 24 ? 24 : 196 * 1024 / ((ar + bn) * TC_BK * 2);
+}
+
+// BN: tile width.  AR: rows of A that are loaded (16, 64 or 128): with few tokens a stage is small,
+// so the ring is deep and most of a block's share of W is under way before the predecessor ends.
+// The MMA always reads 128 rows from the stage's address; what lies beyond AR rows is other tiles'
+// data, feeding accumulator rows that are never read.
+template <int BN, int EPI, int AR>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const TcArgs args) {
-    constexpr int STAGE_A = TC_BM * TC_BK * 2;                 // 16 KB (only a_rows rows are filled)
+    constexpr int STAGE_A = AR * TC_BK * 2;
     constexpr int STAGE_W = BN * TC_BK * 2;
-    constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    constexpr int STAGES = tc_stages(BN, AR);
+    static_assert(STAGES >= 2 && STAGES * STAGE_W >= TC_BM * TC_BK * 2, "the MMA's 128-row read must stay inside");
     constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; a power of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -148,6 +165,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (args.M + TC_BM - 1) / TC_BM;
     const int n_tiles = (args.N + BN - 1) / BN;
@@ -181,14 +199,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             // ------------------------------------------------ producer
-            const uint32_t bytes = (uint32_t)(args.a_rows * TC_BK * 2 + STAGE_W);
+            const uint32_t bytes = (uint32_t)(STAGE_A + STAGE_W);
             uint32_t stage = 0, phase = 0;
+            bool first = true;
+            trace_point(TR_GEMM_TC + 100);   // when this block became resident
             for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x) {
                 const int split = tile % args.splits;
                 const int mn = tile / args.splits;
                 const int m0 = (mn % m_tiles) * TC_BM, n0 = (mn / m_tiles) * BN;
                 const int k_begin = split * k_per, k_end = min(k_tiles, k_begin + k_per);
-                for (int kt = k_begin; kt < k_end; ++kt) {
+                int kt = k_begin;
+                if (first) {
+                    // The weights are written by no kernel: the first stages' tiles of W are fetched
+                    // while the predecessor in the stream may still be running; the tiles of A (its
+                    // output) follow once it has completed.
+                    first = false;
+                    const int pre = min(STAGES, k_end - k_begin);
+                    for (int i = 0; i < pre; ++i) {
+                        mbar_expect_tx(&full[i], bytes);
+                        tma_load_2d(sw + i * STAGE_W, &map_w, (k_begin + i) * TC_BK, n0, &full[i]);
+                    }
+                    const int ahead = min(pre + args.prefetch, k_end - k_begin);
+                    for (int i = pre; i < ahead; ++i) tma_prefetch_l2(&map_w, (k_begin + i) * TC_BK, n0);
+                    pdl_wait();
+                    trace_point(TR_GEMM_TC);
+                    for (int i = 0; i < pre; ++i)
+                        tma_load_2d(sa + i * STAGE_A, &map_a, (k_begin + i) * TC_BK, m0, &full[i]);
+                    kt = k_begin + pre;
+                    if (pre == STAGES) phase = 1; else stage = pre;
+                }
+                for (; kt < k_end; ++kt) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) break;
                     mbar_expect_tx(&full[stage], bytes);
                     tma_load_2d(sa + stage * STAGE_A, &map_a, kt * TC_BK, m0, &full[stage]);
@@ -225,6 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         // ---------------------------------------------------- epilogue: warps 2..5
+        pdl_wait();   // nothing is written before the predecessor has completed
         const int quarter = warp & 3;                     // the 32 lanes of tensor memory this warp may read
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++it) {
@@ -342,29 +383,40 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return r == CUDA_SUCCESS ? 0 : 200000 + (int)r;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int AR>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcArgs& args, int blocks, cudaStream_t stream) {
-    constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    constexpr int STAGES = tc_stages(BN, AR);
     // always more than half of an SM's shared memory, so that two blocks never share an SM (and its
     // 512 columns of tensor memory)
-    const size_t smem = 1024 + (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 256;
+    const size_t smem = 1024 + (size_t)STAGES * (AR + BN) * TC_BK * 2 + 16 * STAGES + 256;
     const size_t request = smem < 120 * 1024 ? 120 * 1024 : smem;
-    auto kernel = gemm_tc_kernel<BN, EPI>;
+    auto kernel = gemm_tc_kernel<BN, EPI, AR>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)request);
     if (e != cudaSuccess) return (int)e;
-    kernel<<<blocks, TC_THREADS, request, stream>>>(ma, mw, args);
-    return (int)cudaGetLastError();
+    return launch(kernel, blocks, TC_THREADS, request, stream, ma, mw, args);
 }
 
-template <int BN>
+template <int BN, int AR>
 static int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const TcArgs& args, int blocks,
                         cudaStream_t stream) {
     switch (epi) {
-        case EPI_F32: return launch_tc<BN, EPI_F32>(ma, mw, args, blocks, stream);
-        case EPI_BF16: return launch_tc<BN, EPI_BF16>(ma, mw, args, blocks, stream);
-        case EPI_SILU: return launch_tc<BN, EPI_SILU>(ma, mw, args, blocks, stream);
-        case EPI_PARTIAL: return launch_tc<BN, EPI_PARTIAL>(ma, mw, args, blocks, stream);
+        case EPI_F32: return launch_tc<BN, EPI_F32, AR>(ma, mw, args, blocks, stream);
+        case EPI_BF16: return launch_tc<BN, EPI_BF16, AR>(ma, mw, args, blocks, stream);
+        case EPI_SILU:
+            if constexpr (BN >= 64) return launch_tc<BN, EPI_SILU, AR>(ma, mw, args, blocks, stream);
+            return AIR_ERR_BAD_ARGUMENT;
+        case EPI_PARTIAL: return launch_tc<BN, EPI_PARTIAL, AR>(ma, mw, args, blocks, stream);
         default: return AIR_ERR_BAD_ARGUMENT;
+    }
+}
+
+template <int BN>
+static int dispatch_rows(int a_rows, int epi, const CUtensorMap& ma, const CUtensorMap& mw, const TcArgs& args,
+                         int blocks, cudaStream_t stream) {
+    switch (a_rows) {
+        case 16: return dispatch_epi<BN, 16>(epi, ma, mw, args, blocks, stream);
+        case 64: return dispatch_epi<BN, 64>(epi, ma, mw, args, blocks, stream);
+        default: return dispatch_epi<BN, 128>(epi, ma, mw, args, blocks, stream);
     }
 }
 
@@ -383,24 +435,29 @@ AIR_API int air_gemm_tc(const void* a, const void* w, void* out, int M, int N, i
     if (epi != EPI_SILU && N % 4) return AIR_ERR_BAD_ARGUMENT;
     const int k_tiles = (K + TC_BK - 1) / TC_BK;
     if (splits > k_tiles) return AIR_ERR_BAD_ARGUMENT;
-    const int a_rows = M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16));
+    const int a_rows = M > 64 ? 128 : (M > 16 ? 64 : 16);
     CUtensorMap ma, mw;
     int rc = make_map(&ma, a, M, K, a_rows);
     if (rc) return rc;
     rc = make_map(&mw, w, N, K, bn);
     if (rc) return rc;
-    TcArgs args{out, M, N, K, a_rows, splits, status};
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (max_blocks > 0 && max_blocks < sms) sms = max_blocks;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn) * splits;
     const int blocks = (int)(tiles < sms ? tiles : sms);
+    // With few rows the product is a stream of weights: while the predecessor runs, each block asks
+    // its share of up to 40 MB of them into L2 (the L2 holds 126 MB).
+    const int prefetch = M <= 64 ? (int)((40ll << 20) / blocks / (bn * TC_BK * 2)) : 0;
+    TcArgs args{out, M, N, K, a_rows, splits, prefetch, status};
     switch (bn) {
-        case 32: return dispatch_epi<32>(epi, ma, mw, args, blocks, stream);
-        case 64: return dispatch_epi<64>(epi, ma, mw, args, blocks, stream);
-        case 128: return dispatch_epi<128>(epi, ma, mw, args, blocks, stream);
-        case 256: return dispatch_epi<256>(epi, ma, mw, args, blocks, stream);
+        case 32: return dispatch_rows<32>(a_rows, epi, ma, mw, args, blocks, stream);
+        case 64: return dispatch_rows<64>(a_rows, epi, ma, mw, args, blocks, stream);
+        case 128: return dispatch_rows<128>(a_rows, epi, ma, mw, args, blocks, stream);
+        case 256: return dispatch_rows<256>(a_rows, epi, ma, mw, args, blocks, stream);
         default: return AIR_ERR_BAD_ARGUMENT;
     }
 }
+
+AIR_API int air_trace_set_gemm_tc(unsigned long long* buffer) { return air::set_trace_here(buffer); }

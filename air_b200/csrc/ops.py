@@ -54,6 +54,33 @@ def _get(name):
     return f
 
 
+def set_pdl(on: bool) -> None:
+    """Whether kernels are launched so that they may overlap the tail of their predecessor."""
+    lib = build.library()
+    lib.air_set_pdl.argtypes = [c_int]
+    lib.air_set_pdl.restype = None
+    lib.air_set_pdl(1 if on else 0)
+
+
+TRACE_NAMES = {1: "embedding", 2: "add_rmsnorm", 3: "qkv_rope_store", 4: "silu_mul", 5: "convert", 6: "table_update",
+               7: "attention_ref", 8: "decode_attention", 9: "decode_combine", 10: "prefill_attention", 11: "gemm_f32",
+               12: "gemm_tc", 13: "sample"}
+
+
+def set_trace(buffer: Optional[torch.Tensor]) -> None:
+    """buffer: int64 CUDA tensor of 1 + 2 * 16384 elements (zeroed), or None to stop tracing.  While set,
+    block 0 of every kernel appends (kernel id, GPU nanosecond timer) after its wait on its predecessor;
+    element 0 counts the entries.  Differences of consecutive times are the kernels' spans in a graph."""
+    lib = build.library()
+    ptr = None if buffer is None else buffer.data_ptr()
+    for src in build.sources():
+        f = getattr(lib, "air_trace_set_" + src[:-3])
+        f.argtypes, f.restype = [c_void_p], c_int
+        rc = f(ptr)
+        if rc:
+            raise KernelError(f"set_trace: CUDA error {rc}")
+
+
 def _check(code: int, name: str):
     global launches
     launches += 1

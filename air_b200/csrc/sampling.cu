@@ -26,6 +26,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __shared__ float partial[SAMPLE_THREADS];
     __shared__ float s_max;
     __shared__ int s_arg;
+    pdl_enter(TR_SAMPLE);
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)r * V;
 
@@ -96,7 +97,8 @@ AIR_API int air_sample(const float* logits, const float* temperature, const floa
                        const int* slots, int* last_token, int R, int V, int* status, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return AIR_ERR_BAD_ARGUMENT;
-    air::sample_kernel<<<R, air::SAMPLE_THREADS, 0, stream>>>(logits, temperature, uniform, out, slots,
-                                                                    last_token, V, status);
-    return (int)cudaGetLastError();
+    return air::launch(air::sample_kernel, R, air::SAMPLE_THREADS, 0, stream, logits, temperature, uniform, out,
+                       slots, last_token, V, status);
 }
+
+AIR_API int air_trace_set_sampling(unsigned long long* buffer) { return air::set_trace_here(buffer); }
