@@ -327,6 +327,25 @@ AIR_API int air_decode_attention(const void* q, const void* cache, const int* bl
     }
 }
 
+// The merge of the splits alone (used by the kernels that produce the partial results elsewhere).
+AIR_API int air_decode_combine(const float* part_o, const float* part_ml, const int* token_seq, void* out, int T,
+                               int H, int D, int splits, cudaStream_t stream) {
+    using namespace air;
+    switch (D) {
+        case 64:
+            return launch(decode_combine_kernel<64>, dim3(H, T), 64, 0, stream, part_o, part_ml, token_seq,
+                          (__nv_bfloat16*)out, H, splits);
+        case 128:
+            return launch(decode_combine_kernel<128>, dim3(H, T), 128, 0, stream, part_o, part_ml, token_seq,
+                          (__nv_bfloat16*)out, H, splits);
+        case 256:
+            return launch(decode_combine_kernel<256>, dim3(H, T), 128, 0, stream, part_o, part_ml, token_seq,
+                          (__nv_bfloat16*)out, H, splits);
+        default:
+            return AIR_ERR_BAD_ARGUMENT;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // air_decode_attention_static: the same attention for callers that must not allocate.
 // Declared and described in no_alloc.h.

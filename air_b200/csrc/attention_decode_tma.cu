@@ -1,0 +1,341 @@
+// Decode attention over the paged cache for bfloat16, keys and values moved by the copy engine.
+//
+// The same split of the work as attention_decode.cu (one query token per request, the query heads
+// of a group as the M dimension of mma.sync m16n8k16, the token's keys split over `splits` blocks,
+// partial results merged by decode_combine), but the bytes take another road.  A producer warp
+// issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of 64-key tiles of K and V from the
+// pages into a ring of shared-memory stages; mbarriers tell the four consumer warps when a tile has
+// landed and the producer when a stage is free again.  Each consumer warp takes 16 of the tile's 64
+// keys and reads its MMA operands with ldmatrix (K as it lies, V transposed), which the swizzle makes
+// free of bank conflicts.  The copy engine asks memory for whole rows at a time, which a warp's
+// 16-byte loads do not, and the consumers issue no load instructions for the cache at all.
+//
+// The cache [page, 2, K, P, D] is addressed as a matrix of rows of D elements; a 64-key tile is
+// 64 / min(P, 64) boxes of min(P, 64) rows, each found through the block table.
+// Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 5.
+#include "common.cuh"
+#include "mma.cuh"
+#include "tma.cuh"
+
+namespace air {
+
+constexpr int DT_CONSUMERS = 4;
+constexpr int DT_THREADS = (DT_CONSUMERS + 1) * 32;
+constexpr int DT_TILE = 64;     // keys per stage
+constexpr int DT_STAGES = 3;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+// Address of the 16-byte chunk `chunk` (0..7) of row `row` in a [64][128 B] tile with 128-byte swizzle.
+__device__ __forceinline__ uint32_t swizzled(uint32_t tile, int row, int chunk) {
+    return tile + row * 128 + ((chunk ^ (row & 7)) << 4);
+}
+
+template <int D>
+__global__ void __launch_bounds__(DT_THREADS)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const __nv_bfloat16* __restrict__ q,
+                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
+                            const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
+                            float* __restrict__ part_o, float* __restrict__ part_ml, int H, int K, int P, int window,
+                            float scale_log2, int* status) {
+    constexpr int SUB = D / 64;                 // 64-column sub-tiles of a row
+    constexpr int SUB_BYTES = DT_TILE * 128;    // 8 KB
+    constexpr int STAGE_BYTES = 2 * SUB * SUB_BYTES;
+    constexpr int KS = D / 16;                  // k-steps of Q K^T
+    constexpr int NT = D / 8;                   // 8-column tiles of the output
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + DT_STAGES * STAGE_BYTES);
+    uint64_t* empty = full + DT_STAGES;
+    volatile int* abort_flag = (volatile int*)(empty + DT_STAGES);
+    float* sm_o = (float*)smem;                              // after the walk: [warps][16][D]
+    float* sm_m = sm_o + DT_CONSUMERS * 16 * D;              // [warps][16]
+    float* sm_l = sm_m + DT_CONSUMERS * 16;
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < DT_STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], DT_CONSUMERS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Where a tile is not filled by one copy (pages smaller than a tile, pages that a window has given
+    // back) the ring starts as zeros: rows that no copy fills then hold zeros or earlier keys, never
+    // bits that could be NaN.
+    if (P < DT_TILE || window > 0) {
+        for (int i = threadIdx.x; i < DT_STAGES * STAGE_BYTES / 16; i += DT_THREADS)
+            reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();
+    trace_point(TR_ATT_DECODE);
+
+    const int t = blockIdx.z;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int G = H / K;
+    const int head_blocks = (G + 15) / 16;
+    const int kvh = blockIdx.y / head_blocks, hb = blockIdx.y % head_blocks;
+    const int split = blockIdx.x, splits = gridDim.x;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* bt = block_table + (size_t)slot * max_blocks;
+    const int tile0 = lo / DT_TILE, tile1 = pos / DT_TILE + 1;
+    const int per = (tile1 - tile0 + splits - 1) / splits;
+    const int begin = tile0 + split * per, end = min(tile1, begin + per);
+    const int n_tiles = max(0, end - begin);
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int g = lane >> 2, tq = lane & 3;
+
+    if (warp == DT_CONSUMERS) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            const int box_rows = P < DT_TILE ? P : DT_TILE;
+            const int boxes = DT_TILE / box_rows;
+            for (int it = 0; it < n_tiles; ++it) {
+                const int stage = it % DT_STAGES;
+                if (it >= DT_STAGES && !mbar_wait(&empty[stage], ((it / DT_STAGES) - 1) & 1, abort_flag)) break;
+                const int kbase = (begin + it) * DT_TILE;
+                int valid = 0;
+                for (int b = 0; b < boxes; ++b) {
+                    const int first = kbase + b * box_rows;
+                    valid += (first <= pos && first + box_rows - 1 >= lo) ? 1 : 0;
+                }
+                mbar_expect_tx(&full[stage], (uint32_t)(valid * box_rows * 128 * SUB * 2));
+                uint8_t* dst = smem + stage * STAGE_BYTES;
+                for (int b = 0; b < boxes; ++b) {
+                    const int first = kbase + b * box_rows;
+                    if (!(first <= pos && first + box_rows - 1 >= lo)) continue;
+                    const int page = bt[first / P];
+                    const int row_k = ((page * 2) * K + kvh) * P + first % P;
+                    const int row_v = row_k + K * P;
+#pragma unroll
+                    for (int s = 0; s < SUB; ++s) {
+                        tma_load_2d(dst + s * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_k, &full[stage]);
+                        tma_load_2d(dst + (SUB + s) * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_v,
+                                    &full[stage]);
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ consumers: 16 keys of every tile each
+        const int r0 = hb * 16 + g, r1 = r0 + 8;
+        uint32_t qa[KS][4];
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk) {
+            const __nv_bfloat16* q0 = q + ((size_t)t * H + kvh * G + r0) * D + 16 * kk + 2 * tq;
+            const __nv_bfloat16* q1 = q + ((size_t)t * H + kvh * G + r1) * D + 16 * kk + 2 * tq;
+            qa[kk][0] = r0 < G ? __ldg(reinterpret_cast<const uint32_t*>(q0)) : 0u;
+            qa[kk][1] = r1 < G ? __ldg(reinterpret_cast<const uint32_t*>(q1)) : 0u;
+            qa[kk][2] = r0 < G ? __ldg(reinterpret_cast<const uint32_t*>(q0 + 8)) : 0u;
+            qa[kk][3] = r1 < G ? __ldg(reinterpret_cast<const uint32_t*>(q1 + 8)) : 0u;
+        }
+        const int mat = lane >> 3, mrow = lane & 7;   // ldmatrix: which 8x8 matrix this lane addresses, which row
+        for (int it = 0; it < n_tiles; ++it) {
+            const int stage = it % DT_STAGES;
+            if (!mbar_wait(&full[stage], (it / DT_STAGES) & 1, abort_flag)) break;
+            const int kbase = (begin + it) * DT_TILE + 16 * warp;     // this warp's 16 keys
+            if (kbase <= pos && kbase + 15 >= lo) {
+                const uint32_t kt = smem_u32(smem + stage * STAGE_BYTES);
+                const uint32_t vt = kt + SUB * SUB_BYTES;
+                float s[2][4] = {};
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk) {
+                    // matrices: (keys 0-7, d 16kk..+7), (keys 0-7, d 16kk+8..), (keys 8-15, same two)
+                    uint32_t b[4];
+                    ldmatrix_x4(b, swizzled(kt + (kk / 4) * SUB_BYTES, 16 * warp + (mat >> 1) * 8 + mrow,
+                                            2 * (kk % 4) + (mat & 1)));
+                    mma_bf16_16816(s[0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b[0], b[1]);
+                    mma_bf16_16816(s[1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b[2], b[3]);
+                }
+                float tm0 = -INFINITY, tm1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = kbase + 8 * j + 2 * tq + e;
+                        const bool ok = key >= lo && key <= pos;
+                        s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+                        s[j][2 + e] = ok ? s[j][2 + e] * scale_log2 : -INFINITY;
+                        tm0 = fmaxf(tm0, s[j][e]);
+                        tm1 = fmaxf(tm1, s[j][2 + e]);
+                    }
+                tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1));
+                tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
+                tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1));
+                tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
+                const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);   // finite: at least one key is visible
+                const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);
+                m0 = n0;
+                m1 = n1;
+                float p[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    p[j][0] = exp2f(s[j][0] - n0);
+                    p[j][1] = exp2f(s[j][1] - n0);
+                    p[j][2] = exp2f(s[j][2] - n1);
+                    p[j][3] = exp2f(s[j][3] - n1);
+                }
+                l0 = l0 * c0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
+                l1 = l1 * c1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+                const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa1 = pack_bf16(p[0][2], p[0][3]);
+                const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]), pa3 = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    o[n][0] *= c0;
+                    o[n][1] *= c0;
+                    o[n][2] *= c1;
+                    o[n][3] *= c1;
+                }
+#pragma unroll
+                for (int n = 0; n < NT; n += 2) {
+                    // matrices: (keys 0-7, d 8n..+7), (keys 8-15, same), (keys 0-7, d 8(n+1)..), (keys 8-15, same)
+                    uint32_t b[4];
+                    const int chunk = n + (mat >> 1);
+                    ldmatrix_x4_trans(b, swizzled(vt + (chunk / 8) * SUB_BYTES, 16 * warp + (mat & 1) * 8 + mrow,
+                                                  chunk % 8));
+                    mma_bf16_16816(o[n], pa0, pa1, pa2, pa3, b[0], b[1]);
+                    mma_bf16_16816(o[n + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);
+        }
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
+
+    // ---------------------------------------------------------------- merge the four warps
+    __syncthreads();   // every tile has been consumed: the ring's memory is used again
+    if (*abort_flag) {
+        for (int i = 0; i < 32; ++i) __nanosleep(2000);   // copies on their way may still land
+        if (threadIdx.x == 0 && status) atomicExch(status, 5);
+        return;
+    }
+    if (warp < DT_CONSUMERS) {
+        if (tq == 0) {
+            sm_m[warp * 16 + g] = m0;
+            sm_m[warp * 16 + g + 8] = m1;
+            sm_l[warp * 16 + g] = l0;
+            sm_l[warp * 16 + g + 8] = l1;
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                sm_o[(warp * 16 + g + 8 * (e >> 1)) * D + 8 * n + 2 * tq + (e & 1)] = o[n][e];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * D; idx += DT_THREADS) {
+        const int r = idx / D, col = idx % D;
+        if (hb * 16 + r >= G) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DT_CONSUMERS; ++w) mm = fmaxf(mm, sm_m[w * 16 + r]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < DT_CONSUMERS; ++w) {
+            const float wgt = sm_m[w * 16 + r] == -INFINITY ? 0.f : exp2f(sm_m[w * 16 + r] - mm);
+            acc += sm_o[(w * 16 + r) * D + col] * wgt;
+            ll += sm_l[w * 16 + r] * wgt;
+        }
+        const int h = kvh * G + hb * 16 + r;
+        if (splits == 1) {
+            out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll);
+        } else {
+            const size_t pi = ((size_t)t * H + h) * splits + split;
+            part_o[pi * D + col] = acc;
+            if (col == 0) {
+                part_ml[pi * 2] = mm;
+                part_ml[pi * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+template <int D>
+int launch_decode_tma(const CUtensorMap& map, const void* q, const int* block_table, int max_blocks,
+                      const int* token_seq, const int* positions, void* out, float* part_o, float* part_ml, int T,
+                      int H, int K, int P, int window, float scale, int splits, int* status, cudaStream_t stream) {
+    const int head_blocks = (H / K + 15) / 16;
+    const size_t ring = (size_t)DT_STAGES * 2 * (D / 64) * DT_TILE * 128;
+    const size_t merge = (size_t)(DT_CONSUMERS * 16 * D + 2 * DT_CONSUMERS * 16) * sizeof(float);
+    const size_t smem = 1024 + (ring > merge ? ring : merge) + 128;
+    auto kernel = decode_attention_tma_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return launch(kernel, dim3(splits, K * head_blocks, T), DT_THREADS, smem, stream, map, (const __nv_bfloat16*)q,
+                  block_table, max_blocks, token_seq, positions, (__nv_bfloat16*)out, part_o, part_ml, H, K, P, window,
+                  scale * 1.4426950408889634f, status);
+}
+
+}  // namespace air
+
+// The merge of the splits (attention_decode.cu).
+extern "C" int air_decode_combine(const float* part_o, const float* part_ml, const int* token_seq, void* out, int T,
+                                  int H, int D, int splits, cudaStream_t stream);
+
+// Arguments as air_decode_attention (attention_decode.cu), plus the number of pages of the cache
+// (its first dimension) and the status word.
+AIR_API int air_decode_attention_tma(const void* q, const void* cache, long long pages, const int* block_table,
+                                     int max_blocks, const int* token_seq, const int* positions, void* out,
+                                     float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
+                                     float scale, int splits, int* status, cudaStream_t stream) {
+    using namespace air;
+    if (T <= 0) return 0;
+    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || splits < 1 || T > 65535 ||
+        (splits > 1 && (!part_o || !part_ml)) || ((uintptr_t)cache & 15))
+        return AIR_ERR_BAD_ARGUMENT;
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return AIR_ERR_BAD_ARGUMENT;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)(pages * 2 * K * P)};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)(P < DT_TILE ? P : DT_TILE)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 200000 + (int)r;
+    int rc;
+    switch (D) {
+        case 64:
+            rc = launch_decode_tma<64>(map, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
+                                       K, P, window, scale, splits, status, stream);
+            break;
+        case 128:
+            rc = launch_decode_tma<128>(map, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
+                                        K, P, window, scale, splits, status, stream);
+            break;
+        case 256:
+            rc = launch_decode_tma<256>(map, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
+                                        K, P, window, scale, splits, status, stream);
+            break;
+        default:
+            return AIR_ERR_BAD_ARGUMENT;
+    }
+    if (rc == 0 && splits > 1) rc = air_decode_combine(part_o, part_ml, token_seq, out, T, H, D, splits, stream);
+    return rc;
+}
+
+AIR_API int air_trace_set_attention_decode_tma(unsigned long long* buffer) { return air::set_trace_here(buffer); }

@@ -32,6 +32,9 @@ _SIGNATURES = {
     "air_prefill_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_float, c_void_p],
     "air_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                 c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -262,15 +265,18 @@ DECODE_HEAD_DIMS = (64, 128, 256)
 
 
 def decode_splits(tokens: int, heads: int, kv_heads: int) -> int:
-    """How many blocks share the keys of one (token, kv head): as many as fit on the GPU at once
-    (two blocks per SM), so that no block waits for a second round."""
+    """How many blocks share the keys of one (token, kv head): so many that about 190 blocks run,
+    which keeps every SM busy without a second round (measured on B200: 6 for 8 tokens x 4 kv heads,
+    1 for 64 tokens, 32 for one token)."""
     per_split = tokens * kv_heads * (-(-(heads // kv_heads) // 16))
-    return max(1, min(32, 296 // per_split))
+    return max(1, min(32, round(192 / per_split)))
 
 
-def decode_attention(q, cache, block_table, token_seq, positions, out, window, scale, splits=None, scratch=None):
-    """bfloat16 attention for one query token per request (see attention_decode.cu).  scratch:
-    (float32 [T*H*splits*D], float32 [T*H*splits*2]) or None to allocate."""
+def decode_attention(q, cache, block_table, token_seq, positions, out, window, scale, splits=None, scratch=None,
+                     status=None, engine="tma"):
+    """bfloat16 attention for one query token per request.  scratch: (float32 [T*H*splits*D], float32
+    [T*H*splits*2]) or None to allocate.  engine "tma": keys and values by the copy engine into shared
+    memory (attention_decode_tma.cu); "ldg": by the warps' own loads (attention_decode.cu)."""
     T, H, d = q.shape
     K, P = cache.shape[2], cache.shape[3]
     _req(q, "q", (torch.bfloat16,))
@@ -294,10 +300,16 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
         if po.numel() < T * H * splits * d or pm.numel() < T * H * splits * 2:
             raise KernelError("decode_attention: scratch is too small")
     global launches
-    _check(_get("air_decode_attention")(
-        q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
-        positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P, int(window or 0), float(scale),
-        splits, _stream()), "decode_attention")
+    if engine == "tma" and (P >= 64 or 64 % P == 0):
+        _check(_get("air_decode_attention_tma")(
+            q.data_ptr(), cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
+            token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P,
+            int(window or 0), float(scale), splits, _ptr(status), _stream()), "decode_attention_tma")
+    else:
+        _check(_get("air_decode_attention")(
+            q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
+            positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P, int(window or 0), float(scale),
+            splits, _stream()), "decode_attention")
     if splits > 1:
         launches += 1
     return out

@@ -298,7 +298,8 @@ def test_kernels_refuse_what_they_cannot_take():
 @pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (4, 4, 128, 16), (40, 2, 64, 32), (8, 1, 256, 16)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("splits", [1, 3, 8])
-def test_decode_attention(H, K, d, P, window, splits):
+@pytest.mark.parametrize("engine", ["tma", "ldg"])
+def test_decode_attention(H, K, d, P, window, splits, engine):
     """One query per request, groups of 1 to 20 query heads per kv head, contexts from one key
     to several pages, any number of splits (also more splits than tiles)."""
     lens = [700, 1, 16, 17, 333, 64]
@@ -309,8 +310,10 @@ def test_decode_attention(H, K, d, P, window, splits):
     positions = np.insert(positions, 2, 0).astype(np.int32)
     seq_of = np.insert(seq_of, 2, -1).astype(np.int32)
     out = torch.full(q.shape, 7.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     ops().decode_attention(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(seq_of), dev(positions), out,
-                           window, 1.0 / math.sqrt(d), splits=splits)
+                           window, 1.0 / math.sqrt(d), splits=splits, status=status, engine=engine)
+    assert status.item() == 0
     keep = seq_of >= 0
     want = attention_reference(q[keep], ks, vs, positions[keep], seq_of[keep], window)
     got = out.float().cpu().numpy()
