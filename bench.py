@@ -133,6 +133,32 @@ def decode_device(engine, requests, steps, warmup, torch, Entry, LAST):
     return ms / steps, clocks.stop(), engine.kernel_launches() - launches0
 
 
+def decode_timeline(engine, requests, torch, Entry, LAST):
+    """Spans of the kernels of one decode step as they run inside the CUDA graph (from the moment a
+    kernel has passed the wait on its predecessor to the moment the next one has), by kernel."""
+    import collections
+    from air_b200.csrc import ops
+    again = [Entry(r, [LAST], [0]) for r in requests]
+    buf = torch.zeros(1 + 2 * 16384, dtype=torch.int64, device=engine.rt.device)
+    ops.set_trace(buf)
+    for _ in range(3):
+        engine.sample(engine.step(again))
+    torch.cuda.synchronize()
+    ops.set_trace(None)
+    b = buf.cpu().tolist()
+    events = sorted((b[2 + 2 * i], b[1 + 2 * i]) for i in range(min(b[0], 16384)) if b[1 + 2 * i] < 100)
+    start = [i for i, e in enumerate(events) if e[1] == 1][-1]           # the last step's embedding
+    step = events[start:]
+    spans = collections.defaultdict(lambda: [0, 0.0])
+    for (t0, k), (t1, _) in zip(step, step[1:]):
+        spans[ops.TRACE_NAMES[k]][0] += 1
+        spans[ops.TRACE_NAMES[k]][1] += (t1 - t0) / 1e3
+    total = (step[-1][0] - step[0][0]) / 1e3
+    print(f"decode step inside the graph: {total:.1f} us from embedding to sampling, {len(step)} kernels")
+    for name, (n, us) in sorted(spans.items(), key=lambda x: -x[1][1]):
+        print(f"  {name:18s} {n:4d} launches {us:9.1f} us  {100 * us / total:5.1f} %  {us / n:7.1f} us each")
+
+
 def decode_e2e(engine, requests, steps, warmup, torch):
     """The same through InferenceService.run_cycle, host tokens in and out every step."""
     from air_b200.engine.service import InferenceService, SchedulerConfig
@@ -177,6 +203,8 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling the decode step alone")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling the decode step alone")
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
+    ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
+    ap.add_argument("--timeline", action="store_true", help="also print the kernels' spans inside the decode graph")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -199,7 +227,8 @@ def main():
     per_request = -(-(args.context + 8) // page) * page
     max_tokens = max(batches) * per_request + 4096
     engine = Engine.from_random(cfg, seed=0, config=EngineConfig(
-        dtype=torch.bfloat16, page_tokens=page, max_tokens=max_tokens, max_requests=max(batches) + 1))
+        dtype=torch.bfloat16, page_tokens=page, max_tokens=max_tokens, max_requests=max(batches) + 1,
+        cuda_graphs=not args.no_graphs))
     mc = engine.model_config
     weight_bytes = engine.model.weight_bytes()
     kv_bytes_per_token = 2 * mc.num_key_value_heads * mc.head_dim * 2 * len(engine.model.spec.order)
@@ -214,6 +243,8 @@ def main():
         fill_cache(engine, requests, start_len, torch)
         ms, clocks, launches = decode_device(engine, requests, args.steps, args.warmup, torch, Entry, LAST_SAMPLED)
         results[b] = {"ms": ms, "clocks": clocks, "launches": launches}
+        if args.timeline and b == args.batch:
+            decode_timeline(engine, requests, torch, Entry, LAST_SAMPLED)
         release(engine, requests)
         if b == args.batch and not args.skip_e2e:
             fill_cache(engine, requests, start_len, torch)
