@@ -24,22 +24,6 @@ constexpr int DT_THREADS = (DT_CONSUMERS + 1) * 32;
 constexpr int DT_TILE = 64;     // keys per stage
 constexpr int DT_STAGES = 3;
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-
-// Address of the 16-byte chunk `chunk` (0..7) of row `row` in a [64][128 B] tile with 128-byte swizzle.
-__device__ __forceinline__ uint32_t swizzled(uint32_t tile, int row, int chunk) {
-    return tile + row * 128 + ((chunk ^ (row & 7)) << 4);
-}
-
 template <int D>
 __global__ void __launch_bounds__(DT_THREADS)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const __nv_bfloat16* __restrict__ q,

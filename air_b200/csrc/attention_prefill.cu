@@ -1,210 +1,298 @@
 // Causal attention over the paged cache for prompt portions in bfloat16 (any batch: several
 // requests, portions of any length, decoded tokens among them).
 //
-// The batch's tokens are cut on the host into tiles of up to 16 consecutive tokens of one
-// request.  A block takes one tile and one kv head; each of its warps takes one query head of
-// the group and computes the 16 x keys score matrix of that head with the tensor cores
-// (mma.sync m16n8k16, bf16 in, fp32 out), 16 keys at a time, with the online softmax in 32-bit.
-// Keys and values come straight from the pages into registers, with the same mapping of MMA
-// slots to the head dimension as the decode kernel (attention_decode.cu): a thread's operands
-// are 16-byte pieces of rows of K and V.  The warps of a block walk the same keys at the same
-// time, so the group's heads share the loaded lines in L1: the cache is read once per group.
+// The host cuts the batch's tokens into tiles of up to 16 consecutive tokens of one request, in
+// groups of 8 tiles that never straddle two requests (a group is filled up with empty tiles).  A
+// block takes TT consecutive tiles of a group and Gh query heads of one kv head, TT * Gh <= 8: one
+// warp per (tile, head), so that all its warps want the same keys.  A producer warp brings 64-key
+// tiles of K and V from the pages into a ring of shared-memory stages with TMA (128-byte swizzle);
+// the other warps wait on the stage's mbarrier, take their MMA operands from it with ldmatrix and
+// compute 16 x 64 scores at a time with mma.sync m16n8k16 (bf16 in, fp32 out), softmax online in
+// 32-bit.  A tile of keys is thus fetched once for up to 128 query rows.
 //
-// tiles [n, 4] int32: (slot, index of the tile's first token in the batch, its position, rows).
-// q, out: [T, H, D] bf16.  cache: [page, 2, K, P, D] bf16.  block_table [slots, max_blocks].
-// The query at position p sees keys max(0, p - window + 1) .. p (window 0: all keys).
+// tiles [8n, 4] int32: (slot, index of the tile's first token in the batch, its position, rows);
+// rows = 0 marks an empty tile.  q, out: [T, H, D] bf16.  cache: [page, 2, K, P, D] bf16.
+// block_table [slots, max_blocks].  The query at position p sees keys max(0, p - window + 1) .. p.
+// Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 6.
 #include "common.cuh"
 #include "mma.cuh"
+#include "tma.cuh"
 
 namespace air {
 
-constexpr int PRE_MAX_WARPS = 8;
+constexpr int PF_MAX_CONSUMERS = 8;
+constexpr int PF_TILE = 64;      // keys per stage
+constexpr int PF_STAGES = 3;
+constexpr int PF_GROUP = 8;      // tiles of 16 tokens per group in the host's list
 
 template <int D>
-__global__ void __launch_bounds__(PRE_MAX_WARPS * 32)
-prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+__global__ void __launch_bounds__((PF_MAX_CONSUMERS + 1) * 32)
+prefill_attention_kernel(const __grid_constant__ CUtensorMap map_cache, const __nv_bfloat16* __restrict__ q,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tiles,
-                         __nv_bfloat16* __restrict__ out, int H, int K, int P, int window, float scale_log2) {
-    constexpr int KC = D / 32, NT = D / 8, NG = D / 64;
-    extern __shared__ float smem[];   // [warps][16][D + 4]: the output tile of each warp
-    pdl_enter(TR_ATT_PREFILL);
+                         __nv_bfloat16* __restrict__ out, int H, int K, int P, int window, float scale_log2, int Gh,
+                         int TT, int* status) {
+    constexpr int SUB = D / 64;
+    constexpr int SUB_BYTES = PF_TILE * 128;
+    constexpr int STAGE_BYTES = 2 * SUB * SUB_BYTES;
+    constexpr int KS = D / 16, NT = D / 8;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + PF_STAGES * STAGE_BYTES);
+    uint64_t* empty = full + PF_STAGES;
+    volatile int* abort_flag = (volatile int*)(empty + PF_STAGES);
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int consumers = TT * Gh;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < PF_STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], consumers);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (P < PF_TILE || window > 0) {   // see attention_decode_tma.cu: rows that no copy fills must not hold NaN bits
+        for (int i = threadIdx.x; i < PF_STAGES * STAGE_BYTES / 16; i += blockDim.x)
+            reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();
+    trace_point(TR_ATT_PREFILL);
+
+    // the block's tiles: heavy ones (late in their request) first
+    const int first_entry = (gridDim.x - 1 - blockIdx.x) * TT;
+    int slot = -1, pos_first = 0, pos_last = -1;
+    for (int i = 0; i < TT; ++i) {
+        const int* e = tiles + 4 * (first_entry + i);
+        if (e[3] > 0) {
+            if (slot < 0) { slot = e[0]; pos_first = e[2]; }
+            pos_last = e[2] + e[3] - 1;
+        }
+    }
+    if (slot < 0) return;     // only empty tiles
     const int G = H / K;
-    const int head_blocks = (G + PRE_MAX_WARPS - 1) / PRE_MAX_WARPS;
+    const int head_blocks = (G + Gh - 1) / Gh;
     const int kvh = blockIdx.y / head_blocks, hb = blockIdx.y % head_blocks;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int hg = hb * PRE_MAX_WARPS + warp;        // head within the group
-    if (hg >= G) return;
-    const int h = kvh * G + hg;
-    const int g = lane >> 2, tq = lane & 3;
-    const int* tile = tiles + 4 * blockIdx.x;
-    const int slot = tile[0], tok0 = tile[1], pos0 = tile[2], rows = tile[3];
     const int* bt = block_table + (size_t)slot * max_blocks;
-    const int last = pos0 + rows - 1;
-    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
-    const int p0 = pos0 + g, p1 = pos0 + g + 8;     // positions of this thread's two rows
+    const int lo_block = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int tile0 = lo_block / PF_TILE, n_tiles = pos_last / PF_TILE + 1 - tile0;
 
-    uint4 qa[KC], qb[KC];
+    if (warp == consumers) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            const int box_rows = P < PF_TILE ? P : PF_TILE;
+            const int boxes = PF_TILE / box_rows;
+            for (int it = 0; it < n_tiles; ++it) {
+                const int stage = it % PF_STAGES;
+                if (it >= PF_STAGES && !mbar_wait(&empty[stage], ((it / PF_STAGES) - 1) & 1, abort_flag)) break;
+                const int kbase = (tile0 + it) * PF_TILE;
+                int valid = 0;
+                for (int b = 0; b < boxes; ++b) {
+                    const int first = kbase + b * box_rows;
+                    valid += (first <= pos_last && first + box_rows - 1 >= lo_block) ? 1 : 0;
+                }
+                mbar_expect_tx(&full[stage], (uint32_t)(valid * box_rows * 128 * SUB * 2));
+                uint8_t* dst = smem + stage * STAGE_BYTES;
+                for (int b = 0; b < boxes; ++b) {
+                    const int first = kbase + b * box_rows;
+                    if (!(first <= pos_last && first + box_rows - 1 >= lo_block)) continue;
+                    const int page = bt[first / P];
+                    const int row_k = ((page * 2) * K + kvh) * P + first % P;
+                    const int row_v = row_k + K * P;
 #pragma unroll
-    for (int c = 0; c < KC; ++c) {
-        qa[c] = g < rows ? ldg16(q + ((size_t)(tok0 + g) * H + h) * D + 32 * c + 8 * tq) : make_uint4(0, 0, 0, 0);
-        qb[c] = g + 8 < rows ? ldg16(q + ((size_t)(tok0 + g + 8) * H + h) * D + 32 * c + 8 * tq)
-                             : make_uint4(0, 0, 0, 0);
+                    for (int s = 0; s < SUB; ++s) {
+                        tma_load_2d(dst + s * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_k, &full[stage]);
+                        tma_load_2d(dst + (SUB + s) * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_v,
+                                    &full[stage]);
+                    }
+                }
+            }
+        }
+    } else if (warp < consumers) {
+        // ------------------------------------------------------------ consumers: one (tile, head) each
+        const int* e = tiles + 4 * (first_entry + warp / Gh);
+        const int tok0 = e[1], pos0 = e[2], rows = e[3];
+        const int hg = hb * Gh + warp % Gh;
+        const bool active = rows > 0 && hg < G;
+        const int h = kvh * G + hg;
+        const int g = lane >> 2, tq = lane & 3;
+        const int mat = lane >> 3, mrow = lane & 7;
+        const int last = pos0 + rows - 1;
+        const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+        const int p0 = pos0 + g, p1 = pos0 + g + 8;
+        uint32_t qa[KS][4];
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk) {
+            const __nv_bfloat16* q0 = q + ((size_t)(tok0 + g) * H + h) * D + 16 * kk + 2 * tq;
+            const __nv_bfloat16* q1 = q + ((size_t)(tok0 + g + 8) * H + h) * D + 16 * kk + 2 * tq;
+            const bool a0 = active && g < rows, a1 = active && g + 8 < rows;
+            qa[kk][0] = a0 ? __ldg(reinterpret_cast<const uint32_t*>(q0)) : 0u;
+            qa[kk][1] = a1 ? __ldg(reinterpret_cast<const uint32_t*>(q1)) : 0u;
+            qa[kk][2] = a0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + 8)) : 0u;
+            qa[kk][3] = a1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + 8)) : 0u;
+        }
+        float o[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+        for (int it = 0; it < n_tiles; ++it) {
+            const int stage = it % PF_STAGES;
+            if (!mbar_wait(&full[stage], (it / PF_STAGES) & 1, abort_flag)) break;
+            const int kbase = (tile0 + it) * PF_TILE;
+            if (active && kbase <= last && kbase + PF_TILE - 1 >= lo) {
+                const uint32_t kt = smem_u32(smem + stage * STAGE_BYTES);
+                const uint32_t vt = kt + SUB * SUB_BYTES;
+                float s[8][4];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        uint32_t b[4];
+                        ldmatrix_x4(b, swizzled(kt + (kk / 4) * SUB_BYTES, 16 * np + (mat >> 1) * 8 + mrow,
+                                                2 * (kk % 4) + (mat & 1)));
+                        mma_bf16_16816(s[2 * np], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b[0], b[1]);
+                        mma_bf16_16816(s[2 * np + 1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b[2], b[3]);
+                    }
+                }
+                const bool inner = kbase + PF_TILE - 1 <= pos0 && (window <= 0 || kbase > last - window);
+                float tm0 = -INFINITY, tm1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int ee = 0; ee < 2; ++ee) {
+                        const int key = kbase + 8 * j + 2 * tq + ee;
+                        const bool ok0 = inner || (key <= p0 && (window <= 0 || key > p0 - window));
+                        const bool ok1 = inner || (key <= p1 && (window <= 0 || key > p1 - window));
+                        s[j][ee] = ok0 ? s[j][ee] * scale_log2 : -INFINITY;
+                        s[j][2 + ee] = ok1 ? s[j][2 + ee] * scale_log2 : -INFINITY;
+                        tm0 = fmaxf(tm0, s[j][ee]);
+                        tm1 = fmaxf(tm1, s[j][2 + ee]);
+                    }
+                tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1));
+                tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
+                tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1));
+                tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
+                const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);
+                // a row that has seen no key yet keeps maximum -inf: subtract 0 instead, all its p are 0
+                const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;
+                const float c0 = exp2f(m0 - b0), c1 = exp2f(m1 - b1);
+                m0 = n0;
+                m1 = n1;
+                float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    s[j][0] = exp2f(s[j][0] - b0);
+                    s[j][1] = exp2f(s[j][1] - b0);
+                    s[j][2] = exp2f(s[j][2] - b1);
+                    s[j][3] = exp2f(s[j][3] - b1);
+                    sum0 += s[j][0] + s[j][1];
+                    sum1 += s[j][2] + s[j][3];
+                }
+                l0 = l0 * c0 + sum0;
+                l1 = l1 * c1 + sum1;
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    o[n][0] *= c0;
+                    o[n][1] *= c0;
+                    o[n][2] *= c1;
+                    o[n][3] *= c1;
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint32_t pa0 = pack_bf16(s[2 * ks][0], s[2 * ks][1]), pa1 = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+                    const uint32_t pa2 = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+                    const uint32_t pa3 = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+                    for (int n = 0; n < NT; n += 2) {
+                        uint32_t b[4];
+                        const int chunk = n + (mat >> 1);
+                        ldmatrix_x4_trans(b, swizzled(vt + (chunk / 8) * SUB_BYTES, 16 * ks + (mat & 1) * 8 + mrow,
+                                                      chunk % 8));
+                        mma_bf16_16816(o[n], pa0, pa1, pa2, pa3, b[0], b[1]);
+                        mma_bf16_16816(o[n + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);
+        }
+        if (active && !*abort_flag) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+            const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+            __nv_bfloat16* d0 = out + ((size_t)(tok0 + g) * H + h) * D + 2 * tq;
+            __nv_bfloat16* d1 = out + ((size_t)(tok0 + g + 8) * H + h) * D + 2 * tq;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                if (g < rows) *reinterpret_cast<uint32_t*>(d0 + 8 * n) = pack_bf16(o[n][0] * i0, o[n][1] * i0);
+                if (g + 8 < rows) *reinterpret_cast<uint32_t*>(d1 + 8 * n) = pack_bf16(o[n][2] * i1, o[n][3] * i1);
+            }
+        }
     }
-    float o[NT][4];
-#pragma unroll
-    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-
-    const size_t page_stride = (size_t)2 * K * P * D;
-    const size_t v_offset = (size_t)K * P * D;
-    for (int kt = lo / 16; kt * 16 <= last; ++kt) {
-        const int kbase = kt * 16;
-        const int page = bt[kbase / P];
-        const __nv_bfloat16* kp = cache + (size_t)page * page_stride + ((size_t)kvh * P + (kbase % P)) * D;
-        const __nv_bfloat16* vp = kp + v_offset;
-        uint4 kf[2][KC];
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int c = 0; c < KC; ++c) kf[j][c] = ldg16(kp + (size_t)(8 * j + g) * D + 32 * c + 8 * tq);
-        uint4 vf[4][NG];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int n = 0; n < NG; ++n)
-                vf[i][n] = ldg16(vp + (size_t)(2 * tq + (i & 1) + 8 * (i >> 1)) * D + 64 * n + 8 * g);
-
-        float s[2][4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-#pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                mma_bf16_16816(s[j], qa[c].x, qb[c].x, qa[c].y, qb[c].y, kf[j][c].x, kf[j][c].y);
-                mma_bf16_16816(s[j], qa[c].z, qb[c].z, qa[c].w, qb[c].w, kf[j][c].z, kf[j][c].w);
-            }
-        }
-        const bool inner = kbase + 15 <= pos0 && (window <= 0 || kbase > last - window);  // no mask needed
-        float tm0 = -INFINITY, tm1 = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = kbase + 8 * j + 2 * tq + e;
-                const bool ok0 = inner || (key <= p0 && (window <= 0 || key > p0 - window));
-                const bool ok1 = inner || (key <= p1 && (window <= 0 || key > p1 - window));
-                s[j][e] = ok0 ? s[j][e] * scale_log2 : -INFINITY;
-                s[j][2 + e] = ok1 ? s[j][2 + e] * scale_log2 : -INFINITY;
-                tm0 = fmaxf(tm0, s[j][e]);
-                tm1 = fmaxf(tm1, s[j][2 + e]);
-            }
-        tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1));
-        tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
-        tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1));
-        tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
-        const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);
-        // a row that has seen no key yet keeps maximum -inf: subtract 0 instead, all its p are 0
-        const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;
-        const float c0 = exp2f(m0 - b0), c1 = exp2f(m1 - b1);
-        m0 = n0;
-        m1 = n1;
-        float p[2][4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            p[j][0] = exp2f(s[j][0] - b0);
-            p[j][1] = exp2f(s[j][1] - b0);
-            p[j][2] = exp2f(s[j][2] - b1);
-            p[j][3] = exp2f(s[j][3] - b1);
-        }
-        l0 = l0 * c0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
-        l1 = l1 * c1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
-        const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa1 = pack_bf16(p[0][2], p[0][3]);
-        const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]), pa3 = pack_bf16(p[1][2], p[1][3]);
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            o[n][0] *= c0;
-            o[n][1] *= c0;
-            o[n][2] *= c1;
-            o[n][3] *= c1;
-        }
-#pragma unroll
-        for (int n = 0; n < NG; ++n) {
-            const uint32_t a[4] = {vf[0][n].x, vf[0][n].y, vf[0][n].z, vf[0][n].w};
-            const uint32_t b[4] = {vf[1][n].x, vf[1][n].y, vf[1][n].z, vf[1][n].w};
-            const uint32_t c[4] = {vf[2][n].x, vf[2][n].y, vf[2][n].z, vf[2][n].w};
-            const uint32_t d[4] = {vf[3][n].x, vf[3][n].y, vf[3][n].z, vf[3][n].w};
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                mma_bf16_16816(o[8 * n + 2 * w], pa0, pa1, pa2, pa3, __byte_perm(a[w], b[w], 0x5410),
-                               __byte_perm(c[w], d[w], 0x5410));
-                mma_bf16_16816(o[8 * n + 2 * w + 1], pa0, pa1, pa2, pa3, __byte_perm(a[w], b[w], 0x7632),
-                               __byte_perm(c[w], d[w], 0x7632));
-            }
-        }
-    }
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
-
-    // through shared memory, so that rows are written in whole 16-byte pieces
-    float* so = smem + (size_t)warp * 16 * (D + 4);
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int col = (n / 8) * 64 + 8 * (2 * tq + (e & 1)) + (n % 8);
-            so[(g + 8 * (e >> 1)) * (D + 4) + col] = o[n][e] * ((e >> 1) ? i1 : i0);
-        }
-    __syncwarp();
-    for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
-        const int r = idx / (D / 8), c8 = (idx % (D / 8)) * 8;
-        if (r >= rows) continue;
-        const float* src = so + r * (D + 4) + c8;
-        uint4 v;
-        v.x = pack_bf16(src[0], src[1]);
-        v.y = pack_bf16(src[2], src[3]);
-        v.z = pack_bf16(src[4], src[5]);
-        v.w = pack_bf16(src[6], src[7]);
-        *reinterpret_cast<uint4*>(out + ((size_t)(tok0 + r) * H + h) * D + c8) = v;
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 32; ++i) __nanosleep(2000);
+        if (threadIdx.x == 0 && status) atomicExch(status, 6);
     }
 }
 
 template <int D>
-int launch_prefill(const void* q, const void* cache, const int* block_table, int max_blocks, const int* tiles,
-                   int n_tiles, void* out, int H, int K, int P, int window, float scale, cudaStream_t stream) {
+int launch_prefill(const CUtensorMap& map, const void* q, const int* block_table, int max_blocks, const int* tiles,
+                   int n_tiles, void* out, int H, int K, int P, int window, float scale, int* status,
+                   cudaStream_t stream) {
     const int G = H / K;
-    const int warps = G < PRE_MAX_WARPS ? G : PRE_MAX_WARPS;
-    const int head_blocks = (G + PRE_MAX_WARPS - 1) / PRE_MAX_WARPS;
-    const size_t smem = (size_t)warps * 16 * (D + 4) * sizeof(float);
+    const int Gh = G < PF_MAX_CONSUMERS ? G : PF_MAX_CONSUMERS;
+    int TT = PF_MAX_CONSUMERS / Gh;                      // tiles per block: 1, 2, 4 or 8
+    TT = TT >= 8 ? 8 : (TT >= 4 ? 4 : (TT >= 2 ? 2 : 1));
+    const int head_blocks = (G + Gh - 1) / Gh;
+    const size_t smem = 1024 + (size_t)PF_STAGES * 2 * (D / 64) * PF_TILE * 128 + 128;
     auto kernel = prefill_attention_kernel<D>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    dim3 grid(n_tiles, K * head_blocks);
-    return launch(kernel, grid, warps * 32, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
-                  block_table, max_blocks, tiles, (__nv_bfloat16*)out, H, K, P, window, scale * 1.4426950408889634f);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return launch(kernel, dim3(n_tiles / TT, K * head_blocks), (TT * Gh + 1) * 32, smem, stream, map,
+                  (const __nv_bfloat16*)q, block_table, max_blocks, tiles, (__nv_bfloat16*)out, H, K, P, window,
+                  scale * 1.4426950408889634f, Gh, TT, status);
 }
 
 }  // namespace air
 
-AIR_API int air_prefill_attention(const void* q, const void* cache, const int* block_table, int max_blocks,
-                                  const int* tiles, int n_tiles, void* out, int H, int K, int D, int P, int window,
-                                  float scale, cudaStream_t stream) {
+// tiles: n_tiles entries, a multiple of 8, in groups of 8 that each belong to one request.
+AIR_API int air_prefill_attention(const void* q, const void* cache, long long pages, const int* block_table,
+                                  int max_blocks, const int* tiles, int n_tiles, void* out, int H, int K, int D, int P,
+                                  int window, float scale, int* status, cudaStream_t stream) {
+    using namespace air;
     if (n_tiles <= 0) return 0;
-    if (H <= 0 || K <= 0 || H % K || P % 16 || K * ((H / K + 7) / 8) > 65535) return AIR_ERR_BAD_ARGUMENT;
+    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || n_tiles % PF_GROUP || ((uintptr_t)cache & 15) ||
+        K * ((H / K + 7) / 8) > 65535)
+        return AIR_ERR_BAD_ARGUMENT;
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return AIR_ERR_BAD_ARGUMENT;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)(pages * 2 * K * P)};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)(P < PF_TILE ? P : PF_TILE)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 200000 + (int)r;
     switch (D) {
         case 64:
-            return air::launch_prefill<64>(q, cache, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window,
-                                           scale, stream);
+            return launch_prefill<64>(map, q, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window, scale,
+                                      status, stream);
         case 128:
-            return air::launch_prefill<128>(q, cache, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window,
-                                            scale, stream);
+            return launch_prefill<128>(map, q, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window, scale,
+                                       status, stream);
         case 256:
-            return air::launch_prefill<256>(q, cache, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window,
-                                            scale, stream);
+            return launch_prefill<256>(map, q, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window, scale,
+                                       status, stream);
         default:
             return AIR_ERR_BAD_ARGUMENT;
     }

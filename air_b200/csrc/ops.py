@@ -29,8 +29,8 @@ _SIGNATURES = {
     "air_table_update": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_decode_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "air_prefill_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                              c_int, c_int, c_float, c_void_p],
+    "air_prefill_attention": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                              c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "air_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
@@ -315,9 +315,13 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
     return out
 
 
-def prefill_attention(q, cache, block_table, tiles, out, window, scale):
+TILE_GROUP = 8     # the list of 16-token tiles comes in groups of 8 that belong to one request
+
+
+def prefill_attention(q, cache, block_table, tiles, out, window, scale, status=None):
     """bfloat16 causal attention for tiles of up to 16 consecutive tokens of a request (see
-    attention_prefill.cu).  tiles [n, 4] int32: (slot, first token, its position, rows)."""
+    attention_prefill.cu).  tiles [8n, 4] int32: (slot, first token, its position, rows), in groups of
+    8 tiles of one request; rows = 0 marks an empty tile."""
     T, H, d = q.shape
     K, P = cache.shape[2], cache.shape[3]
     _req(q, "q", (torch.bfloat16,))
@@ -327,9 +331,14 @@ def prefill_attention(q, cache, block_table, tiles, out, window, scale):
     _req(out, "out", (torch.bfloat16,), (T, H, d))
     if d not in DECODE_HEAD_DIMS:
         raise KernelError(f"prefill_attention takes head sizes {DECODE_HEAD_DIMS}, not {d}")
+    if tiles.shape[0] % TILE_GROUP:
+        raise KernelError("prefill_attention: the tile list must come in groups of 8")
+    if P < 64 and 64 % P:
+        raise KernelError(f"prefill_attention: page size {P} does not divide 64")
     _check(_get("air_prefill_attention")(
-        q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(),
-        tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _stream()), "prefill_attention")
+        q.data_ptr(), cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
+        tiles.data_ptr(), tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _ptr(status),
+        _stream()), "prefill_attention")
     return out
 
 

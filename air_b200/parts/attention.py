@@ -98,8 +98,9 @@ class Attention(Mixer):
         out = torch.empty_like(q)
         if rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.all_decode:
             ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
-        elif rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.tiles is not None:
-            ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale)
+        elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.tiles is not None
+              and (pages.kv.shape[3] >= 64 or 64 % pages.kv.shape[3] == 0)):
+            ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
         else:
             ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         out = out.view(T, H * d)

@@ -340,11 +340,14 @@ def tiles_for(lens, q_lens):
     for s, (n, ql) in enumerate(zip(lens, q_lens)):
         for i in range(0, ql, 16):
             tiles.append([s, tok + i, n - ql + i, min(16, ql - i)])
+        while len(tiles) % 8:
+            tiles.append([s, 0, 0, 0])          # groups of 8 tiles per request
         tok += ql
     return np.array(tiles, dtype=np.int32)
 
 
-@pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (3, 3, 128, 16), (20, 2, 64, 32), (4, 1, 256, 16)])
+@pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (3, 3, 128, 16), (20, 2, 64, 32), (4, 1, 256, 16),
+                                     (8, 4, 128, 128), (24, 2, 64, 64)])
 @pytest.mark.parametrize("window", [0, 21, 100])
 def test_prefill_attention(H, K, d, P, window):
     """Portions of 1 to 150 tokens at any offset in their requests, groups of 1 to 10 heads."""
