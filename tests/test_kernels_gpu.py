@@ -374,3 +374,17 @@ def test_prefill_attention_finds_one_far_key(far):
     for t in range(16):
         for h in range(H):
             assert np.abs(got[t, h] - vs[0][far, h * K // H]).max() < 2e-2
+
+
+@pytest.mark.parametrize("T,I,block", [(3, 352, 32), (37, 1024, 128), (5, 208, 208), (9, 120, 24), (2, 18944, 128)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul_with_gate_and_up_in_blocks(T, I, block, dtype):
+    g = torch.Generator().manual_seed(I + block)
+    gate = (torch.randn(T, I, generator=g) * 3).to(DT[dtype])
+    up = (torch.randn(T, I, generator=g) * 3).to(DT[dtype])
+    x = torch.stack([gate.view(T, I // block, block), up.view(T, I // block, block)], dim=2).reshape(T, 2 * I)
+    out = torch.empty(T, I, dtype=DT[dtype], device="cuda")
+    ops().silu_mul(dev(x.contiguous()), out, block=block)
+    want = plain.silu(gate.float().numpy()) * up.float().numpy()
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    assert np.abs(out.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
