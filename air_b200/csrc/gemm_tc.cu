@@ -25,6 +25,7 @@
 // is set to 4.  The host reads *status with the step's other error codes.
 #include "common.cuh"
 #include "tma.cuh"
+#include "umma.cuh"
 
 namespace air {
 
@@ -33,50 +34,6 @@ constexpr int TC_BK = 64;
 constexpr int TC_THREADS = 192;
 
 enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
-// 128-byte swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
-__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 struct TcArgs {
     void* out;          // EPI_F32/PARTIAL: float [splits][M][N]; EPI_BF16: bf16 [M][N]; EPI_SILU: bf16 [M][N/2]
@@ -192,7 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             // ------------------------------------------------ MMA issuer
-            constexpr uint32_t idesc = umma_idesc(BN);
+            constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
             uint32_t stage = 0, phase = 0, it = 0;
             for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++it) {
                 const int split = tile % args.splits;

@@ -35,6 +35,8 @@ _SIGNATURES = {
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                  c_void_p],
+    "air_prefill_attention_tc": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -374,4 +376,30 @@ def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0):
         raise KernelError(f"gemm_tc: N = {N} must be a multiple of 4")
     _check(_get("air_gemm_tc")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits, max_blocks,
                                _ptr(status), _stream()), "gemm_tc")
+    return out
+
+
+TC_ATTENTION_HEAD_DIMS = (64, 128)
+
+
+def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, status=None):
+    """bfloat16 causal attention with both products on the tcgen05 tensor cores (see
+    attention_prefill_tc.cu); arguments as prefill_attention; head size 64 or 128."""
+    T, H, d = q.shape
+    K, P = cache.shape[2], cache.shape[3]
+    _req(q, "q", (torch.bfloat16,))
+    _req(cache, "cache", (torch.bfloat16,), (None, 2, None, None, d))
+    _req(block_table, "block_table", _I32)
+    _req(tiles, "tiles", _I32, (None, 4))
+    _req(out, "out", (torch.bfloat16,), (T, H, d))
+    if d not in TC_ATTENTION_HEAD_DIMS:
+        raise KernelError(f"prefill_attention_tc takes head sizes {TC_ATTENTION_HEAD_DIMS}, not {d}")
+    if tiles.shape[0] % TILE_GROUP:
+        raise KernelError("prefill_attention_tc: the tile list must come in groups of 8")
+    if P < 64 and 64 % P:
+        raise KernelError(f"prefill_attention_tc: page size {P} does not divide 64")
+    _check(_get("air_prefill_attention_tc")(
+        q.data_ptr(), T, cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
+        tiles.data_ptr(), tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _ptr(status),
+        _stream()), "prefill_attention_tc")
     return out

@@ -100,7 +100,10 @@ class Attention(Mixer):
             ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.tiles is not None
               and (pages.kv.shape[3] >= 64 or 64 % pages.kv.shape[3] == 0)):
-            ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
+            if d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
+                ops.prefill_attention_tc(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
+            else:
+                ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
         else:
             ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         out = out.view(T, H * d)

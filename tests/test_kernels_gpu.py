@@ -388,3 +388,34 @@ def test_silu_mul_with_gate_and_up_in_blocks(T, I, block, dtype):
     want = plain.silu(gate.float().numpy()) * up.float().numpy()
     tol = 2e-6 if dtype == "float32" else 1e-2
     assert np.abs(out.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+
+
+@pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (3, 3, 128, 16), (20, 2, 64, 32), (8, 4, 128, 128)])
+@pytest.mark.parametrize("window", [0, 21, 100])
+def test_prefill_attention_tc(H, K, d, P, window):
+    """The tcgen05 attention: portions of 1 to 150 tokens at any offset in their requests."""
+    lens, q_lens = [150, 1, 64, 33, 333, 200], [150, 1, 1, 33, 18, 77]
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, lens, q_lens, "bfloat16", seed=H + window,
+                                                         num_pages=90)
+    out = torch.full(q.shape, 7.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().prefill_attention_tc(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(tiles_for(lens, q_lens)),
+                               out, window, 1.0 / math.sqrt(d), status=status)
+    assert status.item() == 0
+    want = attention_reference(q, ks, vs, positions, seq_of, window)
+    assert np.abs(out.float().cpu().numpy() - want).max() < 1e-2 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("far", [0, 15, 63, 64, 500, 1023])
+def test_prefill_attention_tc_finds_one_far_key(far):
+    H, K, d, P, n = 8, 2, 128, 64, 1040
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [16], "bfloat16", seed=far, num_pages=20)
+    q[:] = 0.5
+    cache[bt[0, far // P], 0, :, far % P, :] = 8.0
+    out = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
+    ops().prefill_attention_tc(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(tiles_for([n], [16])),
+                               out, 0, 1.0 / math.sqrt(d))
+    got = out.float().cpu().numpy()
+    for t in range(16):
+        for h in range(H):
+            assert np.abs(got[t, h] - vs[0][far, h * K // H]).max() < 2e-2
