@@ -1,21 +1,31 @@
 // Causal attention over the paged cache for prompt portions in bfloat16 on the fifth-generation
-// tensor cores: both products of attention are tcgen05.mma with operands in shared memory and
-// accumulators in tensor memory.
+// tensor cores: both products of attention are tcgen05.mma with accumulators in tensor memory.
 //
-// A block takes one group of the host's tile list (up to 128 consecutive tokens of one request,
-// see attention_prefill.cu) and one query head; its 128 query rows are the M dimension.
-//   warp 0    TMA: the Q tile once, then 64-key tiles of K and V from the pages into a ring;
-//   warp 1    issues S = Q K^T (M 128, N 64, k = head dim) into one of two S accumulators and,
-//             one tile behind, O += P V (M 128, N = head dim, k = 64 keys; V is the MN-major operand,
-//             read as it lies in the page);
-//   warps 2-5 softmax: thread r owns query row r.  It reads its row of S from tensor memory, masks,
-//             keeps a reference maximum and the sum (32-bit), rescales its row of O in tensor memory
-//             when the maximum has moved far, and writes its row of P as bfloat16 into shared memory in
-//             the swizzled K-major layout that the second product reads.  No value crosses threads.
+// A block takes two consecutive groups of the host's tile list (two row tiles of up to 128
+// consecutive tokens of one request, see attention_prefill.cu) and one query head.  The two row
+// tiles share one stream of 64-key tiles of K and V, so a key tile is fetched once for 256 queries.
+//   warp 0      TMA: the Q tiles once, then the key tiles from the pages into a ring;
+//   warps 1, 2  one issuer per row tile: S = Q K^T (M 128, N 64, k = head dim) into one of the row
+//               tile's two S accumulators and, one key tile behind, O += P V (M 128, N = head dim,
+//               k = 64 keys; P is the A operand in tensor memory, V the MN-major B operand, read as
+//               it lies in the page).  tcgen05.mma is all but synchronous for its issuer (a second
+//               instruction waits until the first has started), so whatever an issuer does between
+//               two products leaves the tensor cores idle: with two issuers one's waits are the
+//               other's work.
+//   warps 4-7, 8-11  softmax of the two row tiles: thread r owns query row r.  It reads its row of S
+//               from tensor memory, masks, keeps a reference maximum and the sum (32-bit), rescales
+//               its row of O in tensor memory when the maximum has moved far, and writes its row of P
+//               as bfloat16 pairs over the scores it came from.  No value crosses threads.  A warp's
+//               ex2 takes eight cycles on the special-function unit, so part of the exponentials are
+//               computed on the multiply-add pipe instead (exp2_fma).
 // S(j+1) is multiplied while softmax works on S(j); P V (j) follows as soon as P(j) is written.
+// Under the causal mask the second row tile takes two more key tiles than the first; with a
+// window it also starts later.  A row tile's issuer hands back the stages it does not take.
 //
-// tiles, q, out, cache, block_table, window as in attention_prefill.cu.  Head size 64 or 128.
-// Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 7.
+// tiles, q, out, cache, block_table, window as in attention_prefill.cu; the list pads every request
+// to whole pairs of groups.  Head size 64 or 128.
+// Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 7.  A list
+// whose second group does not go on where the first ends flags *status = 6 (that group is skipped).
 #include "common.cuh"
 #include "tma.cuh"
 #include "umma.cuh"
@@ -24,9 +34,10 @@ namespace air {
 
 constexpr int AT_BM = 128;      // query rows per block
 constexpr int AT_BN = 64;       // keys per step
-constexpr int AT_STAGES = 3;
-constexpr int AT_THREADS = 192;
-constexpr int AT_GROUP = 8;     // 16-token tiles per group of the host's list
+constexpr int AT_ROW_TILES = 2; // row tiles of 128 queries per block, on one stream of keys
+constexpr int AT_STAGES = 4;
+constexpr int AT_THREADS = 384; // warp 0 copies, warps 1 and 2 issue, warps 4-7 and 8-11 are the two softmax groups
+constexpr int AT_GROUP = 8;     // 16-token tiles per group of the host's list (one row tile)
 
 // 2^x by the special-function unit in one instruction (2^-inf = 0; relative error about 2^-22,
 // far below what rounding the probabilities to bfloat16 adds).
@@ -36,33 +47,72 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Two non-negative floats to a pair of bfloat16 (round half up) with integer adds and one byte
+// permute.  The conversion instruction shares the special-function pipe with ex2, which is what
+// this kernel waits for most (79 % busy before this change); the integer pipe is nearly idle.
+__device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x for a pair, on the multiply-add pipe instead of the special-function unit (which takes eight
+// cycles for a warp's ex2 and is what a row-per-thread softmax waits for).  x is clamped to -126,
+// rounded to the nearest integer n by adding 1.5 * 2^23, 2^(x - n) is a cubic on [-0.5, 0.5] (minimax
+// in relative error, 7.5e-5: far below the bfloat16 rounding of the probabilities), and n goes into the
+// exponent field by an integer shift and add.
+__device__ __forceinline__ float2 exp2_fma(float2 x) {
+    const float magic = 12582912.f;
+    x.x = fmaxf(x.x, -126.f);
+    x.y = fmaxf(x.y, -126.f);
+    const float2 t = __fadd2_rn(x, make_float2(magic, magic));
+    const float2 f = __fadd2_rn(x, __fadd2_rn(make_float2(magic, magic), make_float2(-t.x, -t.y)));
+    float2 q = __ffma2_rn(f, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.242611125f, 0.242611125f));
+    q = __ffma2_rn(q, f, make_float2(0.693260968f, 0.693260968f));
+    q = __ffma2_rn(q, f, make_float2(0.999928057f, 0.999928057f));
+    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
+                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
+}
+// Which of every eight pairs of a row take exp2_fma (the rest take ex2): balances the two pipes.
+constexpr uint32_t EXP_FMA_PAIRS = 0x52;
+
+// One row tile's softmax (see the file's head).  X picks the tile's accumulators and barriers.
+struct RowTile {
+    int count;       // query rows of the tile that exist
+    int pos0;        // position of its first row
+    int tok0;        // flat index of its first row
+    int first;       // index in the block's key stream of the first key tile it takes
+    int n;           // key tiles it takes
+};
+
 template <int D>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_cache,
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tiles,
                             __nv_bfloat16* __restrict__ out, int H, int K, int P, int window, float scale_log2,
-                            int* status) {
-    constexpr int SUB = D / 64;
-    constexpr int Q_BYTES = SUB * AT_BM * 128;
-    constexpr int KV_SUB = AT_BN * 128;                    // 8 KB: one 64-column sub-tile of 64 keys
-    constexpr int STAGE_BYTES = 2 * SUB * KV_SUB;
-    constexpr int P_BYTES = AT_BM * 128;                   // [128 rows][64 keys] bf16
-    constexpr uint32_t TMEM_COLS = 256;                    // S0 | S1 | O
-    constexpr uint32_t O_COL = 2 * AT_BN;
+                            int* __restrict__ status) {
+    constexpr int SUB = D / 64;                            // 64-column (128-byte) sub-tiles per row
+    constexpr int Q_BYTES = SUB * AT_BM * 128;             // one row tile of Q
+    constexpr int KV_SUB = AT_BN * 128;                    // one sub-tile of K or V
+    constexpr int STAGE_BYTES = 2 * SUB * KV_SUB;          // K then V
+    constexpr uint32_t TMEM_COLS = 512;                    // S_A0 S_A1 | S_B0 S_B1 | O_A | O_B
+    constexpr uint32_t O_COL = 2 * AT_ROW_TILES * AT_BN;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sq = smem;
-    uint8_t* skv = sq + Q_BYTES;
-    uint8_t* sp = skv + AT_STAGES * STAGE_BYTES;
-    uint64_t* bars = (uint64_t*)(sp + 2 * P_BYTES);
+    uint8_t* skv = sq + AT_ROW_TILES * Q_BYTES;
+    uint64_t* bars = (uint64_t*)(skv + AT_STAGES * STAGE_BYTES);
     uint64_t* q_full = bars;
     uint64_t* kv_full = bars + 1;
     uint64_t* kv_empty = kv_full + AT_STAGES;
-    uint64_t* s_full = kv_empty + AT_STAGES;     // [2]
-    uint64_t* s_free = s_full + 2;               // [2]
-    uint64_t* p_ready = s_free + 2;              // [2]
-    uint64_t* pv_done = p_ready + 2;             // [2]: tile j completes pv_done[j & 1]
-    uint32_t* tmem_slot = (uint32_t*)(pv_done + 2);
+    uint64_t* s_full = kv_empty + AT_STAGES;     // [row tile][2]
+    uint64_t* p_ready = s_full + 4;              // [row tile][2]
+    uint64_t* pv_done = p_ready + 4;             // [row tile][2]: key tile j of a row tile completes [j & 1]
+    uint32_t* tmem_slot = (uint32_t*)(pv_done + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     pdl_trigger();
@@ -71,15 +121,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(q_full, 1);
         for (int i = 0; i < AT_STAGES; ++i) {
             mbar_init(&kv_full[i], 1);
-            mbar_init(&kv_empty[i], 1);
+            mbar_init(&kv_empty[i], AT_ROW_TILES);   // one arrival per issuer
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_free[i], 4);
             mbar_init(&p_ready[i], 4);
+            mbar_init(&pv_done[i], 1);
         }
-        mbar_init(&pv_done[0], 1);
-        mbar_init(&pv_done[1], 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -96,41 +144,60 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     pdl_wait();
     trace_point(TR_ATT_PREFILL);
 
-    // the block's group of tiles (heavy groups first) and head
-    const int* grp = tiles + 4 * AT_GROUP * (gridDim.x - 1 - blockIdx.x);
-    int count = 0;
-    for (int i = 0; i < AT_GROUP; ++i) count += grp[4 * i + 3];
+    // The block's two groups of the list (heavy ones first) and its head.  The second group has to go
+    // on where the first, a full one, ends; the host's list pads every request to whole pairs.
+    const int pair = gridDim.x - 1 - blockIdx.x;
+    const int* grp = tiles + 4 * AT_GROUP * AT_ROW_TILES * pair;
+    int count_a = 0, count_b = 0;
+    for (int i = 0; i < AT_GROUP; ++i) {
+        count_a += grp[4 * i + 3];
+        count_b += grp[4 * (AT_GROUP + i) + 3];
+    }
     const int slot = grp[0], tok0 = grp[1], pos0 = grp[2];
+    if (count_b > 0 && (count_a != AT_BM || grp[4 * AT_GROUP] != slot || grp[4 * AT_GROUP + 1] != tok0 + AT_BM ||
+                        grp[4 * AT_GROUP + 2] != pos0 + AT_BM)) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 6);
+        count_b = 0;
+    }
     const int h = blockIdx.y;
     const int kvh = (int)(((long long)h * K) / H);
     const int* bt = block_table + (size_t)slot * max_blocks;
-    const int pos_last = pos0 + count - 1;
-    const int lo_block = window > 0 ? max(0, pos0 - window + 1) : 0;
-    const int tile0 = lo_block / AT_BN;
-    const int n_tiles = count > 0 ? pos_last / AT_BN + 1 - tile0 : 0;
+    const bool has_b = count_b > 0;
+    const int pos_last_a = pos0 + count_a - 1;
+    const int pos_last = has_b ? pos0 + AT_BM + count_b - 1 : pos_last_a;
+    const int lo_a = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int lo_b = window > 0 ? max(0, pos0 + AT_BM - window + 1) : 0;
+    const int tile0 = lo_a / AT_BN;                                         // the stream's first key tile
+    const int n_stream = count_a > 0 ? pos_last / AT_BN + 1 - tile0 : 0;    // key tiles the block fetches
+    RowTile rt[AT_ROW_TILES];
+    rt[0] = {count_a, pos0, tok0, 0, count_a > 0 ? pos_last_a / AT_BN + 1 - tile0 : 0};
+    const int first_b = has_b ? lo_b / AT_BN - tile0 : 0;
+    rt[1] = {count_b, pos0 + AT_BM, tok0 + AT_BM, first_b, has_b ? n_stream - first_b : 0};
 
     if (warp == 0) {
-        if (lane == 0 && n_tiles > 0) {
+        if (lane == 0 && n_stream > 0) {
             // ------------------------------------------------ producer
-            mbar_expect_tx(q_full, Q_BYTES);
+            mbar_expect_tx(q_full, (uint32_t)(Q_BYTES * (has_b ? 2 : 1)));
+            for (int x = 0; x < (has_b ? 2 : 1); ++x)
 #pragma unroll
-            for (int s = 0; s < SUB; ++s) tma_load_2d(sq + s * AT_BM * 128, &map_q, h * D + 64 * s, tok0, q_full);
+                for (int s = 0; s < SUB; ++s)
+                    tma_load_2d(sq + x * Q_BYTES + s * AT_BM * 128, &map_q, h * D + 64 * s, tok0 + x * AT_BM, q_full);
             const int box_rows = P < AT_BN ? P : AT_BN;
             const int boxes = AT_BN / box_rows;
-            for (int it = 0; it < n_tiles; ++it) {
+            for (int it = 0; it < n_stream; ++it) {
                 const int stage = it % AT_STAGES;
                 if (it >= AT_STAGES && !mbar_wait(&kv_empty[stage], ((it / AT_STAGES) - 1) & 1, abort_flag)) break;
                 const int kbase = (tile0 + it) * AT_BN;
                 int valid = 0;
                 for (int b = 0; b < boxes; ++b) {
                     const int first = kbase + b * box_rows;
-                    valid += (first <= pos_last && first + box_rows - 1 >= lo_block) ? 1 : 0;
+                    valid += (first <= pos_last && first + box_rows - 1 >= lo_a) ? 1 : 0;
                 }
                 mbar_expect_tx(&kv_full[stage], (uint32_t)(valid * box_rows * 128 * SUB * 2));
                 uint8_t* dst = skv + stage * STAGE_BYTES;
                 for (int b = 0; b < boxes; ++b) {
                     const int first = kbase + b * box_rows;
-                    if (!(first <= pos_last && first + box_rows - 1 >= lo_block)) continue;
+                    if (!(first <= pos_last && first + box_rows - 1 >= lo_a)) continue;
                     const int page = bt[first / P];
                     const int row_k = ((page * 2) * K + kvh) * P + first % P;
                     const int row_v = row_k + K * P;
@@ -143,84 +210,120 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
         }
-    } else if (warp == 1) {
-        if (lane == 0 && n_tiles > 0) {
-            // ------------------------------------------------ MMA issuer
+    } else if (warp == 1 || warp == 2) {
+        if (n_stream > 0) {
+            // ------------------------------------------------ MMA issuers, one warp per row tile: while one
+            // waits for its softmax, the other's products keep the tensor cores busy.  The warp runs
+            // together and an elected lane issues (the operands then stay in uniform registers).
+            // A row tile takes the key tiles [first, first + n) of the stream; for the others its
+            // issuer only hands the stage back (after it was filled, so that it cannot run ahead).
+            const int x = warp - 1;
+            const RowTile me = x ? rt[1] : rt[0];
             constexpr uint32_t idesc_qk = umma_idesc(AT_BM, AT_BN);
             constexpr uint32_t idesc_pv = umma_idesc(AT_BM, D, true);
-            bool ok = mbar_wait(q_full, 0, abort_flag);
-            tc_fence_after();
-            for (int it = 0; it <= n_tiles && ok; ++it) {
-                if (it < n_tiles) {
-                    // S(it) = Q K(it)^T into S[it & 1]
-                    const int stage = it % AT_STAGES, b = it & 1;
-                    ok = mbar_wait(&kv_full[stage], (it / AT_STAGES) & 1, abort_flag);
-                    if (ok && it >= 2) ok = mbar_wait(&s_free[b], ((it >> 1) - 1) & 1, abort_flag);
+            const uint32_t qaddr = smem_u32(sq + x * Q_BYTES);
+            const uint32_t s_cols = tmem_base + 2 * x * AT_BN;
+            const uint32_t o_cols = tmem_base + O_COL + x * D;
+            uint64_t* my_s_full = s_full + 2 * x;
+            uint64_t* my_p_ready = p_ready + 2 * x;
+            uint64_t* my_pv_done = pv_done + 2 * x;
+            bool ok = true;
+            auto pass = [&](int from, int to) {   // key tiles that this row tile does not take
+                for (int t = from; t < to && ok; ++t) {
+                    const int stage = t % AT_STAGES;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&kv_full[stage], (t / AT_STAGES) & 1, abort_flag));
+                    if (ok && elect_one()) mbar_arrive(&kv_empty[stage]);
+                    __syncwarp();
+                }
+            };
+            pass(0, me.first);
+            if (me.n > 0) {
+                ok = ok && __all_sync(0xffffffffu, mbar_wait(q_full, 0, abort_flag));
+                tc_fence_after();
+            }
+            for (int j = 0; j <= me.n && ok && me.n > 0; ++j) {
+                if (j < me.n) {
+                    // S(j) = Q K(j)^T into S[j & 1] (which held P(j-2): the product that read it was
+                    // issued before this one)
+                    const int t = me.first + j, stage = t % AT_STAGES;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&kv_full[stage], (t / AT_STAGES) & 1, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t kaddr = smem_u32(skv + stage * STAGE_BYTES);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        umma_bf16(tmem_base + b * AT_BN, umma_desc(smem_u32(sq) + (kk / 4) * AT_BM * 128) + 2 * (kk % 4),
-                                  umma_desc(kaddr + (kk / 4) * KV_SUB) + 2 * (kk % 4), idesc_qk, kk > 0 ? 1u : 0u);
-                    umma_commit(&s_full[b]);
+                        for (int kk = 0; kk < D / 16; ++kk)
+                            umma_bf16(s_cols + (j & 1) * AT_BN, umma_desc(qaddr + (kk / 4) * AT_BM * 128) + 2 * (kk % 4),
+                                      umma_desc(kaddr + (kk / 4) * KV_SUB) + 2 * (kk % 4), idesc_qk, kk > 0 ? 1u : 0u);
+                        umma_commit(&my_s_full[j & 1]);
+                    }
+                    __syncwarp();
                 }
-                if (it >= 1) {
-                    // O += P(it-1) V(it-1)
-                    const int j = it - 1, stage = j % AT_STAGES, b = j & 1;
-                    ok = mbar_wait(&p_ready[b], (j >> 1) & 1, abort_flag);
+                if (j >= 1) {
+                    // O += P(j-1) V(j-1), P from tensor memory (where S(j-1) was)
+                    const int u = j - 1, t = me.first + u, stage = t % AT_STAGES;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&my_p_ready[u & 1], (u >> 1) & 1, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t vaddr = smem_u32(skv + stage * STAGE_BYTES + SUB * KV_SUB);
-                    const uint32_t paddr = smem_u32(sp + b * P_BYTES);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < AT_BN / 16; ++ks)
-                        umma_bf16(tmem_base + O_COL, umma_desc(paddr) + 2 * ks, umma_desc_mn(vaddr + ks * 16 * 128, KV_SUB),
-                                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(&kv_empty[stage]);
-                    umma_commit(&pv_done[b]);
+                        for (int ks = 0; ks < AT_BN / 16; ++ks)
+                            umma_bf16_ts(o_cols, s_cols + (u & 1) * AT_BN + 8 * ks, umma_desc_mn(vaddr + ks * 16 * 128, KV_SUB),
+                                         idesc_pv, (u > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(&my_pv_done[u & 1]);
+                        umma_commit(&kv_empty[stage]);
+                    }
+                    __syncwarp();
                 }
             }
+            pass(me.first + me.n, n_stream);
         }
-    } else if (n_tiles > 0) {
+    } else if (warp >= 4 && (warp >= 8 ? rt[1].n : rt[0].n) > 0) {
         // ---------------------------------------------------- softmax: one thread per query row
+        const int x = (warp - 4) >> 2;
+        const RowTile me = x ? rt[1] : rt[0];
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int pos = pos0 + r;
+        const int pos = me.pos0 + r;
+        uint64_t* my_s_full = s_full + 2 * x;
+        uint64_t* my_p_ready = p_ready + 2 * x;
+        uint64_t* my_pv_done = pv_done + 2 * x;
+        const uint32_t my_s = tmem_base + lane_addr + 2 * x * AT_BN;
+        const uint32_t my_o = tmem_base + lane_addr + O_COL + x * D;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int it = 0; it < n_tiles && ok; ++it) {
+        for (int it = 0; it < me.n && ok; ++it) {
             const int b = it & 1;
-            ok = mbar_wait(&s_full[b], (it >> 1) & 1, abort_flag);
+            ok = mbar_wait(&my_s_full[b], (it >> 1) & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            uint32_t sv[2][32];
-            tmem_ld32(tmem_base + lane_addr + b * AT_BN, sv[0]);
-            tmem_ld32(tmem_base + lane_addr + b * AT_BN + 32, sv[1]);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_free[b]);
-            const int kbase = (tile0 + it) * AT_BN;
+            uint32_t sv[AT_BN];
+            tmem_ld64(my_s + b * AT_BN, sv);
+            const int kbase = (tile0 + me.first + it) * AT_BN;
             // Scores stay as the product left them; the scale goes into the exponent's multiply-add.
             // Only tiles on the diagonal or at a window's edge need the mask (the same for the warp).
-            const int warp_first = pos0 + quarter * 32;
+            const int warp_first = me.pos0 + quarter * 32;
             const bool full_tile = kbase + AT_BN - 1 <= warp_first && (window <= 0 || kbase > warp_first + 31 - window);
-            float mx = -INFINITY;
+            // (four running maxima and, below, two pairs of running sums: independent chains)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (full_tile) {
 #pragma unroll
-                for (int c = 0; c < AT_BN; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
+                for (int c = 0; c < AT_BN; c += 2)
+                    mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
             } else {
 #pragma unroll
                 for (int c = 0; c < AT_BN; ++c) {
                     const int key = kbase + c;
                     const bool vis = key <= pos && (window <= 0 || key > pos - window);
-                    const float x = vis ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
-                    sv[c >> 5][c & 31] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
+                    const float v = vis ? __uint_as_float(sv[c]) : -INFINITY;
+                    sv[c] = __float_as_uint(v);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], v);
                 }
             }
-            mx *= scale_log2;    // the scale is positive: the maximum of the scaled scores
+            // the scale is positive: the maximum of the scaled scores
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // The reference maximum m of the row moves only when the tile's maximum exceeds it by more
             // than 2^8 (or the row had seen no key): probabilities up to 256 are harmless in bfloat16 and
             // in the 32-bit sums, and a row of O that is not rescaled does not have to wait for the
@@ -230,60 +333,74 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float base = m_new == -INFINITY ? 0.f : m_new;   // a row that sees no key yet
             const float corr = move ? fast_exp2(m - base) : 1.f;
             m = m_new;
-            float sum = 0.f;
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             uint32_t pk[AT_BN / 2];
+            const float2 scale2 = make_float2(scale_log2, scale_log2), nbase2 = make_float2(-base, -base);
+            if (full_tile) {
 #pragma unroll
-            for (int c = 0; c < AT_BN; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale_log2, -base));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), scale_log2, -base));
-                sum += p0 + p1;
-                const __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&v);
+                for (int c = 0; c < AT_BN; c += 2) {
+                    const float2 v =
+                        __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, nbase2);
+                    float2 pr;
+                    if ((EXP_FMA_PAIRS >> ((c >> 1) & 7)) & 1) {
+                        pr = exp2_fma(v);
+                    } else {
+                        pr.x = fast_exp2(v.x);
+                        pr.y = fast_exp2(v.y);
+                    }
+                    sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], pr);
+                    pk[c >> 1] = pack_bf16_alu(pr.x, pr.y);
+                }
+            } else {   // (a masked key's -inf stays with ex2)
+#pragma unroll
+                for (int c = 0; c < AT_BN; c += 2) {
+                    const float2 v =
+                        __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, nbase2);
+                    const float2 pr = make_float2(fast_exp2(v.x), fast_exp2(v.y));
+                    sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], pr);
+                    pk[c >> 1] = pack_bf16_alu(pr.x, pr.y);
+                }
             }
-            l = l * corr + sum;
-            // P[b] was read by the product of tile it-2: that one must have completed.  (Two barriers
-            // take turns, so that the one waited for is always the latest that can have completed:
-            // a wait by parity cannot tell a phase from the one two later.)
+            l = l * corr + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
+            // The product of tile it-2 has completed (S(it) was written after it, in the order of
+            // issue).  Looking at its barrier all the same, every time, keeps the parity that a wait
+            // sees at most one phase behind: a wait by parity cannot tell a phase from the one two later.
             if (it >= 2) {
-                ok = mbar_wait(&pv_done[b], ((it >> 1) - 1) & 1, abort_flag);
+                ok = mbar_wait(&my_pv_done[b], ((it >> 1) - 1) & 1, abort_flag);
                 if (!ok) break;
             }
             if (it >= 1 && __any_sync(0xffffffffu, move)) {
                 // O must be rescaled: every product issued so far (up to tile it-1) has to be complete
-                ok = mbar_wait(&pv_done[b ^ 1], ((it - 1) >> 1) & 1, abort_flag);
+                ok = mbar_wait(&my_pv_done[b ^ 1], ((it - 1) >> 1) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < D; c += 32) {
                     uint32_t ov[32];
-                    tmem_ld32(tmem_base + lane_addr + O_COL + c, ov);
+                    tmem_ld32(my_o + c, ov);
 #pragma unroll
                     for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * corr);
-                    tmem_st32(tmem_base + lane_addr + O_COL + c, ov);
+                    tmem_st32(my_o + c, ov);
                 }
             }
-            // P(it): this row's 64 probabilities, 8 chunks of 16 bytes at their swizzled places
-            uint8_t* prow = sp + b * P_BYTES + r * 128;
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
-                    make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P(it): this row's 64 probabilities as 32 columns of pairs, over the scores they came from;
+            // the second product reads its A operand there: no shared memory and no proxy fence on the way
+            tmem_st32(my_s + b * AT_BN, pk);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_ready[b]);
+            if (lane == 0) mbar_arrive(&my_p_ready[b]);
         }
-        if (ok && n_tiles >= 2) ok = mbar_wait(&pv_done[n_tiles & 1], ((n_tiles - 2) >> 1) & 1, abort_flag);
-        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag);
+        if (ok && me.n >= 2) ok = mbar_wait(&my_pv_done[me.n & 1], ((me.n - 2) >> 1) & 1, abort_flag);
+        if (ok) ok = mbar_wait(&my_pv_done[(me.n - 1) & 1], ((me.n - 1) >> 1) & 1, abort_flag);
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * H + h) * D;
+            __nv_bfloat16* dst = out + ((size_t)(me.tok0 + r) * H + h) * D;
 #pragma unroll
             for (int c = 0; c < D; c += 32) {
                 uint32_t ov[32];
-                tmem_ld32(tmem_base + lane_addr + O_COL + c, ov);
-                if (r < count) {
+                tmem_ld32(my_o + c, ov);
+                if (r < me.count) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
                         float y[8];
@@ -326,24 +443,26 @@ template <int D>
 int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* block_table, int max_blocks,
                       const int* tiles, int n_tiles, void* out, int H, int K, int P, int window, float scale, int* status,
                       cudaStream_t stream) {
-    const size_t smem = 1024 + (size_t)(D / 64) * AT_BM * 128 + (size_t)AT_STAGES * 2 * (D / 64) * AT_BN * 128 +
-                        2 * AT_BM * 128 + 256;
+    // (more than half of an SM's shared memory, so that two blocks never share its tensor memory)
+    size_t smem = 1024 + (size_t)AT_ROW_TILES * (D / 64) * AT_BM * 128 +
+                  (size_t)AT_STAGES * 2 * (D / 64) * AT_BN * 128 + 256;
+    if (smem < 120 * 1024) smem = 120 * 1024;
     auto kernel = prefill_attention_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return launch(kernel, dim3(n_tiles / AT_GROUP, H), AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles,
+    return launch(kernel, dim3(n_tiles / (AT_GROUP * AT_ROW_TILES), H), AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles,
                   (__nv_bfloat16*)out, H, K, P, window, scale * 1.4426950408889634f, status);
 }
 
 }  // namespace air
 
-// q [T, H, D] bf16.  tiles: n_tiles entries in groups of 8 per request.  Head size 64 or 128.
+// q [T, H, D] bf16.  tiles: n_tiles entries in groups of 16 per request.  Head size 64 or 128.
 AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, long long pages, const int* block_table,
                                      int max_blocks, const int* tiles, int n_tiles, void* out, int H, int K, int D,
                                      int P, int window, float scale, int* status, cudaStream_t stream) {
     using namespace air;
     if (n_tiles <= 0) return 0;
-    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || n_tiles % AT_GROUP || H > 65535 ||
+    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || n_tiles % (AT_GROUP * AT_ROW_TILES) || H > 65535 ||
         ((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || (D != 64 && D != 128))
         return AIR_ERR_BAD_ARGUMENT;
     CUtensorMap mq, mc;

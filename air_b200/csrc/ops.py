@@ -318,6 +318,7 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
 
 
 TILE_GROUP = 8     # the list of 16-token tiles comes in groups of 8 that belong to one request
+TILE_PAIR = 16     # the tcgen05 kernel takes two groups, one after the other in a request, per block
 
 
 def prefill_attention(q, cache, block_table, tiles, out, window, scale, status=None):
@@ -394,8 +395,8 @@ def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, statu
     _req(out, "out", (torch.bfloat16,), (T, H, d))
     if d not in TC_ATTENTION_HEAD_DIMS:
         raise KernelError(f"prefill_attention_tc takes head sizes {TC_ATTENTION_HEAD_DIMS}, not {d}")
-    if tiles.shape[0] % TILE_GROUP:
-        raise KernelError("prefill_attention_tc: the tile list must come in groups of 8")
+    if tiles.shape[0] % TILE_PAIR:
+        raise KernelError("prefill_attention_tc: the tile list must come in groups of 16 per request")
     if P < 64 and 64 % P:
         raise KernelError(f"prefill_attention_tc: page size {P} does not divide 64")
     _check(_get("air_prefill_attention_tc")(

@@ -49,8 +49,8 @@ class StepContext:
     max_kv_len: int = 0
     all_decode: bool = False
     last_token: Optional[torch.Tensor] = None   # [slots] int32: the device's last choice per request
-    tiles: Optional[torch.Tensor] = None        # [8n, 4] int32: (slot, first token, its position, rows <= 16),
-                                                # in groups of 8 per request, filled up with rows = 0
+    tiles: Optional[torch.Tensor] = None        # [16n, 4] int32: (slot, first token, its position, rows <= 16),
+                                                # in groups of 16 per request, filled up with rows = 0
 
 
 def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepContext:
@@ -74,8 +74,8 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
         tseq.extend([seq.slot] * n)
         for i in range(0, n, 16):
             tiles += [seq.slot, q_start[-1] + i, seq.length + i, min(16, n - i)]
-        while (len(tiles) // 4) % 8:
-            tiles += [seq.slot, 0, 0, 0]          # groups of 8 tiles per request, filled up with empty ones
+        while (len(tiles) // 4) % 16:
+            tiles += [seq.slot, 0, 0, 0]          # groups of 16 tiles per request, filled up with empty ones
         for w in e.want:
             if not (0 <= w < n):
                 raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")

@@ -340,8 +340,8 @@ def tiles_for(lens, q_lens):
     for s, (n, ql) in enumerate(zip(lens, q_lens)):
         for i in range(0, ql, 16):
             tiles.append([s, tok + i, n - ql + i, min(16, ql - i)])
-        while len(tiles) % 8:
-            tiles.append([s, 0, 0, 0])          # groups of 8 tiles per request
+        while len(tiles) % 16:
+            tiles.append([s, 0, 0, 0])          # groups of 16 tiles per request
         tok += ql
     return np.array(tiles, dtype=np.int32)
 
