@@ -17,6 +17,11 @@
 //   EPI_PARTIAL         the k range is split over `splits` blocks; each writes its partial sums to
 //                       C[split][M][N] (float32), which the consumer (norm or rotary kernel) adds up
 //                       in a fixed order.  This keeps all 148 SMs streaming weights when M is small.
+// With many tokens (AR = 256) a block's tile is 256 x 256: two products per k step share the tile of W,
+// each with its own 128 rows of A and its own accumulator (all 512 columns of tensor memory, so the
+// epilogue, by eight warps, is not overlapped with the next tile).  An SM takes 64 bytes a cycle from
+// L2; a 128 x 256 tile needs 48 KB per 512 cycles of products and so waits for its operands a third of
+// the time, a 256 x 256 tile needs 64 KB per 1024 cycles.
 // Rows of A beyond M are not loaded (the box of A is only as tall as needed); the accumulator rows
 // they would feed hold garbage that is never read.  Rows of W beyond N are zero-filled by TMA.
 //
@@ -31,14 +36,14 @@ namespace air {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 192;       // 320 with AR = 256: eight epilogue warps
 
 enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
 
 struct TcArgs {
     void* out;          // EPI_F32/PARTIAL: float [splits][M][N]; EPI_BF16: bf16 [M][N]; EPI_SILU: bf16 [M][N/2]
     int M, N, K;
-    int a_rows;         // height of A's TMA box: 16, 64 or 128
+    int a_rows;         // height of A's TMA box: 16, 64, 128 or 256
     int splits;         // parts of the k range (1 unless EPI_PARTIAL)
     int prefetch;       // further k-tiles of W that a block asks into L2 before its predecessor has ended
     int* status;
@@ -49,12 +54,12 @@ __host__ __device__ constexpr int tc_stages(int bn, int ar) {
     return 196 * 1024 / ((ar + bn) * TC_BK * 2) > 24 ? 24 : 196 * 1024 / ((ar + bn) * TC_BK * 2);
 }
 
-// BN: tile width.  AR: rows of A that are loaded (16, 64 or 128): with few tokens a stage is small,
+// BN: tile width.  AR: rows of A that are loaded (16, 64, 128, or 256 for two row halves): with few tokens a stage is small,
 // so the ring is deep and most of a block's share of W is under way before the predecessor ends.
 // The MMA always reads 128 rows from the stage's address; what lies beyond AR rows is other tiles'
 // data, feeding accumulator rows that are never read.
 template <int BN, int EPI, int AR>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(AR == 256 ? 320 : TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const TcArgs args) {
     constexpr int STAGE_A = AR * TC_BK * 2;
@@ -62,6 +67,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr int STAGES = tc_stages(BN, AR);
     static_assert(STAGES >= 2 && STAGES * STAGE_W >= TC_BM * TC_BK * 2, "the MMA's 128-row read must stay inside");
     constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; a power of two
+    constexpr int HALVES = AR == 256 ? 2 : 1;                  // row halves of a tile, one accumulator each
+    constexpr int NACC = AR == 256 ? 1 : 2;                    // tiles whose accumulators fit at a time
+    constexpr int TILE_M = HALVES * TC_BM;
+    constexpr int EPI_WARPS = 4 * HALVES;
+    static_assert(AR != 256 || BN == 256, "two row halves take all of tensor memory at BN = 256 only");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sa = smem;
@@ -76,7 +86,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tiles = (args.M + TC_BM - 1) / TC_BM;
+    const int m_tiles = (args.M + TILE_M - 1) / TILE_M;
     const int n_tiles = (args.N + BN - 1) / BN;
     const int k_tiles = (args.K + TC_BK - 1) / TC_BK;
     const int k_per = (k_tiles + args.splits - 1) / args.splits;
@@ -89,7 +99,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 4);
+            mbar_init(&acc_empty[i], EPI_WARPS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -115,7 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x) {
                 const int split = tile % args.splits;
                 const int mn = tile / args.splits;
-                const int m0 = (mn % m_tiles) * TC_BM, n0 = (mn / m_tiles) * BN;
+                const int m0 = (mn % m_tiles) * TILE_M, n0 = (mn / m_tiles) * BN;
                 const int k_begin = split * k_per, k_end = min(k_tiles, k_begin + k_per);
                 int kt = k_begin;
                 if (first) {
@@ -147,47 +157,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ------------------------------------------------ MMA issuer
+        {
+            // ------------------------------------------------ MMA issuer.  The warp runs together and
+            // an elected lane issues: the operands then stay in uniform registers.  tcgen05.mma is all
+            // but synchronous for its issuer, so every instruction between two products is time in
+            // which the tensor cores wait; this loop is kept as short as it can be.
             constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+            const uint64_t da0 = umma_desc(smem_u32(sa)), dw0 = umma_desc(smem_u32(sw));
             uint32_t stage = 0, phase = 0, it = 0;
-            for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++it) {
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok && !*abort_flag; tile += gridDim.x, ++it) {
                 const int split = tile % args.splits;
                 const int k_begin = split * k_per, k_end = min(k_tiles, k_begin + k_per);
-                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) break;
+                const uint32_t acc = it % NACC, acc_phase = (it / NACC) & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag));
+                if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_base + acc * BN;
                 for (int kt = k_begin; kt < k_end; ++kt) {
-                    if (!mbar_wait(&full[stage], phase, abort_flag)) break;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag));
+                    if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = umma_desc(smem_u32(sa + stage * STAGE_A));
-                    const uint64_t dw = umma_desc(smem_u32(sw + stage * STAGE_W));
+                    // (the start address field counts 16 bytes)
+                    const uint64_t da = da0 + (uint64_t)(stage * (STAGE_A >> 4));
+                    const uint64_t dw = dw0 + (uint64_t)(stage * (STAGE_W >> 4));
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)
-                        umma_bf16(d, da + 2 * k, dw + 2 * k, idesc, (kt > k_begin || k > 0) ? 1u : 0u);
-                    umma_commit(&empty[stage]);
+                        for (int k = 0; k < TC_BK / 16; ++k)
+#pragma unroll
+                            for (int hf = 0; hf < HALVES; ++hf)
+                                umma_bf16(d + hf * BN, da + (uint64_t)(hf * (TC_BM * TC_BK * 2 >> 4)) + 2 * k, dw + 2 * k, idesc,
+                                          (kt > k_begin || k > 0) ? 1u : 0u);
+                        umma_commit(&empty[stage]);
+                    }
+                    __syncwarp();
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                umma_commit(&acc_full[acc]);
+                if (ok && elect_one()) umma_commit(&acc_full[acc]);
+                __syncwarp();
             }
         }
     } else {
         // ---------------------------------------------------- epilogue: warps 2..5
         pdl_wait();   // nothing is written before the predecessor has completed
         const int quarter = warp & 3;                     // the 32 lanes of tensor memory this warp may read
+        const int half = (warp - 2) >> 2;                 // which 128 rows of the tile (0 unless AR = 256)
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++it) {
             const int split = tile % args.splits;
             const int mn = tile / args.splits;
-            const int m0 = (mn % m_tiles) * TC_BM, n0 = (mn / m_tiles) * BN;
-            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            const int m0 = (mn % m_tiles) * TILE_M + half * TC_BM, n0 = (mn / m_tiles) * BN;
+            const uint32_t acc = it % NACC, acc_phase = (it / NACC) & 1;
             if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
             const bool warp_has_rows = m0 + quarter * 32 < args.M;
             if (warp_has_rows) {
-                const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+                const uint32_t taddr = tmem_base + (acc + half) * BN + ((uint32_t)(quarter * 32) << 16);
                 if (EPI == EPI_SILU) {
                     __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)row * (args.N / 2) + n0 / 2;
 #pragma unroll 1
@@ -286,7 +312,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcArgs&
     auto kernel = gemm_tc_kernel<BN, EPI, AR>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)request);
     if (e != cudaSuccess) return (int)e;
-    return launch(kernel, blocks, TC_THREADS, request, stream, ma, mw, args);
+    return launch(kernel, blocks, AR == 256 ? 320 : TC_THREADS, request, stream, ma, mw, args);
 }
 
 template <int BN, int AR>
@@ -309,6 +335,9 @@ static int dispatch_rows(int a_rows, int epi, const CUtensorMap& ma, const CUten
     switch (a_rows) {
         case 16: return dispatch_epi<BN, 16>(epi, ma, mw, args, blocks, stream);
         case 64: return dispatch_epi<BN, 64>(epi, ma, mw, args, blocks, stream);
+        case 256:
+            if constexpr (BN == 256) return dispatch_epi<BN, 256>(epi, ma, mw, args, blocks, stream);
+            return AIR_ERR_BAD_ARGUMENT;
         default: return dispatch_epi<BN, 128>(epi, ma, mw, args, blocks, stream);
     }
 }
@@ -328,17 +357,20 @@ AIR_API int air_gemm_tc(const void* a, const void* w, void* out, int M, int N, i
     if (epi != EPI_SILU && N % 4) return AIR_ERR_BAD_ARGUMENT;
     const int k_tiles = (K + TC_BK - 1) / TC_BK;
     if (splits > k_tiles) return AIR_ERR_BAD_ARGUMENT;
-    const int a_rows = M > 64 ? 128 : (M > 16 ? 64 : 16);
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (max_blocks > 0 && max_blocks < sms) sms = max_blocks;
+    // (256-row tiles where they still leave three quarters of the SMs a tile each)
+    const bool tall = bn == 256 && M >= 512 && (long long)((M + 255) / 256) * ((N + 255) / 256) * 4 >= 3ll * sms;
+    const int a_rows = tall ? 256 : M > 64 ? 128 : (M > 16 ? 64 : 16);
+    const int tile_m = a_rows == 256 ? 256 : TC_BM;
     CUtensorMap ma, mw;
     int rc = make_map(&ma, a, M, K, a_rows);
     if (rc) return rc;
     rc = make_map(&mw, w, N, K, bn);
     if (rc) return rc;
-    int sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (max_blocks > 0 && max_blocks < sms) sms = max_blocks;
-    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn) * splits;
+    const long long tiles = (long long)((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn) * splits;
     const int blocks = (int)(tiles < sms ? tiles : sms);
     // With few rows the product is a stream of weights: while the predecessor runs, each block asks
     // its share of up to 40 MB of them into L2 (the L2 holds 126 MB).

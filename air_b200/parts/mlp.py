@@ -19,8 +19,9 @@ class SwiGLU(FeedForward):
     the input is read once: blocks of gate rows and of up rows for the same outputs in turn (the
     block is the largest of 128, 64, 32 that divides `intermediate`, else all of it), so that a
     tile of the product holds both factors of its outputs and the tcgen05 kernel can apply the
-    activation in its epilogue; with many rows the library's product is followed by the
-    activation kernel, which reads the same arrangement."""
+    activation in its epilogue, for few rows and for many; where that kernel does not apply (32-bit
+    weights, an odd width) the library's product is followed by the activation kernel, which reads
+    the same arrangement."""
 
     def tensor_specs(self):
         e, i, p = self.spec["hidden"], self.spec["intermediate"], self.prefix
@@ -47,7 +48,9 @@ class SwiGLU(FeedForward):
         self.down = Linear(tensors[p + "down_proj.weight"], rt.status)
 
     def forward(self, x, ctx):
-        if self.gate_up.gate_up_block and self.gate_up.small(x):
+        if self.gate_up.gate_up_block and self.gate_up.tc_ok and x.dtype == torch.bfloat16:
+            # few rows or many: the tcgen05 product with SiLU(gate) * up in its epilogue (the 2 I wide
+            # intermediate is never written)
             act = self.gate_up.silu_mul(x)
         else:
             gu = self.gate_up(x, torch.float32 if self.rt.is_fp32 else self.rt.dtype)

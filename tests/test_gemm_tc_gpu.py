@@ -26,7 +26,7 @@ def close(got, want, K):
 
 @pytest.mark.parametrize("bn", [32, 64, 128, 256])
 @pytest.mark.parametrize("M,N,K", [(8, 64, 64), (1, 256, 128), (16, 512, 192), (37, 388, 352), (128, 256, 256),
-                                   (200, 1000, 1000), (64, 4608, 3584)])
+                                   (200, 1000, 1000), (64, 4608, 3584), (600, 1000, 1000), (515, 260, 136)])
 def test_float32_output(bn, M, N, K):
     o = ops()
     a, w, want = inputs(M, N, K, M + N)
@@ -52,7 +52,7 @@ def test_partial_sums_over_k(bn, splits):
 
 
 @pytest.mark.parametrize("bn", [64, 128, 256])
-@pytest.mark.parametrize("M", [3, 130])
+@pytest.mark.parametrize("M", [3, 130, 700])      # (from 512 rows on, 256-wide tiles take 256 rows: two accumulators)
 def test_silu_epilogue_with_interleaved_gate_and_up(bn, M):
     o = ops()
     I, K = 3 * bn, 320
