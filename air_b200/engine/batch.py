@@ -14,6 +14,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -56,26 +57,31 @@ class StepContext:
 def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepContext:
     """Packs the batch.  `cache` is the CacheManager; every request is open and has its pages
     reserved for this step."""
-    P = cache.page_tokens
-    ids: List[int] = []
-    pos: List[int] = []
-    tseq: List[int] = []
+    ids: List[np.ndarray] = []
+    pos: List[np.ndarray] = []
+    tseq: List[np.ndarray] = []
+    tiles: List[np.ndarray] = []
     q_start = [0]
     kv_len: List[int] = []
     slots: List[int] = []
     rows: List[int] = []
     row_slots: List[int] = []
-    tiles: List[int] = []
-    for s, e in enumerate(entries):
+    for e in entries:
         seq = cache.sequences[e.request]
         n = len(e.tokens)
-        ids.extend(int(t) if int(t) >= 0 else -(seq.slot + 1) for t in e.tokens)
-        pos.extend(range(seq.length, seq.length + n))
-        tseq.extend([seq.slot] * n)
-        for i in range(0, n, 16):
-            tiles += [seq.slot, q_start[-1] + i, seq.length + i, min(16, n - i)]
-        while (len(tiles) // 4) % 16:
-            tiles += [seq.slot, 0, 0, 0]          # groups of 16 tiles per request, filled up with empty ones
+        t = np.asarray(e.tokens, dtype=np.int64)
+        ids.append(np.where(t >= 0, t, -(seq.slot + 1)).astype(np.int32))
+        pos.append(np.arange(seq.length, seq.length + n, dtype=np.int32))
+        tseq.append(np.full(n, seq.slot, dtype=np.int32))
+        # 16-token tiles in groups of 16 per request, filled up with empty ones
+        count = -(-n // 16)
+        tile = np.zeros((-(-count // 16) * 16, 4), dtype=np.int32)
+        tile[:, 0] = seq.slot
+        first = np.arange(count, dtype=np.int32) * 16
+        tile[:count, 1] = q_start[-1] + first
+        tile[:count, 2] = seq.length + first
+        tile[:count, 3] = np.minimum(16, n - first)
+        tiles.append(tile.reshape(-1))
         for w in e.want:
             if not (0 <= w < n):
                 raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
@@ -84,16 +90,19 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
         q_start.append(q_start[-1] + n)
         kv_len.append(seq.length + n)
         slots.append(seq.slot)
-    T, S = len(ids), len(entries)
+    T, S = q_start[-1], len(entries)
     cache.flush_tables()
-    sections = [ids, pos, tseq, q_start, kv_len, slots, rows, row_slots, tiles]
+    empty = np.zeros(0, dtype=np.int32)
+    sections = [np.concatenate(x) if x else empty for x in (ids, pos, tseq)]
+    sections += [np.asarray(x, dtype=np.int32) for x in (q_start, kv_len, slots, rows, row_slots)]
+    sections.append(np.concatenate(tiles) if tiles else empty)
     total = sum(len(x) for x in sections)
     host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
+    view = host.numpy()
     offset = 0
     spans = []
     for x in sections:
-        if x:
-            host[offset:offset + len(x)] = torch.tensor(x, dtype=torch.int32)
+        view[offset:offset + len(x)] = x
         spans.append((offset, len(x)))
         offset += len(x)
     dev = host.to(device, non_blocking=True)

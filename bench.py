@@ -159,6 +159,35 @@ def decode_timeline(engine, requests, torch, Entry, LAST):
         print(f"  {name:18s} {n:4d} launches {us:9.1f} us  {100 * us / total:5.1f} %  {us / n:7.1f} us each")
 
 
+def prefill_timeline(engine, prompt, torch, Entry):
+    """Spans between the starts of this package's kernels in one prefill step.  A library product has
+    no trace point: its time is part of the span of the kernel before it (add_rmsnorm before the QKV
+    and gate/up products, prefill_attention before the output product, and so on)."""
+    import collections
+    from air_b200.csrc import ops
+    buf = torch.zeros(1 + 2 * 16384, dtype=torch.int64, device=engine.rt.device)
+    ops.set_trace(buf)
+    engine.step([Entry("p", prompt, [len(prompt) - 1])])
+    torch.cuda.synchronize()
+    ops.set_trace(None)
+    engine.finish("p")
+    b = buf.cpu().tolist()
+    events = sorted((b[2 + 2 * i], b[1 + 2 * i]) for i in range(min(b[0], 16384)) if b[1 + 2 * i] < 100)
+    spans = collections.defaultdict(lambda: [0, 0.0])
+    order = []
+    for (t0, k), (t1, k1) in zip(events, events[1:]):
+        key = f"{ops.TRACE_NAMES[k]} -> {ops.TRACE_NAMES[k1]}"
+        if key not in spans:
+            order.append(key)
+        spans[key][0] += 1
+        spans[key][1] += (t1 - t0) / 1e3
+    total = (events[-1][0] - events[0][0]) / 1e3
+    print(f"prefill step of {len(prompt)} tokens: {total:.1f} us from embedding to sampling, {len(events)} traced kernels")
+    for key in order:
+        n, us = spans[key]
+        print(f"  {key:42s} {n:4d} times {us:9.1f} us  {100 * us / total:5.1f} %  {us / n:7.1f} us each")
+
+
 def decode_e2e(engine, requests, steps, warmup, torch):
     """The same through InferenceService.run_cycle, host tokens in and out every step."""
     from air_b200.engine.service import InferenceService, SchedulerConfig
@@ -204,7 +233,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling the decode step alone")
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
-    ap.add_argument("--timeline", action="store_true", help="also print the kernels' spans inside the decode graph")
+    ap.add_argument("--timeline", action="store_true", help="also print the kernels' spans inside the decode graph and in the prefill step")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -268,6 +297,8 @@ def main():
         times.append(s.elapsed_time(e))
         engine.finish("p")
     pre_ms = min(times[1:]) if times else float("nan")
+    if args.timeline and not args.skip_prefill:
+        prefill_timeline(engine, prompt, torch, Entry)
     L, E, I, V = len(engine.model.spec.order), mc.hidden_size, mc.intermediate_size, mc.vocab_size
     H, K, d = mc.num_attention_heads, mc.num_key_value_heads, mc.head_dim
     gemm_params = L * (E * (H + 2 * K) * d + H * d * E + 3 * E * I)
