@@ -25,7 +25,7 @@
 // tiles, q, out, cache, block_table, window as in attention_prefill.cu; the list pads every request
 // to whole pairs of groups.  Head size 64 or 128.
 // Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 7.  A list
-// whose second group does not go on where the first ends flags *status = 6 (that group is skipped).
+// whose second group does not go on where the first ends flags *status = 8 (that group is skipped).
 #include "common.cuh"
 #include "tma.cuh"
 #include "umma.cuh"
@@ -156,7 +156,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int slot = grp[0], tok0 = grp[1], pos0 = grp[2];
     if (count_b > 0 && (count_a != AT_BM || grp[4 * AT_GROUP] != slot || grp[4 * AT_GROUP + 1] != tok0 + AT_BM ||
                         grp[4 * AT_GROUP + 2] != pos0 + AT_BM)) {
-        if (threadIdx.x == 0 && status) atomicExch(status, 6);
+        if (threadIdx.x == 0 && status) atomicExch(status, 8);
         count_b = 0;
     }
     const int h = blockIdx.y;

@@ -258,7 +258,12 @@ class Engine:
             raise StepError({1: "a token outside the vocabulary reached the embedding kernel",
                              2: "a token was to be written to a page that its request does not hold",
                              3: "non-finite logits",
-                             4: "a wait inside the matrix-product kernel ran out"}.get(code, f"device status {code}"))
+                             4: "a wait inside the matrix-product kernel ran out",
+                             5: "a wait inside the decode attention kernel ran out",
+                             6: "a wait inside the prefill attention kernel ran out",
+                             7: "a wait inside the tcgen05 prefill attention kernel ran out",
+                             8: "the tile list of the tcgen05 prefill attention kernel is not in pairs of one request",
+                             }.get(code, f"device status {code}"))
 
 
 def _device(name) -> torch.device:

@@ -108,7 +108,7 @@ class HostSampler:
         if c.top_k != 0 and c.top_k < order.size:
             order = order[: c.top_k]
         kept = weights[order].tolist()
-        total = math.fsum([]) + sum(kept, 0.0)
+        total = sum(kept, 0.0)
         if not (total > 0.0) or not math.isfinite(total):
             raise FloatingPointError("sampling distribution is non-finite")
         if c.top_p < 1.0:
