@@ -32,6 +32,8 @@ _SIGNATURES = {
     "air_prefill_attention": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "air_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_gemm_tc_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                          c_void_p],
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                  c_void_p],
@@ -348,11 +350,12 @@ def prefill_attention(q, cache, block_table, tiles, out, window, scale, status=N
 EPI_F32, EPI_BF16, EPI_SILU, EPI_PARTIAL = 0, 1, 2, 3
 
 
-def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0):
+def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_as_m=False):
     """bfloat16 product a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (see gemm_tc.cu).
     epi EPI_F32: out float32 [M,N]; EPI_BF16: out bfloat16 [M,N]; EPI_SILU: w holds gate and up rows
     interleaved in blocks of bn/2, out bfloat16 [M,N/2] = silu(gate)*up; EPI_PARTIAL: out float32
-    [splits,M,N] partial sums over parts of k."""
+    [splits,M,N] partial sums over parts of k.  With up to 64 rows and bn 128 or 256 the product runs with the
+    weights as the M side of the instruction (gemm_tc_small.cu) unless force_rows_as_m."""
     M, K = a.shape
     N = w.shape[0]
     _req(a, "a", (torch.bfloat16,))
@@ -375,9 +378,22 @@ def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0):
         raise KernelError(f"gemm_tc: epilogue {epi}")
     if epi != EPI_SILU and N % 4:
         raise KernelError(f"gemm_tc: N = {N} must be a multiple of 4")
+    if small_rows(M, N, bn, epi) and not force_rows_as_m:
+        # few tokens: the weights are the M side of the instruction (gemm_tc_small.cu)
+        _check(_get("air_gemm_tc_small")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits,
+                                         max_blocks, _ptr(status), _stream()), "gemm_tc_small")
+        return out
     _check(_get("air_gemm_tc")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits, max_blocks,
                                _ptr(status), _stream()), "gemm_tc")
     return out
+
+
+def small_rows(M: int, N: int, bn: int, epi: int) -> bool:
+    """Whether gemm_tc takes the kernel with the weights as the M side: up to 64 tokens, tiles of 128 or
+    256 rows of W; with the activation, gate and up rows in blocks of 128."""
+    if M > 64 or bn not in (128, 256):
+        return False
+    return epi != EPI_SILU or (bn == 256 and N % 256 == 0)
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)

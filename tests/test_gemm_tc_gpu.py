@@ -1,5 +1,6 @@
-"""The tcgen05 matrix product against a float64 product of the same bfloat16 inputs: every
-tile width, every epilogue, sizes with tails in M, N and K, one token to thousands."""
+"""The tcgen05 matrix products against a float64 product of the same bfloat16 inputs: every
+tile width, every epilogue, sizes with tails in M, N and K, one token to thousands; with few
+tokens both kernels (tokens as the M side of the instruction, weights as the M side)."""
 import numpy as np
 import pytest
 import torch
@@ -26,25 +27,33 @@ def close(got, want, K):
 
 @pytest.mark.parametrize("bn", [32, 64, 128, 256])
 @pytest.mark.parametrize("M,N,K", [(8, 64, 64), (1, 256, 128), (16, 512, 192), (37, 388, 352), (128, 256, 256),
-                                   (200, 1000, 1000), (64, 4608, 3584), (600, 1000, 1000), (515, 260, 136)])
-def test_float32_output(bn, M, N, K):
+                                   (200, 1000, 1000), (64, 4608, 3584), (600, 1000, 1000), (515, 260, 136),
+                                   (17, 520, 328), (33, 300, 72), (64, 132, 4096)])
+@pytest.mark.parametrize("rows_as_m", [False, True])
+def test_float32_output(bn, M, N, K, rows_as_m):
     o = ops()
+    if rows_as_m and not o.small_rows(M, N, bn, o.EPI_F32):
+        pytest.skip("one kernel only for this size")
     a, w, want = inputs(M, N, K, M + N)
     out = torch.full((M, N), 9.0, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    o.gemm_tc(a, w, out, bn, o.EPI_F32, status=status)
+    o.gemm_tc(a, w, out, bn, o.EPI_F32, status=status, force_rows_as_m=rows_as_m)
     assert status.item() == 0
     assert close(out, want, K)
 
 
-@pytest.mark.parametrize("bn,splits", [(32, 2), (64, 3), (128, 5), (64, 1)])
-def test_partial_sums_over_k(bn, splits):
+@pytest.mark.parametrize("bn,splits", [(32, 2), (64, 3), (128, 5), (64, 1), (256, 4)])
+@pytest.mark.parametrize("M", [8, 40])
+@pytest.mark.parametrize("rows_as_m", [False, True])
+def test_partial_sums_over_k(bn, splits, M, rows_as_m):
     o = ops()
-    M, N, K = 8, 3584, 18944 // 8
+    N, K = 3584, 18944 // 8
+    if rows_as_m and not o.small_rows(M, N, bn, o.EPI_PARTIAL):
+        pytest.skip("one kernel only for this size")
     a, w, want = inputs(M, N, K, splits)
     out = torch.zeros(splits, M, N, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    o.gemm_tc(a, w, out, bn, o.EPI_PARTIAL, splits=splits, status=status)
+    o.gemm_tc(a, w, out, bn, o.EPI_PARTIAL, splits=splits, status=status, force_rows_as_m=rows_as_m)
     assert status.item() == 0
     assert close(out.sum(0), want, K)
     if splits > 1:
@@ -52,9 +61,12 @@ def test_partial_sums_over_k(bn, splits):
 
 
 @pytest.mark.parametrize("bn", [64, 128, 256])
-@pytest.mark.parametrize("M", [3, 130, 700])      # (from 512 rows on, 256-wide tiles take 256 rows: two accumulators)
-def test_silu_epilogue_with_interleaved_gate_and_up(bn, M):
+@pytest.mark.parametrize("M", [3, 20, 64, 130, 700])   # (from 512 rows on, 256-wide tiles take 256 rows)
+@pytest.mark.parametrize("rows_as_m", [False, True])
+def test_silu_epilogue_with_interleaved_gate_and_up(bn, M, rows_as_m):
     o = ops()
+    if rows_as_m and not o.small_rows(M, 6 * bn, bn, o.EPI_SILU):
+        pytest.skip("one kernel only for this size")
     I, K = 3 * bn, 320
     g = torch.Generator().manual_seed(bn + M)
     a = torch.randn(M, K, generator=g).to(torch.bfloat16)
@@ -63,7 +75,7 @@ def test_silu_epilogue_with_interleaved_gate_and_up(bn, M):
     half = bn // 2
     w = torch.cat([torch.cat([gate[i:i + half], up[i:i + half]]) for i in range(0, I, half)])
     out = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
-    o.gemm_tc(a.cuda(), w.cuda(), out, bn, o.EPI_SILU)
+    o.gemm_tc(a.cuda(), w.cuda(), out, bn, o.EPI_SILU, force_rows_as_m=rows_as_m)
     gd, ud = a.double() @ gate.double().T, a.double() @ up.double().T
     want = gd / (1 + torch.exp(-gd)) * ud
     assert float((out.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
@@ -82,6 +94,19 @@ def test_bfloat16_output_and_many_tiles():
     out2 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     o.gemm_tc(a, w, out2, 128, o.EPI_BF16, status=status, max_blocks=7)
     assert status.item() == 0 and torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("M", [5, 48])
+def test_bfloat16_output_with_few_tokens(M):
+    o = ops()
+    N, K = 1000, 520
+    a, w, want = inputs(M, N, K, M)
+    for bn in (128, 256):
+        out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        o.gemm_tc(a, w, out, bn, o.EPI_BF16, status=status, max_blocks=3)
+        assert status.item() == 0
+        assert float((out.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
 
 
 def test_refusals():
