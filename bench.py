@@ -157,6 +157,15 @@ def decode_timeline(engine, requests, torch, Entry, LAST):
     print(f"decode step inside the graph: {total:.1f} us from embedding to sampling, {len(step)} kernels")
     for name, (n, us) in sorted(spans.items(), key=lambda x: -x[1][1]):
         print(f"  {name:18s} {n:4d} launches {us:9.1f} us  {100 * us / total:5.1f} %  {us / n:7.1f} us each")
+    # one layer from the middle of the step, kernel by kernel
+    names = [ops.TRACE_NAMES[k] for _, k in step]
+    for i in range(len(step) // 2, len(step) - 10):
+        if names[i:i + 3] == ["add_rmsnorm", "gemm_tc", "qkv_rope_store"]:
+            j = next((j for j in range(i + 3, len(step) - 1) if names[j:j + 3] == names[i:i + 3]), None)
+            if j is not None:
+                print("  one layer (us): " + " | ".join(f"{names[q]} {(step[q + 1][0] - step[q][0]) / 1e3:.1f}"
+                                                       for q in range(i, j)))
+            break
 
 
 def prefill_timeline(engine, prompt, torch, Entry):
