@@ -99,6 +99,8 @@ class DecodeGraph:
 
 
 class Engine:
+    feeds_back_tokens = True     # Entry(request, [LAST_SAMPLED]) takes the device's last choice for the request
+
     def __init__(self, model: Model, config: EngineConfig, model_config=None):
         self.model, self.config, self.model_config = model, config, model_config
         self.rt = model.rt

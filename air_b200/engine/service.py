@@ -9,6 +9,14 @@ next admission.  Differences: there is no worker thread (the caller's thread run
 no tokenizer (prompts are token ids), and every cycle is ONE engine step that holds the
 cycle's prompt portions and decoded tokens together.
 
+Decoding one step ahead.  While every active request is decoding and its tokens are chosen on the
+device, a cycle launches the next step BEFORE it reads the tokens of the step in flight: the
+device feeds each request's last choice back by itself (`LAST_SAMPLED`), so the host's reading,
+bookkeeping and scheduling run while the device computes, instead of between its steps.  A request
+that ends by its token count is known beforehand and left out; one that ends by an end-of-sequence
+token has one more token computed, which is dropped.  Tokens reach the caller one cycle later.
+`SchedulerConfig.decode_ahead = False` gives the strictly alternating loop.
+
 When pages run out.  With `reserve_worst_case` (the default, AIR's policy) an admitted request
 has its worst case reserved, so a step can never run out of pages.  Without it, requests are
 admitted while their next portion fits, and a step may find the pool empty: the engine then
@@ -27,7 +35,7 @@ from typing import Deque, Dict, Hashable, List, Optional, Sequence
 
 from ..cache.manager import OutOfPages
 from ..sampling.sampler import GenerationConfig, HostSampler, SamplingConfig
-from .batch import Entry
+from .batch import LAST_SAMPLED, Entry
 from .scheduler import (CapacityScheduler, MicrobatchScheduler, SchedulableSequence, WorkPhase)
 
 
@@ -41,6 +49,7 @@ class SchedulerConfig:
     prefill_quantum_tokens: int = 512
     kv_page_tokens: int = 64
     reserve_worst_case: bool = True
+    decode_ahead: bool = True      # (not in AIR) launch a decode step before the one in flight is read
 
 
 @dataclass
@@ -92,6 +101,14 @@ class _WorkItem:
         return WorkPhase.prefill if self.prompt_position < len(self.prompt) else WorkPhase.decode
 
 
+@dataclass
+class _InFlight:
+    """A decode step that has been launched and whose tokens are on their way to the host."""
+    items: List[_WorkItem]          # in the order of the rows
+    tokens: object                  # pinned int32 tensor [rows]
+    event: object                   # recorded after the copy
+
+
 class InferenceService:
     def __init__(self, engine, scheduler: Optional[SchedulerConfig] = None):
         self.engine = engine
@@ -109,6 +126,8 @@ class InferenceService:
         self.cycles = 0
         self.preemptions = 0
         self.last_batch = None
+        self._inflight: Optional[_InFlight] = None
+        self._pinned = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -221,6 +240,11 @@ class InferenceService:
         """Admission, one micro-batch, one engine step, sampling, finishing.  Returns False when
         there was nothing to run."""
         self._admit()
+        if self._inflight is not None:
+            done = self._inflight
+            self._inflight = self._launch_ahead(done)
+            self._complete(done)
+            return True
         if not self.active:
             return False
         candidates = []
@@ -245,12 +269,79 @@ class InferenceService:
                     return True
         self.last_batch = batch
         self.cycles += 1
+        if self._may_decode_ahead(entries):
+            items = self._items(entries)
+            self._inflight = self._read_later(items, self._choose_on_device(items, logits))
+            return True
         self._accept(entries, logits)
+        self._retire()
+        return True
+
+    # ------------------------------------------------------------------ decoding one step ahead
+    def _items(self, entries: Sequence[Entry]) -> List[_WorkItem]:
+        by_id = {i.request_id: i for i in self.active}
+        return [by_id[e.request] for e in entries]
+
+    def _may_decode_ahead(self, entries: Sequence[Entry]) -> bool:
+        """The step that has just run is a plain decode step of every active request, with tokens
+        chosen on the device, on an engine that feeds them back by itself."""
+        if not (self.config.decode_ahead and getattr(self.engine, "feeds_back_tokens", False)):
+            return False
+        if len(entries) != len(self.active):
+            return False
+        return all(i.phase == WorkPhase.decode and i.generation.sampling.on_device for i in self.active) and \
+            all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+
+    def _choose_on_device(self, items: Sequence[_WorkItem], logits):
+        temps = [float(i.generation.sampling.temperature) for i in items]
+        if any(t > 0.0 for t in temps):
+            uniforms = [i.sampler.next_uniform() if t > 0.0 else 0.0 for i, t in zip(items, temps)]
+            return self.engine.sample(logits, temps, uniforms)
+        return self.engine.sample(logits)
+
+    def _read_later(self, items: List[_WorkItem], ids) -> _InFlight:
+        import torch
+        n = len(items)
+        ring = self._pinned.setdefault(n, [[torch.empty(n, dtype=torch.int32).pin_memory(), torch.cuda.Event()]
+                                           for _ in range(2)])
+        ring.append(ring.pop(0))
+        host, event = ring[0]
+        host.copy_(ids, non_blocking=True)
+        event.record()
+        return _InFlight(list(items), host, event)
+
+    def _launch_ahead(self, flying: _InFlight) -> Optional[_InFlight]:
+        """The step after the one in flight, for the requests that go on whatever it brings; None
+        when that step needs what the one in flight will tell (a new request, pages running out)."""
+        if len(self.active) != len(flying.items) or any(i.done for i in flying.items):
+            return None
+        items = [i for i in flying.items if len(i.generated) + 1 < i.generation.max_new_tokens]
+        if not items or len(items) > self.config.token_budget_per_cycle:
+            return None
+        entries = [Entry(i.request_id, [LAST_SAMPLED], [0]) for i in items]
+        try:
+            logits = self.engine.step(entries)
+        except OutOfPages:
+            return None
+        self.cycles += 1
+        return self._read_later(items, self._choose_on_device(items, logits))
+
+    def _complete(self, flying: _InFlight) -> None:
+        """Reads the tokens of a launched step and accepts them.  (A request that ended meanwhile, by
+        an end-of-sequence token of the step before, had one token too many computed: dropped.)"""
+        flying.event.synchronize()
+        chosen = flying.tokens.tolist()
+        now = time.perf_counter()
+        for item, token in zip(flying.items, chosen):
+            if not item.done:
+                self._accept_token(item, int(token), now)
+        self._retire()
+
+    def _retire(self) -> None:
         for item in [i for i in self.active if i.done]:
             self.active.remove(item)
             self.engine.finish(item.request_id)
             self._finish(item)
-        return True
 
     def _preempt_youngest(self) -> int:
         """Takes the active request that was admitted last out of the engine and puts it back

@@ -1,6 +1,7 @@
 """Generation through the Python entry point and the command line against the plain
 implementation: greedy tokens, the first tokens of a sequence, long decoding, temperature
 sampling, several requests at once."""
+import dataclasses
 import json
 import os
 import subprocess
@@ -115,6 +116,42 @@ def test_temperature_sampling_mixed_batch_of_config_b():
         p = torch.softmax(torch.tensor(logits).double() / 0.8, -1)
         chosen = p[torch.arange(len(r.tokens)), torch.tensor(r.tokens)]
         assert float(chosen.min()) > 1e-5
+
+
+def test_decoding_one_step_ahead_gives_the_same_tokens():
+    """The loop that launches a step before it reads the one in flight against the strictly
+    alternating loop: requests that end by their token count at different times, one that ends by an
+    end-of-sequence token (its id is set to a token that greedy decoding reaches), temperature
+    sampling, a request that arrives while others decode, and all pages back at the end."""
+    from air_b200 import GenerationConfig, SamplingConfig
+    folder = util.model_folder("B")
+    cfg, tensors = util.plain_model(folder)
+    prompts = [util.tokens_for("B", n, 300 + n) for n in (3, 9, 17, 4)]
+    greedy = plain.greedy_generate(cfg, tensors, prompts[0], 12)
+    eos = greedy[6]
+    stop_at = greedy.index(eos) + 1
+
+    def run(ahead):
+        svc = service("B", "float32", decode_ahead=ahead, max_active_requests=3)
+        svc.engine.model.spec = dataclasses.replace(svc.engine.model.spec, eos_token_id=eos)
+        reqs = [(prompts[0], GenerationConfig(max_new_tokens=12, stop_on_eos=True)),
+                (prompts[1], GenerationConfig(max_new_tokens=5, stop_on_eos=False)),
+                (prompts[2], GenerationConfig(max_new_tokens=9, stop_on_eos=False,
+                                              sampling=SamplingConfig(temperature=0.7, seed=5))),
+                (prompts[3], GenerationConfig(max_new_tokens=7, stop_on_eos=False))]   # waits for a free place
+        out = svc.generate_cohort(reqs)
+        assert svc.engine.cache.free_pages() == svc.engine.cache.num_pages
+        svc.engine.check_status()
+        return out, svc.cycles
+
+    ahead, cycles_ahead = run(True)
+    plainly, cycles = run(False)
+    assert [r.tokens for r in ahead] == [r.tokens for r in plainly]
+    assert [r.hit_eos for r in ahead] == [True, False, False, False]
+    assert ahead[0].tokens == greedy[:stop_at]
+    assert ahead[1].tokens == plain.greedy_generate(cfg, tensors, prompts[1], 5)
+    assert ahead[3].tokens == plain.greedy_generate(cfg, tensors, prompts[3], 7)
+    assert cycles_ahead <= cycles + 3      # at most a dropped step per request that stops by itself
 
 
 def test_host_sampler_path_with_top_k_and_top_p():
