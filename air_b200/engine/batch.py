@@ -52,6 +52,8 @@ class StepContext:
     last_token: Optional[torch.Tensor] = None   # [slots] int32: the device's last choice per request
     tiles: Optional[torch.Tensor] = None        # [16n, 4] int32: (slot, first token, its position, rows <= 16),
                                                 # in groups of 16 per request, filled up with rows = 0
+    decode_prefix: int = 0                      # so many leading tokens are single next tokens of their requests;
+                                                # the tiles cover the tokens after them
 
 
 def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepContext:
@@ -66,15 +68,18 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
     slots: List[int] = []
     rows: List[int] = []
     row_slots: List[int] = []
-    for e in entries:
+    decode_prefix = 0
+    for index, e in enumerate(entries):
         seq = cache.sequences[e.request]
         n = len(e.tokens)
+        if n == 1 and decode_prefix == index:
+            decode_prefix += 1      # single tokens at the head of the batch go to the decode kernels
         t = np.asarray(e.tokens, dtype=np.int64)
         ids.append(np.where(t >= 0, t, -(seq.slot + 1)).astype(np.int32))
         pos.append(np.arange(seq.length, seq.length + n, dtype=np.int32))
         tseq.append(np.full(n, seq.slot, dtype=np.int32))
         # 16-token tiles in groups of 16 per request, filled up with empty ones
-        count = -(-n // 16)
+        count = 0 if decode_prefix == index + 1 else -(-n // 16)
         tile = np.zeros((-(-count // 16) * 16, 4), dtype=np.int32)
         tile[:, 0] = seq.slot
         first = np.arange(count, dtype=np.int32) * 16
@@ -117,4 +122,4 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
         block_tables=list(cache.tables), tiles=cut(8).view(-1, 4),
         status=status, q_start_host=q_start, kv_len_host=kv_len, slots_host=slots,
         max_q_len=max((len(e.tokens) for e in entries), default=0), max_kv_len=max(kv_len, default=0),
-        all_decode=all(len(e.tokens) == 1 for e in entries))
+        all_decode=all(len(e.tokens) == 1 for e in entries), decode_prefix=decode_prefix)

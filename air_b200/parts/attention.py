@@ -100,7 +100,16 @@ class Attention(Mixer):
             ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.tiles is not None
               and (pages.kv.shape[3] >= 64 or 64 % pages.kv.shape[3] == 0)):
-            if d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
+            # a mixed step: the single next tokens at the head of the batch take the decode kernel (a row
+            # tile of 128 queries for one token would read its request's whole context for one row), the
+            # prompt portions the tile kernels
+            n = ctx.decode_prefix
+            if n:
+                ops.decode_attention(q[:n], pages.kv, bt, ctx.token_seq[:n], ctx.positions[:n], out[:n], self.window,
+                                     self.scale)
+            if ctx.tiles.shape[0] == 0:
+                pass
+            elif d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
                 ops.prefill_attention_tc(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
             else:
                 ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)

@@ -1,7 +1,8 @@
 """Trace replay on the GPU against the plain implementation: the same requests whole, with
 the last 32 tokens one by one, in portions of changing size down to two tokens, and mixed with
 other requests in a pool so small that pages are used again; in float32 and in bfloat16; for
-the tiny configurations A and B (which differ in every size and option) and W (a window)."""
+the tiny configurations A and B (which differ in every size and option) and W (a window), and for K
+and L, whose heads of 64 and 128 take the tensor-core attention kernels in bfloat16 (L with a window)."""
 import json
 import os
 import tempfile
@@ -13,7 +14,8 @@ import util
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": (1, 7, 33, 97, 150), "B": (5, 40, 97, 131, 64, 18), "W": (3, 50, 97, 140)}
+LENGTHS = {"A": (1, 7, 33, 97, 150), "B": (5, 40, 97, 131, 64, 18), "W": (3, 50, 97, 140),
+           "K": (2, 65, 150, 300), "L": (9, 129, 64, 270)}
 
 
 def streams_for(name):
@@ -21,7 +23,7 @@ def streams_for(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "K", "L"])
 def test_whole(name, dtype):
     folder, streams = util.model_folder(name), streams_for(name)
     steps = util.trace_whole(streams)
@@ -30,7 +32,7 @@ def test_whole(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "K", "L"])
 def test_bulk_then_last_32_one_by_one(name, dtype):
     folder, streams = util.model_folder(name), streams_for(name)
     steps = util.trace_bulk_tail(streams, tail=32)
@@ -39,7 +41,7 @@ def test_bulk_then_last_32_one_by_one(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "K", "L"])
 def test_portions_of_changing_size(name, dtype):
     folder, streams = util.model_folder(name), streams_for(name)
     steps = util.trace_portions(streams)
@@ -49,7 +51,7 @@ def test_portions_of_changing_size(name, dtype):
 
 @pytest.mark.parametrize("page", [16, 64])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "K", "L"])
 def test_mixed_with_pages_used_again(name, dtype, page):
     folder = util.model_folder(name)
     lengths = LENGTHS[name] + (120, 2, 77, 101, 64, 129)
@@ -62,7 +64,7 @@ def test_mixed_with_pages_used_again(name, dtype, page):
         assert group.pool.takes > group.pool.num_pages, "pages were used again"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "K", "L"])
 def test_float32_does_not_depend_on_the_cut(name):
     """In float32 every kernel reduces in an order that depends only on the position, so the
     four ways of cutting give the same bits."""
@@ -73,6 +75,27 @@ def test_float32_does_not_depend_on_the_cut(name):
     assert a.keys() == b.keys() == c.keys()
     for k in a:
         assert np.array_equal(a[k], b[k]) and np.array_equal(a[k], c[k]), k
+
+
+@pytest.mark.parametrize("name", ["K", "L"])
+def test_bfloat16_heads_of_64_and_128_take_the_tensor_core_kernels(name):
+    """The kernels' own trace says which attention kernels a mixed replay ran: the decode kernel and the
+    tile kernel, never the 32-bit one."""
+    import torch
+    from air_b200.csrc import ops
+    folder, streams = util.model_folder(name), streams_for(name)
+    steps = util.trace_mixed(streams, seed=1, live=3)
+    buf = torch.zeros(1 + 2 * 16384, dtype=torch.int64, device="cuda")
+    ops.set_trace(buf)
+    try:
+        got, _ = util.replay(folder, "bfloat16", steps, max_tokens=util.peak_tokens(steps), page_tokens=64)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_trace(None)
+    util.check_against_plain(got, folder, streams, "bfloat16")
+    b = buf.cpu().tolist()
+    ran = {ops.TRACE_NAMES.get(b[1 + 2 * i] % 100) for i in range(min(b[0], 16384))}
+    assert {"decode_attention", "prefill_attention"} <= ran and "attention_ref" not in ran
 
 
 def test_trace_run_program_writes_files_and_done_lines():

@@ -24,7 +24,16 @@ TINY_W = dict(BASE, num_hidden_layers=3, hidden_size=96, num_attention_heads=3, 
               intermediate_size=208, vocab_size=301, max_position_embeddings=512, rope_theta=50000.0,
               rms_norm_eps=3e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=40,
               max_window_layers=1)
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "W": (TINY_W, 2)}
+# Two more with the head sizes that the tensor-core attention kernels take (64 and 128; the three above
+# have 16 and 32 and run the 32-bit attention kernel in both precisions), one of them with a window.
+TINY_K = dict(BASE, num_hidden_layers=2, hidden_size=128, num_attention_heads=2, num_key_value_heads=1,
+              intermediate_size=160, vocab_size=199, max_position_embeddings=512, rope_theta=30000.0,
+              rms_norm_eps=2e-6, tie_word_embeddings=True, use_sliding_window=False)
+TINY_L = dict(BASE, num_hidden_layers=2, hidden_size=384, num_attention_heads=3, num_key_value_heads=3,
+              intermediate_size=256, vocab_size=230, max_position_embeddings=512, rope_theta=1e5,
+              rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=70,
+              max_window_layers=1)
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "W": (TINY_W, 2), "K": (TINY_K, 3), "L": (TINY_L, 4)}
 
 _folders = {}
 _tmp = []
