@@ -116,7 +116,8 @@ class Engine:
         self.graph_kernel_launches = 0
         self.graphs = {}
         self.use_graphs = config.cuda_graphs and all(
-            getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+            getattr(b.mixer, "graph_safe", False) and getattr(b.feed_forward, "graph_safe", False)
+            for b in model.blocks)
 
     # ------------------------------------------------------------------ construction
     @classmethod

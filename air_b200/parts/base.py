@@ -100,5 +100,7 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    graph_safe: bool = False    # as for Mixer: nothing in forward() reads the batch or a result on the host
+
     def forward(self, x, ctx):
         raise NotImplementedError

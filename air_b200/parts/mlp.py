@@ -23,6 +23,8 @@ class SwiGLU(FeedForward):
     weights, an odd width) the library's product is followed by the activation kernel, which reads
     the same arrangement."""
 
+    graph_safe = True
+
     def tensor_specs(self):
         e, i, p = self.spec["hidden"], self.spec["intermediate"], self.prefix
         return [TensorSpec(p + "gate_proj.weight", (i, e)), TensorSpec(p + "up_proj.weight", (i, e)),

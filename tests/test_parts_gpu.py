@@ -246,3 +246,156 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps():
     assert torch.allclose(torch.cat(got_b), whole_b, atol=1e-5, rtol=1e-5)
     assert not torch.allclose(whole_a[5], whole_a[6])
     engine.cache.check()
+
+
+# ------------------------------------------------------------------ toy parts of the other kinds
+def test_a_toy_position_encoding_registers_and_rotates():
+    """Another position encoding, defined here: positions divided by a factor, and only the first half
+    of a head rotated.  The attention part takes it by name and its kernel reads the table."""
+    from air_b200.cache.manager import CacheManager
+    from air_b200.parts import PositionEncoding, PartSpec, register_position_encoding
+    from air_b200.parts.attention import Attention
+
+    @register_position_encoding("toy_scaled_partial")
+    class ToyScaledPartial(PositionEncoding):
+        def load(self, tensors, rt):
+            super().load(tensors, rt)
+            rot, n = int(self.spec["rotary_dim"]), int(self.spec["max_positions"])
+            self.rotary_dim = rot
+            i = torch.arange(rot // 2, dtype=torch.float64)
+            angle = (torch.arange(n, dtype=torch.float64) / self.spec["factor"])[:, None] * \
+                (1.0 / torch.pow(torch.tensor(float(self.spec["theta"]), dtype=torch.float64), 2.0 * i / rot))[None, :]
+            self._table = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).float().to(rt.device)
+
+        def table(self):
+            return self._table
+
+    hidden, heads, kv, d, rot, T, theta, factor = 80, 4, 2, 32, 16, 37, 500.0, 4.0
+    spec = PartSpec("attention", {"hidden": hidden, "heads": heads, "kv_heads": kv, "head_dim": d, "qkv_bias": True,
+                                  "window": None,
+                                  "position": PartSpec("toy_scaled_partial", {"rotary_dim": rot, "theta": theta,
+                                                                              "factor": factor, "max_positions": 64})})
+    part = Attention(spec, "a.")
+    assert type(part.position).__name__ == "ToyScaledPartial"
+    t = tensors_for(part, 7, "float32")
+    part.load({k: v.cuda() for k, v in t.items()}, runtime("float32"))
+    cache = CacheManager([part.cache_needs()], 16, 8, 2, dtype=torch.float32, device="cuda")
+    x = torch.randn(T, hidden, generator=torch.Generator().manual_seed(4))
+    outs, i = [], 0
+    for n in (30, 1, 6):
+        ctx, entries = context_for(cache, [("r", [0] * n, [])])
+        y = part.forward(x[i:i + n].cuda(), ctx, cache.views(0), True)
+        outs.append((y.sum(0) if y.dim() == 3 else y).cpu())
+        cache.commit("r", n)
+        i += n
+    out = torch.cat(outs).numpy()
+    w, xn = as_np(t), x.numpy()
+    pos = np.arange(T) / factor
+
+    def rotate(v):       # the first `rot` elements of every head, the rest as they are
+        return np.concatenate([plain.rope(v[..., :rot], pos, theta), v[..., rot:]], axis=-1)
+
+    q = rotate(plain.linear(xn, w["a.q_proj.weight"], w["a.q_proj.bias"]).reshape(T, heads, d))
+    k = rotate(plain.linear(xn, w["a.k_proj.weight"], w["a.k_proj.bias"]).reshape(T, kv, d))
+    v = plain.linear(xn, w["a.v_proj.weight"], w["a.v_proj.bias"]).reshape(T, kv, d)
+    want = plain.linear(plain.attention(q, k, v).reshape(T, heads * d), w["a.o_proj.weight"])
+    assert np.abs(out - want).max() < 1e-5 * np.abs(want).max()
+
+
+def test_a_toy_feed_forward_with_routing_registers_builds_and_steps():
+    """A feed-forward that sends every token to one of its experts (router logits in 32-bit, the
+    largest wins), defined here together with an architecture that has it in every second layer.  It is
+    registered, given random weights and stepped through the engine whole, in portions and beside
+    another request; the part alone equals a loop over tokens."""
+    from dataclasses import dataclass
+    from air_b200.engine.batch import Entry
+    from air_b200.engine.engine import Engine, EngineConfig
+    from air_b200.parts import (FeedForward, PartSpec, BlockSpec, ModelSpec, RunStep, register_feed_forward,
+                                register_architecture)
+    from air_b200.weights.loader import TensorSpec
+
+    @register_feed_forward("toy_routed")
+    class ToyRouted(FeedForward):
+        def tensor_specs(self):
+            e, i, n, p = self.spec["hidden"], self.spec["intermediate"], self.spec["experts"], self.prefix
+            specs = [TensorSpec(p + "router.weight", (n, e))]
+            for x in range(n):
+                specs += [TensorSpec(p + f"experts.{x}.gate.weight", (i, e)), TensorSpec(p + f"experts.{x}.up.weight", (i, e)),
+                          TensorSpec(p + f"experts.{x}.down.weight", (e, i))]
+            return specs
+
+        def load(self, tensors, rt):
+            super().load(tensors, rt)
+            p = self.prefix
+            self.router = tensors[p + "router.weight"].float()
+            self.experts = [tuple(tensors[p + f"experts.{x}.{n}.weight"].float() for n in ("gate", "up", "down"))
+                            for x in range(self.spec["experts"])]
+            self.chosen = []
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            choice = (xf @ self.router.T).argmax(-1)
+            self.chosen.append(choice.cpu())
+            out = torch.zeros_like(xf)
+            for e, (g, u, d) in enumerate(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = xf[rows]
+                    out[rows] = (torch.nn.functional.silu(h @ g.T) * (h @ u.T)) @ d.T
+            return out
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        architecture: str
+        hidden_size: int
+        vocab_size: int
+        num_hidden_layers: int
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["architectures"][0], d["hidden_size"], d["vocab_size"], d["num_hidden_layers"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "hidden_size": self.hidden_size,
+                    "vocab_size": self.vocab_size, "num_hidden_layers": self.num_hidden_layers}
+
+    def toy_spec(c):
+        norm = PartSpec("rms", {"size": c.hidden_size, "eps": 1e-5})
+        att = PartSpec("attention", {"hidden": c.hidden_size, "heads": 3, "kv_heads": 3, "head_dim": 16,
+                                     "qkv_bias": True, "window": None,
+                                     "position": PartSpec("rope_half", {"rotary_dim": 16, "theta": 100.0,
+                                                                        "max_positions": 128})})
+        dense = PartSpec("swiglu", {"hidden": c.hidden_size, "intermediate": 40})
+        routed = PartSpec("toy_routed", {"hidden": c.hidden_size, "intermediate": 24, "experts": 3})
+        layers = tuple(BlockSpec("pre_norm", f"model.layers.{i}.", att, routed if i % 2 else dense, norm, norm)
+                       for i in range(c.num_hidden_layers))
+        return ModelSpec(c.architecture, c.hidden_size, c.vocab_size, 128, layers,
+                         tuple(RunStep(i) for i in range(c.num_hidden_layers)), norm, "model.embed_tokens.weight",
+                         "model.norm.", "lm_head.weight")
+
+    register_architecture("ToyRoutedForCausalLM", ToyConfig, toy_spec)
+    cfg = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 48, "vocab_size": 90, "num_hidden_layers": 4}
+    engine = Engine.from_random(cfg, seed=8, config=EngineConfig(dtype=torch.float32, page_tokens=16,
+                                                                 max_tokens=256, max_requests=3))
+    assert [type(b.feed_forward).__name__ for b in engine.model.blocks] == ["SwiGLU", "ToyRouted", "SwiGLU", "ToyRouted"]
+    a = [t % 90 for t in util.tokens_for("A", 45, 3)]
+    b = [t % 90 for t in util.tokens_for("A", 21, 4)]
+    whole_a = engine.step([Entry("wa", a, range(45))]).cpu()
+    whole_b = engine.step([Entry("wb", b, range(21))]).cpu()
+    engine.finish("wa"); engine.finish("wb")
+    routed = engine.model.blocks[1].feed_forward
+    assert len(torch.cat(routed.chosen).unique()) > 1, "the tokens went to more than one expert"
+    got_a = [engine.step([Entry("a", a[:20], range(20))]).cpu()]
+    out = engine.step([Entry("b", b[:19], range(19)), Entry("a", a[20:22], range(2))]).cpu()
+    got_b = [out[:19]]; got_a.append(out[19:])
+    out = engine.step([Entry("b", b[19:20], [0]), Entry("a", a[22:], range(23))]).cpu()
+    got_b.append(out[:1]); got_a.append(out[1:])
+    got_b.append(engine.step([Entry("b", b[20:], [0])]).cpu())
+    assert torch.allclose(torch.cat(got_a), whole_a, atol=1e-5, rtol=1e-5)
+    assert torch.allclose(torch.cat(got_b), whole_b, atol=1e-5, rtol=1e-5)
+    # the part alone: one token at a time gives what the batch gave
+    x = torch.randn(9, 48, generator=torch.Generator().manual_seed(1)).cuda()
+    together = routed.forward(x, None)
+    alone = torch.cat([routed.forward(x[i:i + 1], None) for i in range(9)])
+    assert torch.allclose(together, alone, atol=1e-6)
+    engine.cache.check()
