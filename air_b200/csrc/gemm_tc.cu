@@ -1,12 +1,13 @@
 // bfloat16 matrix product on the fifth-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T with
-// float32 accumulation in tensor memory, for prefill (M in the thousands) and decode (M of a
-// few tokens) alike, with the epilogues that the decoder wants fused in.
+// float32 accumulation in tensor memory and the TOKENS as the M side of the instruction, with the
+// epilogues that the decoder wants fused in.  It serves any number of rows; for up to 64 tokens and
+// tiles of 128 or 256 rows of W the engine takes gemm_tc_small.cu (the weights as the M side) instead.
 //
 // One persistent block per SM, 192 threads:
 //   warp 0   one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
 //            of an up to 128 x 64 tile of A and a BN x 64 tile of W per stage into a ring of stages;
-//   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M = 128, N = BN, K = 16, four per
-//            stage) into one of two accumulators and commits the stage's "empty" barrier;
+//   warp 1   allocates tensor memory; an elected lane issues tcgen05.mma (M = 128, N = BN, K = 16, four
+//            per stage) into one of two accumulators and commits the stage's "empty" barrier;
 //   warps 2-5  read a finished accumulator with tcgen05.ld (each thread one row = one token, 32
 //            columns at a time) and write the result, while the next tile is being multiplied.
 // A thread of the epilogue holds a whole row of the tile, so what the decoder does per token and
