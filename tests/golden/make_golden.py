@@ -96,7 +96,8 @@ def air_name(name):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("AIR_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("AIR_REFERENCE_DIR"), required="AIR_REFERENCE_DIR" not in os.environ,
+                    help="a checkout of EmersonDowell/AIR (or set AIR_REFERENCE_DIR)")
     ap.add_argument("--out", default=os.path.join(HERE, "air_reference_tiny.npz"))
     args = ap.parse_args()
     ref = args.reference
