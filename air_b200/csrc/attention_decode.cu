@@ -253,28 +253,47 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 }
 
 // Merges the splits of one (token, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+// The kernel is a chain of latencies, so a thread asks for eight splits' values at once (and for the
+// token's slot beside them: a padding token has its place in the buffers too) and folds them into a
+// running maximum, sum and value, in the order of the splits.
 template <int D>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       const int* __restrict__ token_seq, __nv_bfloat16* __restrict__ out, int H,
                                       int splits) {
     pdl_enter(TR_ATT_COMBINE);
     const int t = blockIdx.y, h = blockIdx.x;
-    if (token_seq[t] < 0) return;
     const size_t base = ((size_t)t * H + h) * splits;
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
-    float ll = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float m = part_ml[(base + s) * 2];
-        ll += m == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(m - mm);
-    }
+    const int slot = token_seq[t];
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float m = part_ml[(base + s) * 2];
-            if (m != -INFINITY) acc += part_o[(base + s) * D + col] * exp2f(m - mm);
+        float mm = -INFINITY, ll = 0.f, acc = 0.f;
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float m[8], l[8], o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool in = s0 + i < splits;
+                const float2 ml = in ? *reinterpret_cast<const float2*>(part_ml + (base + s0 + i) * 2)
+                                     : make_float2(-INFINITY, 0.f);
+                m[i] = ml.x;
+                l[i] = ml.y;
+                o[i] = in ? part_o[(base + s0 + i) * D + col] : 0.f;
+            }
+            float top = mm;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) top = fmaxf(top, m[i]);
+            if (top == -INFINITY) continue;            // nothing seen yet
+            const float keep = exp2f(mm - top);         // 0 while mm is -inf
+            ll *= keep;
+            acc *= keep;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (m[i] == -INFINITY) continue;        // (its values are not looked at: they may be anything)
+                const float w = exp2f(m[i] - top);
+                ll += l[i] * w;
+                acc += o[i] * w;
+            }
+            mm = top;
         }
-        out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll);
+        if (slot >= 0) out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll);
     }
 }
 

@@ -53,9 +53,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
 }
 
 // The same with four elements per access, for E % 4 == 0.  `parts` tensors of delta's shape,
-// one after the other, are summed in order (the partial sums of a split product).
+// one after the other, are summed in order (the partial sums of a split product).  With few rows the
+// kernel is a chain of latencies, so a thread first issues all of its loads (up to ELT_PARTS parts at
+// once) and the block is as wide as the row (one access per thread where E <= 4096).
+constexpr int ELT_PARTS = 8;
 template <typename TD, typename TW, typename TO>
-__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restrict__ delta, int parts,
+__global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restrict__ delta, int parts,
                                         size_t part_stride, const TW* __restrict__ w, TO* __restrict__ out,
                                         const int* __restrict__ rows, int E, float eps) {
     __shared__ float scratch[32];
@@ -64,14 +67,26 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restr
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * E;
     float ss = 0.f;
+    const int i0 = threadIdx.x * 4;
+    float w0[4] = {0.f, 0.f, 0.f, 0.f};
+    if (i0 < E) load4(w + i0, w0);          // the weights of the thread's first elements, asked for with the rest
     for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
-        float x[4];
+        float x[4], d[ELT_PARTS][4];
         load4(h + src + i, x);
-        for (int p = 0; p < parts; ++p) {
-            float d[4];
-            load4(delta + p * part_stride + src + i, d);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) x[j] += d[j];
+        for (int p = 0; p < ELT_PARTS; ++p)
+            if (p < parts) load4(delta + p * part_stride + src + i, d[p]);
+#pragma unroll
+        for (int p = 0; p < ELT_PARTS; ++p)
+            if (p < parts) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] += d[p][j];
+            }
+        for (int p = ELT_PARTS; p < parts; ++p) {
+            float e[4];
+            load4(delta + p * part_stride + src + i, e);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] += e[j];
         }
         store4(xrow + i, x);
 #pragma unroll
@@ -82,7 +97,12 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restr
     for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
         float x[4], wv[4], y[4];
         load4(xrow + i, x);
-        load4(w + i, wv);
+        if (i == i0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = w0[j];
+        } else {
+            load4(w + i, wv);
+        }
         if (!rows && parts > 0) store4(h + src + i, x);
 #pragma unroll
         for (int j = 0; j < 4; ++j) y[j] = x[j] * scale * wv[j];
@@ -175,8 +195,10 @@ __global__ void qkv_rope_store_kernel(const TI* __restrict__ qkv, const TB* __re
 
 // The same for full rotation (rot == d) with four pairs per thread.  `parts` tensors of qkv's
 // shape are summed in order (the partial sums of a split product).
+constexpr int ROPE_PARTS = 4;      // partial sums that a thread asks for ahead of the index chain
+constexpr int ROPE_THREADS = 640;
 template <typename TI, typename TB, typename TO>
-__global__ void qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts, size_t part_stride,
+__global__ void __launch_bounds__(ROPE_THREADS) qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts, size_t part_stride,
                                            const TB* __restrict__ bias, const float* __restrict__ table,
                                            const int* __restrict__ positions, const int* __restrict__ token_seq,
                                            const int* __restrict__ block_table, int max_blocks,
@@ -184,11 +206,26 @@ __global__ void qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts
                                            int H, int K, int d, int P, int write_kv, int* status) {
     pdl_enter(TR_ROPE);
     const int t = blockIdx.x;
-    const int slot = token_seq[t];
-    if (slot < 0) return;
-    const int pos = positions[t];
     const int width = (H + 2 * K) * d, half = d / 2;
     const TI* in = qkv + (size_t)t * width;
+    const int per_head = half / 4;
+    const int heads = write_kv ? H + 2 * K : H;
+    // With few tokens the kernel is a chain of latencies: the first item's partial sums are asked
+    // for before the token's slot, position and page are looked up (a padding token's row exists too).
+    float pa[ROPE_PARTS][4], pb[ROPE_PARTS][4];
+    const int first = threadIdx.x;
+    if (first < heads * per_head) {
+        const int base = (first / per_head) * d, j = (first % per_head) * 4;
+#pragma unroll
+        for (int p = 0; p < ROPE_PARTS; ++p)
+            if (p < parts) {
+                load4(in + p * part_stride + base + j, pa[p]);
+                load4(in + p * part_stride + base + half + j, pb[p]);
+            }
+    }
+    const int slot = token_seq[t];
+    const int pos = positions[t];
+    if (slot < 0) return;
     TO* kdst = nullptr;
     TO* vdst = nullptr;
     if (write_kv) {
@@ -200,16 +237,25 @@ __global__ void qkv_rope_store_vec4_kernel(const TI* __restrict__ qkv, int parts
             vdst = kdst + (size_t)K * P * d;
         }
     }
-    const int per_head = half / 4;
-    const int heads = write_kv ? H + 2 * K : H;
     const float* cs = table + (size_t)pos * d;
     for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
         const int head = idx / per_head, j = (idx % per_head) * 4;
         const int base = head * d;
         float a[4], b[4];
-        load4(in + base + j, a);
-        load4(in + base + half + j, b);
-        for (int p = 1; p < parts; ++p) {
+        if (idx == first) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[e] = pa[0][e]; b[e] = pb[0][e]; }
+#pragma unroll
+            for (int p = 1; p < ROPE_PARTS; ++p)
+                if (p < parts) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { a[e] += pa[p][e]; b[e] += pb[p][e]; }
+                }
+        } else {
+            load4(in + base + j, a);
+            load4(in + base + half + j, b);
+        }
+        for (int p = (idx == first ? ROPE_PARTS : 1); p < parts; ++p) {
             float x[4], y[4];
             load4(in + p * part_stride + base + j, x);
             load4(in + p * part_stride + base + half + j, y);
@@ -341,9 +387,10 @@ AIR_API int air_add_rmsnorm(float* h, const void* delta, int delta_dtype, int pa
     const size_t smem = (size_t)E * sizeof(float);
     if (smem > 200 * 1024 || parts < 0) return AIR_ERR_BAD_ARGUMENT;
     if (!delta) parts = 0;
-    const int threads = E >= 2048 ? 512 : 256;
+    int threads = E >= 2048 ? 512 : 256;
     AIR_DISPATCH(delta_dtype, TD, AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
         if (E % 4 == 0) {
+            if (R <= 64) threads = min(1024, max(128, (E / 4 + 31) / 32 * 32));   // few rows: one access per thread
             auto kernel = add_rmsnorm_vec4_kernel<TD, TW, TO>;
             if (smem > 48 * 1024)
                 cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -370,7 +417,10 @@ AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, int parts, const v
     if (rot < 0 || rot > d || (rot & 1) || parts < 1) return AIR_ERR_BAD_ARGUMENT;
     AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(bias_dtype, TB, AIR_DISPATCH(out_dtype, TO, {
         if (rot == d && d % 8 == 0) {
-            return launch(qkv_rope_store_vec4_kernel<TI, TB, TO>, T, 256, 0, stream, (const TI*)qkv, parts,
+            // few tokens: one item per thread, so that every load of the block is in flight at once
+            const int items = (write_kv ? H + 2 * K : H) * (d / 8);
+            const int threads = T <= 64 ? min(ROPE_THREADS, max(128, (items + 31) / 32 * 32)) : 256;
+            return launch(qkv_rope_store_vec4_kernel<TI, TB, TO>, T, threads, 0, stream, (const TI*)qkv, parts,
                           (size_t)T * (H + 2 * K) * d, (const TB*)bias, table, positions, token_seq, block_table,
                           max_blocks, (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
         } else {
