@@ -4,6 +4,7 @@ scheduler and trace replay all call it.
 """
 from __future__ import annotations
 
+import gc
 import os
 from dataclasses import dataclass
 from typing import Hashable, List, Optional, Sequence
@@ -78,8 +79,17 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = ops.launches
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = engine.model.forward(self.ctx, engine.cache)
+        # No garbage collection while the stream is capturing: freeing another engine's graphs, events or
+        # pinned memory then is a CUDA call that is not permitted during capture and would spoil it.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = engine.model.forward(self.ctx, engine.cache)
+        finally:
+            if collecting:
+                gc.enable()
         self.kernels = ops.launches - before
 
     def run(self, ids, positions, slots) -> torch.Tensor:
