@@ -110,6 +110,44 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restric
     }
 }
 
+// The same for many rows (a prompt portion), where the rows hide each other's latencies and a thread
+// that holds fewer registers lets more of them run at a time.
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_vec4_many_kernel(float* __restrict__ h, const TD* __restrict__ delta, int parts,
+                                        size_t part_stride, const TW* __restrict__ w, TO* __restrict__ out,
+                                        const int* __restrict__ rows, int E, float eps) {
+    __shared__ float scratch[32];
+    extern __shared__ float xrow[];
+    pdl_enter(TR_NORM);
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+        float x[4];
+        load4(h + src + i, x);
+        for (int p = 0; p < parts; ++p) {
+            float d[4];
+            load4(delta + p * part_stride + src + i, d);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] += d[j];
+        }
+        store4(xrow + i, x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
+    }
+    const float total = block_sum(ss, scratch);
+    const float scale = rsqrtf(total / (float)E + eps);
+    for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+        float x[4], wv[4], y[4];
+        load4(xrow + i, x);
+        load4(w + i, wv);
+        if (!rows && parts > 0) store4(h + src + i, x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[j] = x[j] * scale * wv[j];
+        store4(out + (size_t)r * E + i, y);
+    }
+}
+
 // ---------------------------------------------------------------- bias + rotary + cache write
 // qkv [T, (H + 2K) d] is the output of the fused projection.  For every token: add the
 // bias, rotate the heads of q and k with the table's cos/sin of the token's position
@@ -290,6 +328,76 @@ __global__ void __launch_bounds__(ROPE_THREADS) qkv_rope_store_vec4_kernel(const
     }
 }
 
+// The same for many tokens (a prompt portion): plain loops, fewer registers, 256 threads.
+template <typename TI, typename TB, typename TO>
+__global__ void qkv_rope_store_vec4_many_kernel(const TI* __restrict__ qkv, int parts, size_t part_stride,
+                                           const TB* __restrict__ bias, const float* __restrict__ table,
+                                           const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                           const int* __restrict__ block_table, int max_blocks,
+                                           TO* __restrict__ q_out, TO* __restrict__ cache,
+                                           int H, int K, int d, int P, int write_kv, int* status) {
+    pdl_enter(TR_ROPE);
+    const int t = blockIdx.x;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    const int width = (H + 2 * K) * d, half = d / 2;
+    const TI* in = qkv + (size_t)t * width;
+    TO* kdst = nullptr;
+    TO* vdst = nullptr;
+    if (write_kv) {
+        const int page = block_table[(size_t)slot * max_blocks + pos / P];
+        if (page < 0) {
+            if (threadIdx.x == 0 && status) atomicExch(status, 2);
+        } else {
+            kdst = cache + ((size_t)page * 2 * K * P + (size_t)(pos % P)) * d;
+            vdst = kdst + (size_t)K * P * d;
+        }
+    }
+    const int per_head = half / 4;
+    const int heads = write_kv ? H + 2 * K : H;
+    const float* cs = table + (size_t)pos * d;
+    for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
+        const int head = idx / per_head, j = (idx % per_head) * 4;
+        const int base = head * d;
+        float a[4], b[4];
+        load4(in + base + j, a);
+        load4(in + base + half + j, b);
+        for (int p = 1; p < parts; ++p) {
+            float x[4], y[4];
+            load4(in + p * part_stride + base + j, x);
+            load4(in + p * part_stride + base + half + j, y);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
+        }
+        if (bias) {
+            float x[4], y[4];
+            load4(bias + base + j, x);
+            load4(bias + base + half + j, y);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
+        }
+        const bool is_v = head >= H + K;
+        if (!is_v) {
+            float c[4], sn[4];
+            load4(cs + j, c);
+            load4(cs + half + j, sn);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float ra = a[e] * c[e] - b[e] * sn[e], rb = a[e] * sn[e] + b[e] * c[e];
+                a[e] = ra;
+                b[e] = rb;
+            }
+        }
+        TO* dst;
+        if (head < H) dst = q_out + ((size_t)t * H + head) * d;
+        else if (!kdst) continue;
+        else dst = (is_v ? vdst + (size_t)(head - H - K) * P * d : kdst + (size_t)(head - H) * P * d);
+        store4(dst + j, a);
+        store4(dst + half + j, b);
+    }
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 // in [T, 2I]: blocks of `block` gate columns and `block` up columns in turn (block = I: all gate
 // columns, then all up columns).  out [T, I].
@@ -391,7 +499,7 @@ AIR_API int air_add_rmsnorm(float* h, const void* delta, int delta_dtype, int pa
     AIR_DISPATCH(delta_dtype, TD, AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
         if (E % 4 == 0) {
             if (R <= 64) threads = min(1024, max(128, (E / 4 + 31) / 32 * 32));   // few rows: one access per thread
-            auto kernel = add_rmsnorm_vec4_kernel<TD, TW, TO>;
+            auto kernel = R <= 64 ? add_rmsnorm_vec4_kernel<TD, TW, TO> : add_rmsnorm_vec4_many_kernel<TD, TW, TO>;
             if (smem > 48 * 1024)
                 cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             return launch(kernel, R, threads, smem, stream, h, (const TD*)delta, parts, (size_t)h_rows * E,
@@ -420,7 +528,8 @@ AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, int parts, const v
             // few tokens: one item per thread, so that every load of the block is in flight at once
             const int items = (write_kv ? H + 2 * K : H) * (d / 8);
             const int threads = T <= 64 ? min(ROPE_THREADS, max(128, (items + 31) / 32 * 32)) : 256;
-            return launch(qkv_rope_store_vec4_kernel<TI, TB, TO>, T, threads, 0, stream, (const TI*)qkv, parts,
+            return launch(T <= 64 ? qkv_rope_store_vec4_kernel<TI, TB, TO> : qkv_rope_store_vec4_many_kernel<TI, TB, TO>, T,
+                          threads, 0, stream, (const TI*)qkv, parts,
                           (size_t)T * (H + 2 * K) * d, (const TB*)bias, table, positions, token_seq, block_table,
                           max_blocks, (TO*)q_out, (TO*)cache, H, K, d, P, write_kv, status);
         } else {
