@@ -357,7 +357,9 @@ AIR_API int air_gemm_tc(const void* a, const void* w, void* out, int M, int N, i
     if (epi == EPI_SILU && (bn < 64 || N % bn || (N / 2) % 8)) return AIR_ERR_BAD_ARGUMENT;
     if (epi != EPI_SILU && N % 4) return AIR_ERR_BAD_ARGUMENT;
     const int k_tiles = (K + TC_BK - 1) / TC_BK;
-    if (splits > k_tiles) return AIR_ERR_BAD_ARGUMENT;
+    // every part of the k range must hold at least one k-tile (an accumulator that no product wrote is not zero)
+    if (splits > k_tiles || (long long)(splits - 1) * ((k_tiles + splits - 1) / splits) >= k_tiles)
+        return AIR_ERR_BAD_ARGUMENT;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

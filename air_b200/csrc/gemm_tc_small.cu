@@ -320,7 +320,9 @@ AIR_API int air_gemm_tc_small(const void* x, const void* w, void* out, int T, in
         return AIR_ERR_BAD_ARGUMENT;
     if (epi == TS_SILU && (tile_rows != 256 || N % 256)) return AIR_ERR_BAD_ARGUMENT;
     const int k_tiles = (K + TS_BK - 1) / TS_BK;
-    if (splits > k_tiles) return AIR_ERR_BAD_ARGUMENT;
+    // every part of the k range must hold at least one k-tile (an accumulator that no product wrote is not zero)
+    if (splits > k_tiles || (long long)(splits - 1) * ((k_tiles + splits - 1) / splits) >= k_tiles)
+        return AIR_ERR_BAD_ARGUMENT;
     const int nt = T > 32 ? 64 : (T > 16 ? 32 : 16);
     CUtensorMap mw, mx;
     int rc = ts_make_map(&mw, w, N, K, tile_rows);

@@ -115,3 +115,9 @@ def test_refusals():
     w = torch.zeros(8, 36, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(o.KernelError, match="multiple of 8"):
         o.gemm_tc(a, w, torch.zeros(4, 8, device="cuda"), 32, o.EPI_F32)
+    # 16 k-tiles in 5 parts would be 4 + 4 + 4 + 4 + 0: an empty part's accumulator is never written
+    a = torch.zeros(8, 1024, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(256, 1024, dtype=torch.bfloat16, device="cuda")
+    for bn in (64, 128):            # both kernels
+        with pytest.raises(o.KernelError, match="size or dtype"):
+            o.gemm_tc(a, w, torch.zeros(5, 8, 256, device="cuda"), bn, o.EPI_PARTIAL, splits=5)
