@@ -64,6 +64,10 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    // keys and values pass through L2 once: evict-first, so that their stream leaves the weights that the
+    // following products have asked for there
+    uint64_t kv_policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(kv_policy));
     pdl_wait();
     trace_point(TR_ATT_DECODE);
 
@@ -112,9 +116,10 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
                     const int row_v = row_k + K * P;
 #pragma unroll
                     for (int s = 0; s < SUB; ++s) {
-                        tma_load_2d(dst + s * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_k, &full[stage]);
-                        tma_load_2d(dst + (SUB + s) * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_v,
-                                    &full[stage]);
+                        tma_load_2d_hint(dst + s * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_k, &full[stage],
+                                         kv_policy);
+                        tma_load_2d_hint(dst + (SUB + s) * SUB_BYTES + b * box_rows * 128, &map_cache, 64 * s, row_v,
+                                         &full[stage], kv_policy);
                     }
                 }
             }
