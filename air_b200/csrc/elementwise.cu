@@ -57,8 +57,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
 // kernel is a chain of latencies, so a thread first issues all of its loads (up to ELT_PARTS parts at
 // once) and the block is as wide as the row (one access per thread where E <= 4096).
 constexpr int ELT_PARTS = 8;
+#ifndef NORM_REGS
+#define NORM_REGS 56
+#endif
 template <typename TD, typename TW, typename TO>
-__global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restrict__ delta, int parts,
+__global__ void __maxnreg__(NORM_REGS) add_rmsnorm_vec4_kernel(float* __restrict__ h, const TD* __restrict__ delta, int parts,
                                         size_t part_stride, const TW* __restrict__ w, TO* __restrict__ out,
                                         const int* __restrict__ rows, int E, float eps) {
     __shared__ float scratch[32];
