@@ -29,7 +29,9 @@ def choose_tile(out_features: int, in_features: int, may_split: bool = True):
     if out_features >= 256 * SMS:
         return 128, 1        # several waves of tiles: the tail does not matter (measured: 128 before 256)
     best = None
-    for bn in (256, 128, 64, 32):
+    # (tiles of 128 or 256 rows of W run with the weights as the M side of the instruction, which is what a
+    # step of few tokens wants; narrower tiles are for matrices smaller than that)
+    for bn in ((256, 128) if out_features >= 128 else (64, 32)):
         for s in range(1, 9 if may_split else 2):
             if s > 1 and k_tiles // s < 8:
                 continue
