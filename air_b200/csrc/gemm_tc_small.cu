@@ -35,7 +35,6 @@ struct TsArgs {
     void* out;          // F32/PARTIAL: float [splits][T][N]; BF16: bf16 [T][N]; SILU: bf16 [T][N/2]
     int T, N, K;
     int splits;
-    int prefetch;       // further k-tiles of W that a block asks into L2 before its predecessor has ended
     int* status;
 };
 
@@ -135,8 +134,9 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         mbar_expect_tx(&full[i], bytes);
                         tma_load_2d(sw + i * STAGE_W, &map_w, (k_begin + i) * TS_BK, n0, &full[i]);
                     }
-                    const int ahead = min(pre + args.prefetch, k_end - k_begin);
-                    for (int i = pre; i < ahead; ++i) tma_prefetch_l2(&map_w, (k_begin + i) * TS_BK, n0);
+                    // (Asking further k-tiles into L2 here, as gemm_tc.cu does, was measured to cost 1.7 % of a
+                    // decode step with this kernel: the ring is deep, and the requests delay the loads of
+                    // the small kernels that run meanwhile.)
                     pdl_wait();
                     trace_point(TR_GEMM_TC);
                     for (int i = 0; i < pre; ++i) tma_load_2d(sx + i * STAGE_X, &map_x, (k_begin + i) * TS_BK, 0, &full[i]);
@@ -335,10 +335,7 @@ AIR_API int air_gemm_tc_small(const void* x, const void* w, void* out, int T, in
     if (max_blocks > 0 && max_blocks < sms) sms = max_blocks;
     const long long tiles = (long long)((N + tile_rows - 1) / tile_rows) * splits;
     const int blocks = (int)(tiles < sms ? tiles : sms);
-    // While the predecessor runs, each block asks its share of up to 40 MB of weights into L2 (the L2
-    // holds 126 MB).
-    const int prefetch = (int)((40ll << 20) / blocks / (tile_rows * TS_BK * 2));
-    TsArgs args{out, T, N, K, splits, prefetch, status};
+    TsArgs args{out, T, N, K, splits, status};
     if (tile_rows == 256) return ts_dispatch_tokens<2>(nt, epi, mw, mx, args, blocks, stream);
     return ts_dispatch_tokens<1>(nt, epi, mw, mx, args, blocks, stream);
 }
