@@ -146,7 +146,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     // The block's two groups of the list (heavy ones first) and its head.  The second group has to go
     // on where the first, a full one, ends; the host's list pads every request to whole pairs.
-    const int pair = gridDim.x - 1 - blockIdx.x;
+    // (blocks are handed out in the order of blockIdx.x, then blockIdx.y: all heads of the heaviest pair
+    // first, then all heads of the next, so that the light pairs fill in behind the heavy ones)
+    const int pair = gridDim.y - 1 - blockIdx.y;
     const int* grp = tiles + 4 * AT_GROUP * AT_ROW_TILES * pair;
     int count_a = 0, count_b = 0;
     for (int i = 0; i < AT_GROUP; ++i) {
@@ -159,7 +161,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (threadIdx.x == 0 && status) atomicExch(status, 8);
         count_b = 0;
     }
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int kvh = (int)(((long long)h * K) / H);
     const int* bt = block_table + (size_t)slot * max_blocks;
     const bool has_b = count_b > 0;
@@ -450,7 +452,7 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* b
     auto kernel = prefill_attention_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return launch(kernel, dim3(n_tiles / (AT_GROUP * AT_ROW_TILES), H), AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles,
+    return launch(kernel, dim3(H, n_tiles / (AT_GROUP * AT_ROW_TILES)), AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles,
                   (__nv_bfloat16*)out, H, K, P, window, scale * 1.4426950408889634f, status);
 }
 
@@ -462,7 +464,7 @@ AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, lo
                                      int P, int window, float scale, int* status, cudaStream_t stream) {
     using namespace air;
     if (n_tiles <= 0) return 0;
-    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || n_tiles % (AT_GROUP * AT_ROW_TILES) || H > 65535 ||
+    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || n_tiles % (AT_GROUP * AT_ROW_TILES) || n_tiles / (AT_GROUP * AT_ROW_TILES) > 65535 ||
         ((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || (D != 64 && D != 128))
         return AIR_ERR_BAD_ARGUMENT;
     CUtensorMap mq, mc;
