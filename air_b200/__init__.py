@@ -11,7 +11,7 @@ from .sampling.sampler import GenerationConfig, SamplingConfig  # noqa: F401
 
 def __getattr__(name):
     # the engine's modules load torch and the CUDA library; import them on first use
-    if name in ("InferenceService", "SchedulerConfig", "InferenceResponse"):
+    if name in ("InferenceService", "SchedulerConfig", "InferenceResponse", "CancellationSource", "CancellationToken"):
         from .engine import service
         return getattr(service, name)
     if name in ("Engine", "EngineConfig", "write_random_model"):

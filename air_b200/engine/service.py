@@ -78,6 +78,37 @@ class QueueFull(RuntimeError):
     pass
 
 
+class CancellationToken:
+    """include/air/serving.hpp:212-224: what a request carries; true once its source was cancelled."""
+
+    def __init__(self, state=None):
+        self._state = state
+
+    def is_cancelled(self) -> bool:
+        return bool(self._state and self._state[0])
+
+    def __bool__(self) -> bool:
+        return self._state is not None
+
+
+class CancellationSource:
+    """include/air/serving.hpp:226-235: `token()` goes with the request, `cancel()` ends it: a queued request
+    at the next admission ("request cancelled while queued"), an active one before the next step
+    ("request cancelled while active"); its pages go back like those of a finished request."""
+
+    def __init__(self):
+        self._state = [False]
+
+    def token(self) -> CancellationToken:
+        return CancellationToken(self._state)
+
+    def cancel(self) -> None:
+        self._state[0] = True
+
+    def is_cancelled(self) -> bool:
+        return self._state[0]
+
+
 @dataclass
 class _WorkItem:
     request_id: int
@@ -95,6 +126,7 @@ class _WorkItem:
     admitted: float = 0.0
     first_token: float = 0.0
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
+    cancellation: CancellationToken = field(default_factory=CancellationToken)
 
     @property
     def phase(self) -> WorkPhase:
@@ -125,6 +157,7 @@ class InferenceService:
         self._next_id = 0
         self.cycles = 0
         self.preemptions = 0
+        self.cancelled_requests = 0
         self.last_batch = None
         self._inflight: Optional[_InFlight] = None
         self._pinned = {}
@@ -142,7 +175,8 @@ class InferenceService:
         return cls(engine, scheduler)
 
     # ------------------------------------------------------------------ requests
-    def submit(self, prompt_tokens: Sequence[int], generation: Optional[GenerationConfig] = None) -> int:
+    def submit(self, prompt_tokens: Sequence[int], generation: Optional[GenerationConfig] = None,
+               cancellation: Optional[CancellationToken] = None) -> int:
         generation = generation or GenerationConfig()
         generation.sampling.validate()
         spec = self.engine.model.spec
@@ -156,7 +190,7 @@ class InferenceService:
         if len(self.queued) >= self.config.max_queued_requests:
             raise QueueFull("inference submission queue is full")
         item = _WorkItem(self._next_id, prompt, len(prompt), generation, HostSampler(generation.sampling),
-                         submitted=time.perf_counter())
+                         submitted=time.perf_counter(), cancellation=cancellation or CancellationToken())
         self._next_id += 1
         self.queued.append(item)
         return item.request_id
@@ -178,9 +212,13 @@ class InferenceService:
         self.active.append(item)
         return item.request_id
 
-    def generate(self, prompt_tokens: Sequence[int], generation: Optional[GenerationConfig] = None
-                 ) -> InferenceResponse:
-        return self.generate_cohort([(prompt_tokens, generation)])[0]
+    def generate(self, prompt_tokens: Sequence[int], generation: Optional[GenerationConfig] = None,
+                 cancellation: Optional[CancellationToken] = None) -> InferenceResponse:
+        request = self.submit(prompt_tokens, generation, cancellation)
+        while request not in self.finished:
+            if not self.run_cycle() and not self.active and not self.queued:
+                break
+        return self.finished.pop(request)
 
     def generate_cohort(self, requests) -> List[InferenceResponse]:
         """Submits the requests together and runs cycles until all of them are finished."""
@@ -194,8 +232,25 @@ class InferenceService:
         return [self.finished.pop(i) for i in ids]
 
     # ------------------------------------------------------------------ one cycle
+    def _cancellations(self) -> None:
+        """src/runtime/serving.cpp:1522-1530, 1761-1766: cancelled requests leave before admission and
+        before the cycle's batch is made."""
+        for item in [i for i in self.queued if i.cancellation.is_cancelled()]:
+            self.queued.remove(item)
+            self.cancelled_requests += 1
+            self._finish(item, error="request cancelled while queued")
+        hit = False
+        for item in self.active:
+            if not item.done and item.cancellation.is_cancelled():
+                item.done, item.error = True, "request cancelled while active"
+                self.cancelled_requests += 1
+                hit = True
+        if hit and self._inflight is None:
+            self._retire()      # (with a step in flight they leave when it has been read)
+
     def _admit(self) -> None:
         cache = self.engine.cache
+        self._cancellations()
         while self.queued:
             item = self.queued[0]
             worst = len(item.prompt) + max(0, item.generation.max_new_tokens - len(item.generated))
@@ -340,8 +395,9 @@ class InferenceService:
     def _retire(self) -> None:
         for item in [i for i in self.active if i.done]:
             self.active.remove(item)
-            self.engine.finish(item.request_id)
-            self._finish(item)
+            if item.request_id in self.engine.cache.sequences:
+                self.engine.finish(item.request_id)
+            self._finish(item, error=item.error)
 
     def _preempt_youngest(self) -> int:
         """Takes the active request that was admitted last out of the engine and puts it back
@@ -424,4 +480,5 @@ class InferenceService:
         return {"queued_requests": len(self.queued), "active_requests": len(self.active),
                 "reserved_pages": sum(i.reservation_pages for i in self.active),
                 "kv_pages_total": cache.num_pages, "kv_pages_free": cache.free_pages(),
-                "cycles": self.cycles, "preemptions": self.preemptions}
+                "cycles": self.cycles, "preemptions": self.preemptions,
+                "cancelled_requests": self.cancelled_requests}

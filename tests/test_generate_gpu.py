@@ -154,6 +154,34 @@ def test_decoding_one_step_ahead_gives_the_same_tokens():
     assert cycles_ahead <= cycles + 3      # at most a dropped step per request that stops by itself
 
 
+def test_cancellation_with_a_step_in_flight():
+    """A request cancelled while the loop decodes one step ahead: it leaves with the tokens read so far, the
+    other one goes on and gets the tokens it would have got alone, all pages come back."""
+    from air_b200 import GenerationConfig
+    from air_b200.engine.service import CancellationSource
+    folder = util.model_folder("B")
+    cfg, tensors = util.plain_model(folder)
+    prompts = [util.tokens_for("B", 6, 400), util.tokens_for("B", 11, 401)]
+    svc = service("B", "float32")
+    source = CancellationSource()
+    ids = [svc.submit(prompts[0], GenerationConfig(max_new_tokens=20, stop_on_eos=False), source.token()),
+           svc.submit(prompts[1], GenerationConfig(max_new_tokens=12, stop_on_eos=False))]
+    for _ in range(6):
+        svc.run_cycle()
+    assert svc._inflight is not None, "the loop is one step ahead"
+    source.cancel()
+    while ids[1] not in svc.finished:
+        svc.run_cycle()
+    a, b = svc.finished[ids[0]], svc.finished[ids[1]]
+    assert a.error == "request cancelled while active" and 1 <= len(a.tokens) < 20
+    assert a.tokens == plain.greedy_generate(cfg, tensors, prompts[0], len(a.tokens))
+    assert b.error is None and b.tokens == plain.greedy_generate(cfg, tensors, prompts[1], 12)
+    while svc.run_cycle():
+        pass
+    assert svc.engine.cache.free_pages() == svc.engine.cache.num_pages
+    svc.engine.check_status()
+
+
 def test_host_sampler_path_with_top_k_and_top_p():
     from air_b200 import GenerationConfig, SamplingConfig
     folder = util.model_folder("A")

@@ -177,3 +177,33 @@ def test_a_single_request_that_outgrows_the_pool_fails():
     r = svc.generate(list(range(10)), GenerationConfig(max_new_tokens=30, stop_on_eos=False))
     assert r.error == "insufficient KV pages for one sequence"
     assert eng.cache.free_pages() == 2
+
+
+def test_cancellation_while_queued_and_while_active():
+    """A cancelled request leaves at the next admission pass: one that still waits in the queue with
+    "cancelled while queued", one that is being computed with "cancelled while active" and the tokens it
+    has so far; its pages go back, the others go on."""
+    from air_b200.engine.service import CancellationSource
+    eng = FakeEngine(pages=16)
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=2, prefill_quantum_tokens=4))
+    sources = [CancellationSource() for _ in range(3)]
+    ids = [svc.submit([1 + i, 2, 3, 4, 5, 6], GenerationConfig(max_new_tokens=6), s.token())
+           for i, s in enumerate(sources)]
+    svc.run_cycle()                                   # two are admitted, the third waits
+    assert len(svc.active) == 2 and len(svc.queued) == 1
+    sources[2].cancel()
+    svc.run_cycle()
+    assert svc.finished[ids[2]].error == "request cancelled while queued" and not svc.queued
+    for _ in range(3):
+        svc.run_cycle()
+    produced = len(svc.active[0].generated)
+    assert produced >= 1
+    sources[0].cancel()
+    while ids[1] not in svc.finished:
+        svc.run_cycle()
+    first = svc.finished[ids[0]]
+    assert first.error == "request cancelled while active" and len(first.tokens) in (produced, produced + 1)
+    assert svc.finished[ids[1]].error is None and len(svc.finished[ids[1]].tokens) == 6
+    assert svc.snapshot()["cancelled_requests"] == 2
+    assert eng.cache.free_pages() == eng.cache.num_pages
+    eng.cache.check()
