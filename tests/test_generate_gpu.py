@@ -182,6 +182,35 @@ def test_cancellation_with_a_step_in_flight():
     svc.engine.check_status()
 
 
+@pytest.mark.parametrize("reserve", [True, False])
+def test_service_under_churn(reserve):
+    """Twenty requests of random lengths through a service with four places, a small token budget and a
+    pool that holds only part of them at a time (with and without worst-case reservation, i.e. with
+    waiting in the queue and with preemption and recomputation): every request gets the tokens that the
+    plain implementation generates for it alone, and every page comes back."""
+    from air_b200 import GenerationConfig
+    folder = util.model_folder("A")
+    cfg, tensors = util.plain_model(folder)
+    rng = np.random.default_rng(7)
+    reqs = []
+    for i in range(20):
+        prompt = util.tokens_for("A", int(rng.integers(1, 70)), 600 + i)
+        reqs.append((prompt, GenerationConfig(max_new_tokens=int(rng.integers(1, 20)), stop_on_eos=False)))
+    svc = service("A", "float32", max_active_requests=4, token_budget_per_cycle=48, prefill_quantum_tokens=16,
+                  max_tokens=288 if reserve else 160, reserve_worst_case=reserve)
+    got = svc.generate_cohort(reqs)
+    for (prompt, g), r in zip(reqs, got):
+        assert r.error is None
+        assert r.tokens == plain.greedy_generate(cfg, tensors, prompt, g.max_new_tokens)
+    while svc.run_cycle():
+        pass
+    assert svc.engine.cache.free_pages() == svc.engine.cache.num_pages
+    svc.engine.cache.check()
+    svc.engine.check_status()
+    if not reserve:
+        assert svc.preemptions > 0, "the small pool ran out and the youngest request was computed again"
+
+
 def test_host_sampler_path_with_top_k_and_top_p():
     from air_b200 import GenerationConfig, SamplingConfig
     folder = util.model_folder("A")
