@@ -406,6 +406,27 @@ def test_prefill_attention_tc(H, K, d, P, window):
     assert np.abs(out.float().cpu().numpy() - want).max() < 1e-2 * max(1.0, np.abs(want).max())
 
 
+def test_prefill_attention_tc_reports_a_list_that_is_not_in_pairs():
+    """Two requests with one group of 8 tiles each, one after the other: the second group does not go on
+    where the first ends, so the kernel flags status 8 instead of mixing the requests."""
+    H, K, d, P = 4, 2, 64, 64
+    lens, q_lens = [100, 90], [100, 90]
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, lens, q_lens, "bfloat16", seed=3, num_pages=8)
+    tiles, tok = [], 0
+    for s_, n in enumerate(q_lens):
+        for i in range(0, n, 16):
+            tiles.append([s_, tok + i, i, min(16, n - i)])
+        while len(tiles) % 8:
+            tiles.append([s_, 0, 0, 0])
+        tok += n
+    assert len(tiles) == 16
+    out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().prefill_attention_tc(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt),
+                               dev(np.array(tiles, dtype=np.int32)), out, 0, 1.0 / math.sqrt(d), status=status)
+    assert status.item() == 8
+
+
 @pytest.mark.parametrize("far", [0, 15, 63, 64, 500, 1023])
 def test_prefill_attention_tc_finds_one_far_key(far):
     H, K, d, P, n = 8, 2, 128, 64, 1040
