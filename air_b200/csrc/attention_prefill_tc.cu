@@ -248,7 +248,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     // S(j) = Q K(j)^T into S[j & 1] (which held P(j-2): the product that read it was
                     // issued before this one)
                     const int t = me.first + j, stage = t % AT_STAGES;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&kv_full[stage], (t / AT_STAGES) & 1, abort_flag));
+                    if (!mbar_try_wait(&kv_full[stage], (t / AT_STAGES) & 1))      // (mostly there already: one try)
+                        ok = __all_sync(0xffffffffu, mbar_wait(&kv_full[stage], (t / AT_STAGES) & 1, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t kaddr = smem_u32(skv + stage * STAGE_BYTES);

@@ -176,7 +176,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_base + acc * BN;
                 for (int kt = k_begin; kt < k_end; ++kt) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag));
+                    // (a stage that is already there costs one try; the bounded loop only where the issuer has to wait)
+                    if (!mbar_try_wait(&full[stage], phase)) ok = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     // (the start address field counts 16 bytes)

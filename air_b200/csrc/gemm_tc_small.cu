@@ -168,7 +168,8 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             tc_fence_after();
             const uint32_t d = tmem_base + acc * ACC_COLS;
             for (int kt = k_begin; kt < k_end; ++kt) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag));
+                // (a stage that is already there costs one try; the bounded loop only where the issuer has to wait)
+                if (!mbar_try_wait(&full[stage], phase)) ok = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag));
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t dw = dw0 + (uint64_t)(stage * (STAGE_W >> 4));
