@@ -15,7 +15,7 @@ import util
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": (1, 7, 33, 97, 150), "B": (5, 40, 97, 131, 64, 18), "W": (3, 50, 97, 140),
-           "K": (2, 65, 150, 300), "L": (9, 129, 64, 270)}
+           "K": (2, 65, 150, 300), "L": (9, 129, 64, 270), "M": (3, 70, 200)}
 
 
 def streams_for(name):
@@ -77,10 +77,10 @@ def test_float32_does_not_depend_on_the_cut(name):
         assert np.array_equal(a[k], b[k]) and np.array_equal(a[k], c[k]), k
 
 
-@pytest.mark.parametrize("name", ["K", "L"])
+@pytest.mark.parametrize("name", ["K", "L", "M"])
 def test_bfloat16_heads_of_64_and_128_take_the_tensor_core_kernels(name):
     """The kernels' own trace says which attention kernels a mixed replay ran: the decode kernel and the
-    tile kernel, never the 32-bit one."""
+    tile kernel, never the 32-bit one.  (M has heads of 256: the mma.sync tile kernel.)"""
     import torch
     from air_b200.csrc import ops
     folder, streams = util.model_folder(name), streams_for(name)

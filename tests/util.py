@@ -33,7 +33,11 @@ TINY_L = dict(BASE, num_hidden_layers=2, hidden_size=384, num_attention_heads=3,
               intermediate_size=256, vocab_size=230, max_position_embeddings=512, rope_theta=1e5,
               rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=70,
               max_window_layers=1)
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "W": (TINY_W, 2), "K": (TINY_K, 3), "L": (TINY_L, 4)}
+TINY_M = dict(BASE, num_hidden_layers=2, hidden_size=512, num_attention_heads=2, num_key_value_heads=1,
+              intermediate_size=192, vocab_size=150, max_position_embeddings=512, rope_theta=20000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=True, use_sliding_window=False)      # heads of 256
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "W": (TINY_W, 2), "K": (TINY_K, 3), "L": (TINY_L, 4),
+           "M": (TINY_M, 5)}
 
 _folders = {}
 _tmp = []
