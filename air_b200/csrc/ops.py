@@ -97,8 +97,19 @@ def _check(code: int, name: str):
         raise KernelError(f"{name}: CUDA error {code} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The current stream's handle (the stream that a graph capture or a stream context has made current).
+    A step launches hundreds of kernels from Python, so this asks the runtime directly where it can."""
+    global _device_index
+    if _raw_stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return _raw_stream(_device_index)
 
 
 def _req(t: torch.Tensor, name: str, dtypes=None, shape=None):
@@ -109,8 +120,12 @@ def _req(t: torch.Tensor, name: str, dtypes=None, shape=None):
     if dtypes is not None and t.dtype not in dtypes:
         raise KernelError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
     if shape is not None:
-        if t.dim() != len(shape) or any(s is not None and s != g for s, g in zip(shape, t.shape)):
-            raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+        got = t.shape
+        if len(got) != len(shape):
+            raise KernelError(f"{name} has shape {tuple(got)}, expected {tuple(shape)}")
+        for s, g in zip(shape, got):
+            if s is not None and s != g:
+                raise KernelError(f"{name} has shape {tuple(got)}, expected {tuple(shape)}")
     return t
 
 
