@@ -427,6 +427,34 @@ def test_prefill_attention_tc_reports_a_list_that_is_not_in_pairs():
     assert status.item() == 8
 
 
+@pytest.mark.parametrize("kernel", ["decode", "prefill", "prefill_tc"])
+@pytest.mark.parametrize("n,w", [(300, 37), (300, 64), (257, 129), (200, 200)])
+def test_window_edge_is_exact_in_the_tensor_core_kernels(kernel, n, w):
+    """The key at distance w - 1 from the last query counts, the key at distance w does not: one of them
+    at a time is made to stand out, and the last token's output either is its value or is not.  The
+    window's edge falls inside a tile of keys, on a tile's first key and on a page's first key."""
+    H, K, d, P = 4, 2, 128 if kernel != "prefill" else 256, 64
+    q_len = 1 if kernel == "decode" else 40
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [q_len], "bfloat16", seed=n + w, num_pages=8)
+    q[:] = 0.5
+    last = n - 1
+    for key, visible in ((last - w + 1, True), (last - w, False)):
+        if key < 0:
+            continue
+        c = cache.copy()
+        c[bt[0, key // P], 0, :, key % P, :] = 8.0
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
+        args = (dev(q, torch.bfloat16), dev(c, torch.bfloat16), dev(bt))
+        if kernel == "decode":
+            ops().decode_attention(*args, dev(seq_of), dev(positions), out, w, 1.0 / math.sqrt(d))
+        elif kernel == "prefill":
+            ops().prefill_attention(*args, dev(tiles_for([n], [q_len])), out, w, 1.0 / math.sqrt(d))
+        else:
+            ops().prefill_attention_tc(*args, dev(tiles_for([n], [q_len])), out, w, 1.0 / math.sqrt(d))
+        hit = np.abs(out.float().cpu().numpy()[-1, 0] - vs[0][key, 0]).max() < 3e-2
+        assert hit == visible, (key, visible)
+
+
 @pytest.mark.parametrize("far", [0, 15, 63, 64, 500, 1023])
 def test_prefill_attention_tc_finds_one_far_key(far):
     H, K, d, P, n = 8, 2, 128, 64, 1040
