@@ -64,6 +64,17 @@ def test_mixed_with_pages_used_again(name, dtype, page):
         assert group.pool.takes > group.pool.num_pages, "pages were used again"
 
 
+@pytest.mark.parametrize("page", [32, 128])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["K", "L"])
+def test_mixed_with_other_page_sizes(name, dtype, page):
+    """Pages of half a key tile and of two key tiles (the tensor-core kernels fetch 64 keys at a time)."""
+    folder, streams = util.model_folder(name), streams_for(name)
+    steps = util.trace_mixed(streams, seed=9, live=3)
+    got, engine = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps, page=page), page_tokens=page)
+    util.check_against_plain(got, folder, streams, dtype)
+
+
 @pytest.mark.parametrize("name", ["A", "B", "W", "K", "L"])
 def test_float32_does_not_depend_on_the_cut(name):
     """In float32 every kernel reduces in an order that depends only on the position, so the
