@@ -292,7 +292,7 @@ AIR_API int air_decode_attention_tma(const void* q, const void* cache, long long
                                      float scale, int splits, int* status, cudaStream_t stream) {
     using namespace air;
     if (T <= 0) return 0;
-    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || splits < 1 || T > 65535 ||
+    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || splits < 1 || T > 65535 ||
         (splits > 1 && (!part_o || !part_ml)) || ((uintptr_t)cache & 15))
         return AIR_ERR_BAD_ARGUMENT;
     EncodeTiled enc = encode_tiled();

@@ -269,7 +269,7 @@ AIR_API int air_prefill_attention(const void* q, const void* cache, long long pa
                                   int window, float scale, int* status, cudaStream_t stream) {
     using namespace air;
     if (n_tiles <= 0) return 0;
-    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || n_tiles % PF_GROUP || ((uintptr_t)cache & 15) ||
+    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || n_tiles % PF_GROUP || ((uintptr_t)cache & 15) ||
         K * ((H / K + 7) / 8) > 65535)
         return AIR_ERR_BAD_ARGUMENT;
     EncodeTiled enc = encode_tiled();

@@ -465,7 +465,7 @@ AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, lo
                                      int P, int window, float scale, int* status, cudaStream_t stream) {
     using namespace air;
     if (n_tiles <= 0) return 0;
-    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 && 64 % P) || n_tiles % (AT_GROUP * AT_ROW_TILES) || n_tiles / (AT_GROUP * AT_ROW_TILES) > 65535 ||
+    if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || n_tiles % (AT_GROUP * AT_ROW_TILES) || n_tiles / (AT_GROUP * AT_ROW_TILES) > 65535 ||
         ((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || (D != 64 && D != 128))
         return AIR_ERR_BAD_ARGUMENT;
     CUtensorMap mq, mc;

@@ -283,6 +283,12 @@ def table_update(table, updates):
 DECODE_HEAD_DIMS = (64, 128, 256)
 
 
+def tile_pages(page_tokens: int) -> bool:
+    """Whether the kernels that fetch 64 keys at a time with the copy engine take this page size: a tile of
+    keys must lie in one page or be made of whole pages."""
+    return 64 % page_tokens == 0 if page_tokens < 64 else page_tokens % 64 == 0
+
+
 def decode_splits(tokens: int, heads: int, kv_heads: int) -> int:
     """How many blocks share the keys of one (token, kv head): so many that about 190 blocks run,
     which keeps every SM busy without a second round (measured on B200: 6 for 8 tokens x 4 kv heads,
@@ -319,7 +325,7 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
         if po.numel() < T * H * splits * d or pm.numel() < T * H * splits * 2:
             raise KernelError("decode_attention: scratch is too small")
     global launches
-    if engine == "tma" and (P >= 64 or 64 % P == 0):
+    if engine == "tma" and tile_pages(P):
         _check(_get("air_decode_attention_tma")(
             q.data_ptr(), cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
             token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P,
@@ -353,8 +359,8 @@ def prefill_attention(q, cache, block_table, tiles, out, window, scale, status=N
         raise KernelError(f"prefill_attention takes head sizes {DECODE_HEAD_DIMS}, not {d}")
     if tiles.shape[0] % TILE_GROUP:
         raise KernelError("prefill_attention: the tile list must come in groups of 8")
-    if P < 64 and 64 % P:
-        raise KernelError(f"prefill_attention: page size {P} does not divide 64")
+    if not tile_pages(P):
+        raise KernelError(f"prefill_attention: page size {P} is neither a divisor nor a multiple of 64")
     _check(_get("air_prefill_attention")(
         q.data_ptr(), cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
         tiles.data_ptr(), tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _ptr(status),
@@ -428,8 +434,8 @@ def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, statu
         raise KernelError(f"prefill_attention_tc takes head sizes {TC_ATTENTION_HEAD_DIMS}, not {d}")
     if tiles.shape[0] % TILE_PAIR:
         raise KernelError("prefill_attention_tc: the tile list must come in groups of 16 per request")
-    if P < 64 and 64 % P:
-        raise KernelError(f"prefill_attention_tc: page size {P} does not divide 64")
+    if not tile_pages(P):
+        raise KernelError(f"prefill_attention_tc: page size {P} is neither a divisor nor a multiple of 64")
     _check(_get("air_prefill_attention_tc")(
         q.data_ptr(), T, cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
         tiles.data_ptr(), tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _ptr(status),

@@ -99,7 +99,7 @@ class Attention(Mixer):
         if rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.all_decode:
             ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.tiles is not None
-              and (pages.kv.shape[3] >= 64 or 64 % pages.kv.shape[3] == 0)):
+              and ops.tile_pages(pages.kv.shape[3])):
             # a mixed step: the single next tokens at the head of the batch take the decode kernel (a row
             # tile of 128 queries for one token would read its request's whole context for one row), the
             # prompt portions the tile kernels

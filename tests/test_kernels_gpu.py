@@ -293,6 +293,15 @@ def test_kernels_refuse_what_they_cannot_take():
         o.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
     with pytest.raises(o.KernelError, match="shape"):
         o.gemm_f32(torch.zeros(2, 8, device="cuda"), torch.zeros(3, 9, device="cuda"), None, torch.zeros(2, 3, device="cuda"))
+    # pages of 80 tokens: a tile of 64 keys would straddle two pages, the copy-engine kernels refuse them
+    qb = torch.zeros(16, 2, 128, dtype=torch.bfloat16, device="cuda")
+    cb = torch.zeros(4, 2, 1, 80, 128, dtype=torch.bfloat16, device="cuda")
+    tiles = torch.zeros(16, 4, dtype=torch.int32, device="cuda")
+    table = torch.zeros(1, 4, dtype=torch.int32, device="cuda")
+    for kernel in (o.prefill_attention, o.prefill_attention_tc):
+        with pytest.raises(o.KernelError, match="neither a divisor nor a multiple of 64"):
+            kernel(qb, cb, table, tiles, torch.empty_like(qb), 0, 1.0)
+    assert o.tile_pages(16) and o.tile_pages(64) and o.tile_pages(192) and not o.tile_pages(48) and not o.tile_pages(96)
 
 
 @pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (4, 4, 128, 16), (40, 2, 64, 32), (8, 1, 256, 16)])

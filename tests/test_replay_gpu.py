@@ -64,11 +64,13 @@ def test_mixed_with_pages_used_again(name, dtype, page):
         assert group.pool.takes > group.pool.num_pages, "pages were used again"
 
 
-@pytest.mark.parametrize("page", [32, 128])
+@pytest.mark.parametrize("page", [32, 128, 48, 80])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["K", "L"])
 def test_mixed_with_other_page_sizes(name, dtype, page):
-    """Pages of half a key tile and of two key tiles (the tensor-core kernels fetch 64 keys at a time)."""
+    """Pages of half a key tile and of two key tiles (the tensor-core kernels fetch 64 keys at a time), and
+    pages of 48 and 80 tokens, in which a tile of 64 keys would straddle pages: those take the kernels
+    that read key by key."""
     folder, streams = util.model_folder(name), streams_for(name)
     steps = util.trace_mixed(streams, seed=9, live=3)
     got, engine = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps, page=page), page_tokens=page)
