@@ -437,7 +437,7 @@ def test_prefill_attention_tc_reports_a_list_that_is_not_in_pairs():
 
 
 @pytest.mark.parametrize("kernel", ["decode", "prefill", "prefill_tc"])
-@pytest.mark.parametrize("n,w", [(300, 37), (300, 64), (257, 129), (200, 200)])
+@pytest.mark.parametrize("n,w", [(300, 37), (300, 64), (257, 129), (200, 200), (70, 1), (129, 2)])
 def test_window_edge_is_exact_in_the_tensor_core_kernels(kernel, n, w):
     """The key at distance w - 1 from the last query counts, the key at distance w does not: one of them
     at a time is made to stand out, and the last token's output either is its value or is not.  The
