@@ -22,8 +22,11 @@
 // Under the causal mask the second row tile takes two more key tiles than the first; with a
 // window it also starts later.  A row tile's issuer hands back the stages it does not take.
 //
+// The grid is (heads, pairs) with the last pair of the list first: blocks are handed out in the order of
+// blockIdx.x, then blockIdx.y, so all heads of the heaviest pair of a prompt start first.
+//
 // tiles, q, out, cache, block_table, window as in attention_prefill.cu; the list pads every request
-// to whole pairs of groups.  Head size 64 or 128.
+// to whole pairs of groups.  Head size 64 or 128; pages of a divisor or a multiple of 64 tokens.
 // Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 7.  A list
 // whose second group does not go on where the first ends flags *status = 8 (that group is skipped).
 #include "common.cuh"
