@@ -40,16 +40,21 @@ def test_greedy_generation_matches_plain(name):
     svc.engine.check_status()
 
 
-def test_first_tokens_of_a_sequence():
-    """Positions 0, 1, 2: one key, two keys, three keys; decoded one by one from the very start."""
+@pytest.mark.parametrize("name", ["B", "K", "L"])
+def test_first_tokens_of_a_sequence(name):
+    """Positions 0, 1, 2: one key, two keys, three keys; decoded one by one from the very start, and as a
+    portion of two tokens followed by single ones (K and L: the tensor-core attention kernels in bfloat16)."""
     from air_b200.engine.batch import Entry
-    folder = util.model_folder("B")
-    toks = util.tokens_for("B", 4, 77)
+    folder = util.model_folder(name)
+    toks = util.tokens_for(name, 5, 77)
     want = util.plain_logits(folder, toks)
     for dtype, tol in (("float32", util.FP32_TOL), ("bfloat16", util.BF16_MAX_TOL)):
-        svc = service("B", dtype)
+        svc = service(name, dtype, page_tokens=64)
         got = np.concatenate([svc.engine.step([Entry("r", [t], [0])]).cpu().numpy() for t in toks])
         assert np.abs(got - want).max() < tol * max(1.0, np.abs(want).max())
+        got = [svc.engine.step([Entry("s", toks[:2], [0, 1])]).cpu().numpy()]
+        got += [svc.engine.step([Entry("s", [t], [0])]).cpu().numpy() for t in toks[2:]]
+        assert np.abs(np.concatenate(got) - want).max() < tol * max(1.0, np.abs(want).max())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
