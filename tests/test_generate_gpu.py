@@ -57,18 +57,20 @@ def test_first_tokens_of_a_sequence(name):
         assert np.abs(np.concatenate(got) - want).max() < tol * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("name", ["A", "K"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_decoding_stays_on_the_plain_logits(dtype):
+def test_long_decoding_stays_on_the_plain_logits(dtype, name):
     """300 tokens decoded one by one after a short prompt (teacher-forced with the plain
-    implementation's greedy tokens), across many pages."""
+    implementation's greedy tokens), across many pages (K in bfloat16: the decode attention kernel and the
+    tcgen05 products inside the decode graph)."""
     from air_b200.engine.batch import Entry
-    folder = util.model_folder("A")
+    folder = util.model_folder(name)
     cfg, tensors = util.plain_model(folder)
-    prompt = util.tokens_for("A", 5, 9)
+    prompt = util.tokens_for(name, 5, 9)
     tokens = prompt + plain.greedy_generate(cfg, tensors, prompt, 40)
     tokens = (tokens * 8)[:320]                      # teacher-forced stream
     want = util.plain_logits(folder, tokens)
-    svc = service("A", dtype, max_tokens=384)
+    svc = service(name, dtype, max_tokens=384)
     eng = svc.engine
     got = [eng.step([Entry("r", tokens[:5], range(5))]).cpu().numpy()]
     got += [eng.step([Entry("r", [t], [0])]).cpu().numpy() for t in tokens[5:]]
