@@ -39,7 +39,8 @@ _SIGNATURES = {
                                  c_void_p],
     "air_prefill_attention_tc": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
-    "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                   c_void_p, c_void_p],
 }
 
 _fn = {}
@@ -253,21 +254,27 @@ def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window
     return out
 
 
-def sample(logits, temperature, uniform, out, status=None, slots=None, last_token=None):
+def sample(logits, temperature, uniform, out, status=None, slots=None, last_token=None, top_k=None, top_p=None):
     """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or temperature is None), else the
-    index drawn from softmax(logits[r] / temperature[r]) with the uniform number uniform[r].
-    With slots and last_token, also last_token[slots[r]] = out[r]."""
+    index drawn from softmax(logits[r] / temperature[r]) with the uniform number uniform[r], after
+    keeping the top_k[r] largest logits (0: all) and of those the shortest prefix of the descending order
+    that holds the share top_p[r] of the weight (1: all).  With slots and last_token, also
+    last_token[slots[r]] = out[r]."""
     R, V = logits.shape
     _req(logits, "logits", (torch.float32,))
     if temperature is not None:
         _req(temperature, "temperature", (torch.float32,), (R,))
         _req(uniform, "uniform", (torch.float32,), (R,))
+    if top_k is not None:
+        _req(top_k, "top_k", _I32, (R,))
+    if top_p is not None:
+        _req(top_p, "top_p", (torch.float32,), (R,))
     _req(out, "out", _I32, (R,))
     if slots is not None:
         _req(slots, "slots", _I32, (R,))
         _req(last_token, "last_token", _I32)
-    _check(_get("air_sample")(logits.data_ptr(), _ptr(temperature), _ptr(uniform), out.data_ptr(), _ptr(slots),
-                              _ptr(last_token), R, V, _ptr(status), _stream()), "sample")
+    _check(_get("air_sample")(logits.data_ptr(), _ptr(temperature), _ptr(uniform), _ptr(top_k), _ptr(top_p),
+                              out.data_ptr(), _ptr(slots), _ptr(last_token), R, V, _ptr(status), _stream()), "sample")
     return out
 
 

@@ -233,10 +233,11 @@ class Engine:
             all_decode=True, last_token=self.last_token)
         return logits, ctx
 
-    def sample(self, logits: torch.Tensor, temperature=None, uniform=None) -> torch.Tensor:
+    def sample(self, logits: torch.Tensor, temperature=None, uniform=None, top_k=None, top_p=None) -> torch.Tensor:
         """Chooses a token for every row of the last step's logits on the device: the lowest
         index of the maximum where temperature[r] <= 0 (or temperature is None), else a draw from
-        softmax(logits / temperature) with the uniform number uniform[r].  Returns int32 [rows] on
+        softmax(logits / temperature) with the uniform number uniform[r], cut to the top_k[r] largest logits
+        (0: all) and the share top_p[r] of the weight (1: all) where given.  Returns int32 [rows] on
         the device; each choice is also remembered for its request, so that the next step can
         take it as Entry(request, [LAST_SAMPLED]) without a copy to the host."""
         ctx = self.last_context
@@ -246,13 +247,13 @@ class Engine:
         if ctx is None or ctx.row_slots.shape[0] != logits.shape[0]:
             raise StepError("sample() takes the logits of the step that has just run")
 
-        def dev(x):
+        def dev(x, dtype=torch.float32):
             if x is None or isinstance(x, torch.Tensor):
                 return x
-            return torch.tensor(x, dtype=torch.float32).to(logits.device, non_blocking=True)
+            return torch.tensor(x, dtype=dtype).to(logits.device, non_blocking=True)
 
         ops.sample(logits, dev(temperature), dev(uniform), out, status=self.status, slots=ctx.row_slots,
-                   last_token=self.last_token)
+                   last_token=self.last_token, top_k=dev(top_k, torch.int32), top_p=dev(top_p))
         return out
 
     def kernel_launches(self) -> int:

@@ -52,6 +52,8 @@ class SchedulerConfig:
     kv_page_tokens: int = 64
     reserve_worst_case: bool = True
     decode_ahead: bool = True      # (not in AIR) launch a decode step before the one in flight is read
+    sample_cuts_on_device: bool = True   # (not in AIR) top-k / top-p draws on the device too: AIR's distribution,
+                                         # but not the token that AIR's walk gives for a seed (False: host sampler)
 
 
 @dataclass
@@ -346,13 +348,21 @@ class InferenceService:
             return False
         if len(entries) != len(self.active):
             return False
-        return all(i.phase == WorkPhase.decode and i.generation.sampling.on_device for i in self.active) and \
+        return all(i.phase == WorkPhase.decode and self._on_device(i) for i in self.active) and \
             all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+
+    def _on_device(self, item: _WorkItem) -> bool:
+        s = item.generation.sampling
+        return s.on_device or (self.config.sample_cuts_on_device and getattr(self.engine, "feeds_back_tokens", False))
 
     def _choose_on_device(self, items: Sequence[_WorkItem], logits):
         temps = [float(i.generation.sampling.temperature) for i in items]
         if any(t > 0.0 for t in temps):
             uniforms = [i.sampler.next_uniform() if t > 0.0 else 0.0 for i, t in zip(items, temps)]
+            cuts = [i.generation.sampling for i in items]
+            if any(c.top_k != 0 or c.top_p < 1.0 for c in cuts):
+                return self.engine.sample(logits, temps, uniforms, [int(c.top_k) for c in cuts],
+                                          [float(c.top_p) for c in cuts])
             return self.engine.sample(logits, temps, uniforms)
         return self.engine.sample(logits)
 
@@ -426,14 +436,8 @@ class InferenceService:
         rows = [by_id[e.request] for e in entries if e.want]
         chosen: List[Optional[int]] = [None] * len(rows)
         if rows:
-            if all(i.generation.sampling.on_device for i in rows):
-                temps = [float(i.generation.sampling.temperature) for i in rows]
-                if any(t > 0.0 for t in temps):
-                    uniforms = [i.sampler.next_uniform() if t > 0.0 else 0.0 for i, t in zip(rows, temps)]
-                    ids = self.engine.sample(logits, temps, uniforms)
-                else:
-                    ids = self.engine.sample(logits)
-                chosen = [int(t) for t in ids.tolist()]
+            if all(self._on_device(i) for i in rows):
+                chosen = [int(t) for t in self._choose_on_device(rows, logits).tolist()]
             else:
                 host = logits.float().cpu().numpy()
                 chosen = [i.sampler.sample(host[r]) for r, i in enumerate(rows)]

@@ -218,11 +218,35 @@ def test_service_under_churn(reserve):
         assert svc.preemptions > 0, "the small pool ran out and the youngest request was computed again"
 
 
+def test_top_k_and_top_p_on_the_device_through_the_service():
+    """The default: requests with top-k / top-p are sampled on the device (and decoded one step ahead).
+    Every token is one of the k most likely of the plain implementation at its place, the run repeats
+    with its seed and differs with another."""
+    from air_b200 import GenerationConfig, SamplingConfig
+    folder = util.model_folder("B")
+    cfg, tensors = util.plain_model(folder)
+    prompt = util.tokens_for("B", 9, 31)
+
+    def run(seed):
+        svc = service("B", "float32")
+        g = GenerationConfig(max_new_tokens=14, stop_on_eos=False,
+                             sampling=SamplingConfig(temperature=1.3, top_k=5, top_p=0.95, seed=seed))
+        out = svc.generate(prompt, g).tokens
+        assert svc._inflight is None and svc.engine.cache.free_pages() == svc.engine.cache.num_pages
+        return out
+
+    a, b, c = run(3), run(3), run(4)
+    assert a == b and a != c
+    logits = plain.forward(cfg, tensors, prompt + a)[len(prompt) - 1:-1]
+    for row, token in zip(logits, a):
+        assert token in np.argsort(-row, kind="stable")[:5]
+
+
 def test_host_sampler_path_with_top_k_and_top_p():
     from air_b200 import GenerationConfig, SamplingConfig
     folder = util.model_folder("A")
     cfg, tensors = util.plain_model(folder)
-    svc = service("A", "float32")
+    svc = service("A", "float32", sample_cuts_on_device=False)
     prompt = util.tokens_for("A", 6, 1)
     sampling = SamplingConfig(temperature=0.9, top_k=7, top_p=0.8, seed=11)
     got = svc.generate(prompt, GenerationConfig(max_new_tokens=8, stop_on_eos=False, sampling=sampling)).tokens

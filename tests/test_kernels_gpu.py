@@ -282,6 +282,47 @@ def test_temperature_sampling_follows_the_distribution_and_the_uniform_number():
     assert out3[0].item() == out3[2].item() == int(row.argmax())
 
 
+def kept_like_the_host_sampler(row, temp, k, p):
+    """The indices that AIR's sampler keeps (src/runtime/sampling.cpp:23-53): weights exp((x - max) / T), a
+    stable descending sort, the k largest (0: all), then the shortest prefix whose weights reach p of the
+    remaining total (at least one)."""
+    w = np.exp((row.astype(np.float64) - row.max()) / temp)
+    order = np.argsort(-w, kind="stable")
+    if k and k < order.size:
+        order = order[:k]
+    if p < 1.0:
+        total, cum, keep = w[order].sum(), 0.0, 0
+        for i in order:
+            cum += w[i]
+            keep += 1
+            if cum >= p * total:
+                break
+        order = order[:keep]
+    return np.sort(order), w
+
+
+@pytest.mark.parametrize("k,p", [(0, 0.8), (7, 1.0), (50, 0.6), (3, 0.999), (1, 0.5), (0, 0.05), (2000, 0.9)])
+def test_top_k_and_top_p_on_the_device_keep_what_the_host_sampler_keeps(k, p):
+    """Draws with many uniform numbers: every drawn index is one that AIR's sampler keeps, every kept index
+    is drawn, and the index is where the cumulative weight of the kept indices (in index order) passes the
+    uniform number.  The logits have ties at the cut's value, which a stable sort keeps in index order."""
+    V, R, temp = 1500, 3000, 0.8
+    g = torch.Generator().manual_seed(k * 10 + int(p * 100))
+    row = (torch.randn(V, generator=g) * 2).round(decimals=1)          # one decimal: many exact ties
+    kept, w = kept_like_the_host_sampler(row.numpy(), temp, k, p)
+    u = torch.rand(R, generator=g)
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops().sample(dev(row.repeat(R, 1)), dev(torch.full((R,), temp)), dev(u), out,
+                 top_k=dev(torch.full((R,), k, dtype=torch.int32)), top_p=dev(torch.full((R,), p)))
+    got = out.cpu().numpy()
+    assert set(got.tolist()) <= set(kept.tolist()), "an index outside the kept set was drawn"
+    if len(kept) <= 60:
+        assert set(got.tolist()) == set(kept.tolist()), "a kept index was never drawn"
+    cdf = np.cumsum(w[kept]) / w[kept].sum()
+    want = kept[np.minimum(np.searchsorted(cdf, u.double().numpy()), len(kept) - 1)]
+    assert (got == want).mean() > 0.97
+
+
 def test_kernels_refuse_what_they_cannot_take():
     o = ops()
     q = torch.zeros(2, 2, 24, device="cuda")
