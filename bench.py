@@ -47,10 +47,27 @@ def peaks():
         try:
             with open(path) as f:
                 d = json.load(f)
-            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
-        except (ValueError, KeyError):
+            return {"hbm_gbs": _figure(d, "hbm_gbs"), "bf16_tflops": _figure(d, "bf16_tflops"), "source": "measured"}
+        except (ValueError, KeyError, TypeError):
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
+
+
+def _figure(record, key):
+    """A peak from the record: a number, or an object that holds it under 'value' (or the key's own name); the
+    key may also lie one level down (under 'peaks', say)."""
+    if key not in record:
+        for inner in record.values():
+            if isinstance(inner, dict) and key in inner:
+                record = inner
+                break
+    v = record[key]
+    if isinstance(v, dict):
+        v = v["value"] if "value" in v else v[key]
+    v = float(v)
+    if not v > 0:
+        raise ValueError(key)
+    return v
 
 
 class ClockSampler:
