@@ -54,6 +54,9 @@ class StepContext:
                                                 # in groups of 16 per request, filled up with rows = 0
     decode_prefix: int = 0                      # so many leading tokens are single next tokens of their requests;
                                                 # the tiles cover the tokens after them
+    residual: Optional[torch.Tensor] = None     # [T, hidden] float32, set by the block that runs: a mixer or a
+                                                # feed-forward may add its output into it (in 32-bit) and return
+                                                # None instead of returning the output for the next norm to add
 
 
 def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepContext:

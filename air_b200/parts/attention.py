@@ -116,4 +116,9 @@ class Attention(Mixer):
         else:
             ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         out = out.view(T, H * d)
-        return self.o.partial(out) if self.o.small(out) else self.o(out, torch.float32)
+        if self.o.small(out):
+            return self.o.partial(out)
+        residual = getattr(ctx, "residual", None)
+        if self.o.adds_into(out, residual):
+            return self.o.add_into(out, residual)
+        return self.o(out, torch.float32)

@@ -12,7 +12,10 @@ class PreNormBlock:
 
     The residual stream h is float32.  Each addition is fused into the norm that follows
     it: the block receives the previous block's output still pending, and hands its own
-    feed-forward output on in the same way; the model's final norm adds the last one."""
+    feed-forward output on in the same way; the model's final norm adds the last one.  A part may
+    instead add its output into the stream itself (StepContext.residual) and return None: with
+    many rows the library's product does that addition in its epilogue, in 32-bit, and the norm
+    that follows reads the stream alone."""
 
     def __init__(self, spec: BlockSpec):
         self.spec = spec
@@ -36,7 +39,8 @@ class PreNormBlock:
         return self.mixer.cache_needs()
 
     def forward(self, h, pending, ctx, cache, owns_cache=True):
+        ctx.residual = h
         x = self.mixer_norm.forward(h, pending)
-        a = self.mixer.forward(x, ctx, cache, owns_cache)
+        a = self.mixer.forward(x, ctx, cache, owns_cache)      # None: the mixer has added its output to h itself
         x = self.ff_norm.forward(h, a)
         return h, self.feed_forward.forward(x, ctx)

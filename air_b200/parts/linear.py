@@ -78,6 +78,17 @@ class Linear:
         out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
         return ops.gemm_tc(x, self.weight, out, 2 * self.gate_up_block, ops.EPI_SILU, status=self.status)
 
+    def adds_into(self, x: torch.Tensor, residual) -> bool:
+        """Whether add_into() applies: 16-bit weights, a float32 stream of this product's shape."""
+        return (residual is not None and self.weight.dtype != torch.float32 and x.dtype == self.weight.dtype
+                and x.is_cuda and residual.dtype == torch.float32
+                and tuple(residual.shape) == (x.shape[0], self.out_features))
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor) -> None:
+        """residual += x W^T, the sum taken in 32-bit in the library product's epilogue (the product is not
+        rounded to 16 bits first, and is not written and read again by the norm that follows)."""
+        torch.addmm(residual, x, self.weight.t(), out_dtype=torch.float32, out=residual)
+
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype, bias=None) -> torch.Tensor:
         w = self.weight
         if w.dtype == torch.float32:

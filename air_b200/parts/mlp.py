@@ -64,4 +64,9 @@ class SwiGLU(FeedForward):
             gu = self.gate_up(x, torch.float32 if self.rt.is_fp32 else self.rt.dtype)
             act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
             ops.silu_mul(gu, act, block=self.block)
-        return self.down.partial(act) if self.down.small(act) else self.down(act, torch.float32)
+        if self.down.small(act):
+            return self.down.partial(act)
+        residual = getattr(ctx, "residual", None)
+        if self.down.adds_into(act, residual):
+            return self.down.add_into(act, residual)
+        return self.down(act, torch.float32)

@@ -70,6 +70,19 @@ def test_swiglu_part(dtype):
     want = plain.swiglu(x.float().numpy(), n["f.gate_proj.weight"], n["f.up_proj.weight"], n["f.down_proj.weight"])
     assert out.dtype == torch.float32
     assert np.abs(out.cpu().numpy() - want).max() < (1e-5 if dtype == "float32" else 2e-2) * np.abs(want).max()
+    if dtype == "bfloat16":
+        # many rows and a residual stream in the context: the output is added into the stream (in 32-bit),
+        # nothing is handed on
+        from types import SimpleNamespace
+        x = torch.randn(150, 80, generator=torch.Generator().manual_seed(2)).to(DT[dtype])
+        stream = torch.randn(150, 80, generator=torch.Generator().manual_seed(3))
+        h = stream.clone().cuda()
+        assert part.forward(x.cuda(), SimpleNamespace(residual=h)) is None
+        want = stream.numpy() + plain.swiglu(x.float().numpy(), n["f.gate_proj.weight"], n["f.up_proj.weight"],
+                                             n["f.down_proj.weight"])
+        assert np.abs(h.cpu().numpy() - want).max() < 2e-2 * np.abs(want).max()
+        handed_on = part.forward(x.cuda(), None)            # without a stream: as before
+        assert np.abs(stream.numpy() + handed_on.cpu().numpy() - want).max() < 2e-2 * np.abs(want).max()
 
 
 @pytest.mark.parametrize("heads,kv,d,window", [(6, 2, 48, None), (5, 5, 16, 9), (4, 1, 80, None)])
