@@ -111,6 +111,51 @@ def test_bfloat16_heads_of_64_and_128_take_the_tensor_core_kernels(name):
     assert {"decode_attention", "prefill_attention"} <= ran and "attention_ref" not in ran
 
 
+def random_configuration(rng):
+    """A tiny configuration drawn at random: heads of 16 to 256 in groups of 1 to 7, widths that follow from
+    them, any feed-forward width and vocabulary, with or without windowed layers."""
+    d = int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 256]))
+    kv = int(rng.choice([1, 2, 3, 4]))
+    heads = kv * int(rng.choice([1, 2, 3, 5, 7]))
+    while heads * d > 1024:
+        d = int(rng.choice([16, 32, 48, 64]))
+    layers = int(rng.integers(1, 4))
+    return dict(util.BASE, num_hidden_layers=layers, hidden_size=heads * d, num_attention_heads=heads,
+                num_key_value_heads=kv, intermediate_size=int(rng.integers(8, 80)) * int(rng.choice([2, 4, 8, 16])),
+                vocab_size=int(rng.integers(40, 900)), max_position_embeddings=512,
+                rope_theta=float(rng.choice([1e4, 5e4, 1e6])), rms_norm_eps=float(rng.choice([1e-6, 1e-5, 3e-6])),
+                tie_word_embeddings=bool(rng.random() < 0.5), use_sliding_window=bool(rng.random() < 0.4),
+                sliding_window=int(rng.integers(5, 200)), max_window_layers=int(rng.integers(0, layers + 1)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(6))
+def test_random_configurations_and_traces(seed, dtype):
+    """Sizes, page size, number of live requests, portions and lengths all drawn at random; the pool holds just
+    what the trace needs, so pages are used again."""
+    from air_b200.engine.engine import write_random_model
+    from plain import qwen2_plain as plain
+    rng = np.random.default_rng(7000 + seed)
+    cfg = random_configuration(rng)
+    with tempfile.TemporaryDirectory() as folder:
+        write_random_model(folder, cfg, seed, "bfloat16")
+        lengths = [int(x) for x in rng.integers(1, 330, size=int(rng.integers(3, 8)))]
+        streams = {f"r{i}": rng.integers(0, cfg["vocab_size"], size=m).tolist() for i, m in enumerate(lengths)}
+        steps = util.trace_mixed(streams, seed=seed, live=int(rng.integers(1, 5)), tail=int(rng.integers(1, 20)),
+                                 portions=tuple(int(x) for x in rng.integers(2, 90, size=6)))
+        page = int(rng.choice([16, 32, 64, 128]))
+        got, _ = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps, page=page), page_tokens=page)
+        pcfg, tensors = plain.read_model(folder)
+        for rid, toks in streams.items():
+            ref = plain.forward(pcfg, tensors, list(toks))
+            scale = max(1.0, float(np.abs(ref).max()))
+            err = np.stack([np.abs(got[(rid, p)] - ref[p]) for p in range(len(toks))])
+            if dtype == "float32":
+                assert err.max() < util.FP32_TOL * scale, cfg
+            else:
+                assert err.max() < util.BF16_MAX_TOL * scale and err.mean(1).max() < util.BF16_MEAN_TOL * scale, cfg
+
+
 def test_trace_run_program_writes_files_and_done_lines():
     folder = util.model_folder("B")
     streams = {"x": util.tokens_for("B", 70, 11), "y": util.tokens_for("B", 45, 12)}
