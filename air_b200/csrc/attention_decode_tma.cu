@@ -13,6 +13,13 @@
 // The cache [page, 2, K, P, D] is addressed as a matrix of rows of D elements; a 64-key tile is
 // 64 / min(P, 64) boxes of min(P, 64) rows, each found through the block table.
 // Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 5.
+//
+// With `fresh.qkv` the kernel also does what qkv_rope_store does for its token (elementwise.cu): it adds up
+// the partial sums of the q/k/v product and the bias, rotates q and k by the table's row of the token's
+// position, keeps q in shared memory, and writes k and v to the page.  The blocks whose tiles hold the
+// token's own position do not wait for that write to be visible to the copy engine: they put the two new
+// rows into the tile in shared memory once it has landed.  A decode step is then one launch shorter per
+// layer, and the keys start to stream as soon as the product has ended.
 #include "common.cuh"
 #include "mma.cuh"
 #include "tma.cuh"
@@ -24,9 +31,21 @@ constexpr int DT_THREADS = (DT_CONSUMERS + 1) * 32;
 constexpr int DT_TILE = 64;     // keys per stage
 constexpr int DT_STAGES = 3;
 
+// The token's new q, k and v as the product left them (see the head of the file); qkv == nullptr: q is read
+// from `q`, and k and v are in the cache already.
+struct FreshQkv {
+    const float* qkv;        // [parts][T][(H + 2 K) D] partial sums
+    int parts;
+    size_t part_stride;
+    const float* bias;       // [(H + 2 K) D] or nullptr
+    const float* table;      // [positions][D]: cos | sin
+    __nv_bfloat16* cache;    // where k and v are written (nullptr: another run has written them)
+};
+
 template <int D>
 __global__ void __launch_bounds__(DT_THREADS)
-decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const __nv_bfloat16* __restrict__ q,
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const FreshQkv fresh,
+                            const __nv_bfloat16* __restrict__ q,
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
                             const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                             float* __restrict__ part_o, float* __restrict__ part_ml, int H, int K, int P, int window,
@@ -41,6 +60,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
     uint64_t* full = (uint64_t*)(smem + DT_STAGES * STAGE_BYTES);
     uint64_t* empty = full + DT_STAGES;
     volatile int* abort_flag = (volatile int*)(empty + DT_STAGES);
+    __nv_bfloat16* sm_q = (__nv_bfloat16*)((uint8_t*)(empty + DT_STAGES) + 64);   // [16][D], with fresh.qkv
+    __nv_bfloat16* sm_kv = sm_q + 16 * D;                                          // [2][D]: the new k and v rows
     float* sm_o = (float*)smem;                              // after the walk: [warps][16][D]
     float* sm_m = sm_o + DT_CONSUMERS * 16 * D;              // [warps][16]
     float* sm_l = sm_m + DT_CONSUMERS * 16;
@@ -128,19 +149,106 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
         // ------------------------------------------------------------ consumers: 16 keys of every tile each
         const int r0 = hb * 16 + g, r1 = r0 + 8;
         uint32_t qa[KS][4];
+        const int own_tile = pos / DT_TILE;           // the tile that holds the token's own key
+        const bool patch = fresh.qkv && fresh.cache && own_tile >= begin && own_tile < end;
+        if (fresh.qkv) {
+            // this block's query heads, and k and v where its tiles hold the new key: items of four pairs
+            // (i, i + D/2), as in qkv_rope_store_vec4_kernel
+            constexpr int HALF = D / 2, PER_HEAD = HALF / 4;
+            const int width = (H + 2 * K) * D;
+            const int nq = min(16, G - hb * 16);
+            const int heads = nq + (patch ? 2 : 0);
+            const float* in = fresh.qkv + (size_t)t * width;
+            const float* cs = fresh.table + (size_t)pos * D;
+            __nv_bfloat16* kdst = nullptr;
+            if (patch && hb == 0) {
+                const int page = bt[pos / P];
+                if (page < 0) {
+                    if (threadIdx.x == 0 && status) atomicExch(status, 2);
+                } else {
+                    kdst = fresh.cache + ((size_t)page * 2 * K * P + (size_t)kvh * P + (size_t)(pos % P)) * D;
+                }
+            }
+            for (int idx = threadIdx.x; idx < heads * PER_HEAD; idx += DT_CONSUMERS * 32) {
+                const int hh = idx / PER_HEAD, j = (idx % PER_HEAD) * 4;
+                const int col = (hh < nq ? kvh * G + hb * 16 + hh : (hh == nq ? H + kvh : H + K + kvh)) * D;
+                float a[4], b[4];
+                load4(in + col + j, a);
+                load4(in + col + HALF + j, b);
+                for (int part = 1; part < fresh.parts; ++part) {
+                    float x[4], y[4];
+                    load4(in + part * fresh.part_stride + col + j, x);
+                    load4(in + part * fresh.part_stride + col + HALF + j, y);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
+                }
+                if (fresh.bias) {
+                    float x[4], y[4];
+                    load4(fresh.bias + col + j, x);
+                    load4(fresh.bias + col + HALF + j, y);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
+                }
+                if (hh <= nq) {                       // q and k are rotated, v is not
+                    float c[4], sn[4];
+                    load4(cs + j, c);
+                    load4(cs + HALF + j, sn);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float ra = a[e] * c[e] - b[e] * sn[e], rb = a[e] * sn[e] + b[e] * c[e];
+                        a[e] = ra;
+                        b[e] = rb;
+                    }
+                }
+                __nv_bfloat16* dst = hh < nq ? sm_q + hh * D : sm_kv + (hh - nq) * D;
+                store4(dst + j, a);
+                store4(dst + HALF + j, b);
+                if (hh >= nq && kdst) {
+                    __nv_bfloat16* gdst = kdst + (hh == nq ? (size_t)0 : (size_t)K * P * D);
+                    store4(gdst + j, a);
+                    store4(gdst + HALF + j, b);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(DT_CONSUMERS * 32) : "memory");
+        }
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk) {
-            const __nv_bfloat16* q0 = q + ((size_t)t * H + kvh * G + r0) * D + 16 * kk + 2 * tq;
-            const __nv_bfloat16* q1 = q + ((size_t)t * H + kvh * G + r1) * D + 16 * kk + 2 * tq;
-            qa[kk][0] = r0 < G ? __ldg(reinterpret_cast<const uint32_t*>(q0)) : 0u;
-            qa[kk][1] = r1 < G ? __ldg(reinterpret_cast<const uint32_t*>(q1)) : 0u;
-            qa[kk][2] = r0 < G ? __ldg(reinterpret_cast<const uint32_t*>(q0 + 8)) : 0u;
-            qa[kk][3] = r1 < G ? __ldg(reinterpret_cast<const uint32_t*>(q1 + 8)) : 0u;
+            if (fresh.qkv) {
+                const __nv_bfloat16* q0 = sm_q + g * D + 16 * kk + 2 * tq;
+                const __nv_bfloat16* q1 = q0 + 8 * D;
+                qa[kk][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0) : 0u;
+                qa[kk][1] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1) : 0u;
+                qa[kk][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + 8) : 0u;
+                qa[kk][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1 + 8) : 0u;
+            } else {
+                const __nv_bfloat16* q0 = q + ((size_t)t * H + kvh * G + r0) * D + 16 * kk + 2 * tq;
+                const __nv_bfloat16* q1 = q + ((size_t)t * H + kvh * G + r1) * D + 16 * kk + 2 * tq;
+                qa[kk][0] = r0 < G ? __ldg(reinterpret_cast<const uint32_t*>(q0)) : 0u;
+                qa[kk][1] = r1 < G ? __ldg(reinterpret_cast<const uint32_t*>(q1)) : 0u;
+                qa[kk][2] = r0 < G ? __ldg(reinterpret_cast<const uint32_t*>(q0 + 8)) : 0u;
+                qa[kk][3] = r1 < G ? __ldg(reinterpret_cast<const uint32_t*>(q1 + 8)) : 0u;
+            }
         }
         const int mat = lane >> 3, mrow = lane & 7;   // ldmatrix: which 8x8 matrix this lane addresses, which row
+        bool alive = true;
         for (int it = 0; it < n_tiles; ++it) {
             const int stage = it % DT_STAGES;
-            if (!mbar_wait(&full[stage], (it / DT_STAGES) & 1, abort_flag)) break;
+            // (a warp whose wait ran out goes on without work, so that it still meets the others at the barrier below)
+            if (alive && !mbar_wait(&full[stage], (it / DT_STAGES) & 1, abort_flag)) alive = false;
+            if (patch && begin + it == own_tile) {
+                // the token's own k and v: into their row of the tile (what the copy brought there is older)
+                const int row = pos - own_tile * DT_TILE;
+                if (alive && threadIdx.x < 2 * (D / 8)) {
+                    const int which = threadIdx.x / (D / 8), c = threadIdx.x % (D / 8);
+                    const uint4 val = *reinterpret_cast<const uint4*>(sm_kv + which * D + c * 8);
+                    const uint32_t at = swizzled(smem_u32(smem + stage * STAGE_BYTES) + (which * SUB + c / 8) * SUB_BYTES,
+                                                 row, c % 8);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(val.x), "r"(val.y),
+                                 "r"(val.z), "r"(val.w) : "memory");
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(DT_CONSUMERS * 32) : "memory");
+            }
+            if (!alive) continue;
             const int kbase = (begin + it) * DT_TILE + 16 * warp;     // this warp's 16 keys
             if (kbase <= pos && kbase + 15 >= lo) {
                 const uint32_t kt = smem_u32(smem + stage * STAGE_BYTES);
@@ -263,17 +371,17 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
 }
 
 template <int D>
-int launch_decode_tma(const CUtensorMap& map, const void* q, const int* block_table, int max_blocks,
+int launch_decode_tma(const CUtensorMap& map, const FreshQkv& fresh, const void* q, const int* block_table, int max_blocks,
                       const int* token_seq, const int* positions, void* out, float* part_o, float* part_ml, int T,
                       int H, int K, int P, int window, float scale, int splits, int* status, cudaStream_t stream) {
     const int head_blocks = (H / K + 15) / 16;
     const size_t ring = (size_t)DT_STAGES * 2 * (D / 64) * DT_TILE * 128;
     const size_t merge = (size_t)(DT_CONSUMERS * 16 * D + 2 * DT_CONSUMERS * 16) * sizeof(float);
-    const size_t smem = 1024 + (ring > merge ? ring : merge) + 128;
+    const size_t smem = 1024 + (ring > merge ? ring : merge) + 128 + (fresh.qkv ? (size_t)18 * D * 2 : 0);
     auto kernel = decode_attention_tma_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return launch(kernel, dim3(splits, K * head_blocks, T), DT_THREADS, smem, stream, map, (const __nv_bfloat16*)q,
+    return launch(kernel, dim3(splits, K * head_blocks, T), DT_THREADS, smem, stream, map, fresh, (const __nv_bfloat16*)q,
                   block_table, max_blocks, token_seq, positions, (__nv_bfloat16*)out, part_o, part_ml, H, K, P, window,
                   scale * 1.4426950408889634f, status);
 }
@@ -284,13 +392,12 @@ int launch_decode_tma(const CUtensorMap& map, const void* q, const int* block_ta
 extern "C" int air_decode_combine(const float* part_o, const float* part_ml, const int* token_seq, void* out, int T,
                                   int H, int D, int splits, cudaStream_t stream);
 
-// Arguments as air_decode_attention (attention_decode.cu), plus the number of pages of the cache
-// (its first dimension) and the status word.
-AIR_API int air_decode_attention_tma(const void* q, const void* cache, long long pages, const int* block_table,
-                                     int max_blocks, const int* token_seq, const int* positions, void* out,
-                                     float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
-                                     float scale, int splits, int* status, cudaStream_t stream) {
-    using namespace air;
+namespace air {
+
+static int decode_attention_tma(const FreshQkv& fresh, const void* q, const void* cache, long long pages,
+                                const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                void* out, float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
+                                float scale, int splits, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || splits < 1 || T > 65535 ||
         (splits > 1 && (!part_o || !part_ml)) || ((uintptr_t)cache & 15))
@@ -309,22 +416,51 @@ AIR_API int air_decode_attention_tma(const void* q, const void* cache, long long
     int rc;
     switch (D) {
         case 64:
-            rc = launch_decode_tma<64>(map, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
-                                       K, P, window, scale, splits, status, stream);
+            rc = launch_decode_tma<64>(map, fresh, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml,
+                                       T, H, K, P, window, scale, splits, status, stream);
             break;
         case 128:
-            rc = launch_decode_tma<128>(map, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
-                                        K, P, window, scale, splits, status, stream);
+            rc = launch_decode_tma<128>(map, fresh, q, block_table, max_blocks, token_seq, positions, out, part_o,
+                                        part_ml, T, H, K, P, window, scale, splits, status, stream);
             break;
         case 256:
-            rc = launch_decode_tma<256>(map, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,
-                                        K, P, window, scale, splits, status, stream);
+            rc = launch_decode_tma<256>(map, fresh, q, block_table, max_blocks, token_seq, positions, out, part_o,
+                                        part_ml, T, H, K, P, window, scale, splits, status, stream);
             break;
         default:
             return AIR_ERR_BAD_ARGUMENT;
     }
     if (rc == 0 && splits > 1) rc = air_decode_combine(part_o, part_ml, token_seq, out, T, H, D, splits, stream);
     return rc;
+}
+
+}  // namespace air
+
+// Arguments as air_decode_attention (attention_decode.cu), plus the number of pages of the cache
+// (its first dimension) and the status word.
+AIR_API int air_decode_attention_tma(const void* q, const void* cache, long long pages, const int* block_table,
+                                     int max_blocks, const int* token_seq, const int* positions, void* out,
+                                     float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
+                                     float scale, int splits, int* status, cudaStream_t stream) {
+    return air::decode_attention_tma(air::FreshQkv{nullptr, 0, 0, nullptr, nullptr, nullptr}, q, cache, pages,
+                                     block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H, K, D, P,
+                                     window, scale, splits, status, stream);
+}
+
+// The same from the q/k/v product's output instead of q: qkv float32 [parts][T][(H + 2 K) D] (partial sums that
+// are added in order), bias float32 or null, table float32 [positions][D] (cos | sin: all of a head is
+// rotated); write_kv = 0 where another run's layer has written this step's keys and values already.
+AIR_API int air_decode_attention_tma_fresh(const float* qkv, int parts, const float* bias, const float* table,
+                                           int write_kv, void* cache, long long pages, const int* block_table,
+                                           int max_blocks, const int* token_seq, const int* positions, void* out,
+                                           float* part_o, float* part_ml, int T, int H, int K, int D, int P,
+                                           int window, float scale, int splits, int* status, cudaStream_t stream) {
+    if (!qkv || !table || parts < 1 || ((uintptr_t)qkv & 15) || ((uintptr_t)bias & 15) || ((uintptr_t)table & 15))
+        return AIR_ERR_BAD_ARGUMENT;
+    const air::FreshQkv fresh{qkv, parts, (size_t)T * (size_t)(H + 2 * K) * (size_t)D, bias, table,
+                              write_kv ? (__nv_bfloat16*)cache : nullptr};
+    return air::decode_attention_tma(fresh, nullptr, cache, pages, block_table, max_blocks, token_seq, positions, out,
+                                     part_o, part_ml, T, H, K, D, P, window, scale, splits, status, stream);
 }
 
 AIR_API int air_trace_set_attention_decode_tma(unsigned long long* buffer) { return air::set_trace_here(buffer); }

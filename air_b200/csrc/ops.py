@@ -37,6 +37,9 @@ _SIGNATURES = {
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                  c_void_p],
+    "air_decode_attention_tma_fresh": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "air_prefill_attention_tc": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -343,6 +346,51 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
             positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P, int(window or 0), float(scale),
             splits, _stream()), "decode_attention")
     if splits > 1:
+        launches += 1
+    return out
+
+
+def decode_attention_fresh_ok(qkv, table, cache, head_dim) -> bool:
+    """Whether decode_attention_fresh takes this: float32 product output, a table that rotates all of a head,
+    pages that the copy engine's tiles fit."""
+    return (qkv.dtype == torch.float32 and head_dim in DECODE_HEAD_DIMS and table is not None
+            and table.shape[1] == head_dim and cache.dtype == torch.bfloat16 and tile_pages(cache.shape[3]))
+
+
+def decode_attention_fresh(qkv, bias, table, cache, block_table, token_seq, positions, out, heads, window, scale,
+                           write_kv=True, splits=None, status=None):
+    """bfloat16 attention for one query token per request, straight from the q/k/v product: qkv float32
+    [T, (H + 2K) d] or [parts, T, (H + 2K) d] partial sums; the kernel adds the bias, rotates q and k by the
+    table's row of each token's position, writes k and v to the pages (write_kv) and attends, which
+    qkv_rope_store followed by decode_attention do in two launches (attention_decode_tma.cu)."""
+    T, H = qkv.shape[-2], heads
+    d, K, P = cache.shape[4], cache.shape[2], cache.shape[3]
+    width = (H + 2 * K) * d
+    parts = 1 if qkv.dim() == 2 else qkv.shape[0]
+    _req(qkv, "qkv", (torch.float32,), (T, width) if qkv.dim() == 2 else (parts, T, width))
+    if bias is not None:
+        _req(bias, "bias", (torch.float32,), (width,))
+    _req(table, "table", (torch.float32,), (None, d))
+    _req(cache, "cache", (torch.bfloat16,), (None, 2, None, None, d))
+    _req(block_table, "block_table", _I32)
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(positions, "positions", _I32, (T,))
+    _req(out, "out", (torch.bfloat16,), (T, H, d))
+    if not decode_attention_fresh_ok(qkv, table, cache, d):
+        raise KernelError("decode_attention_fresh: head size, rotary width or page size that this kernel does not take")
+    if splits is None:
+        splits = decode_splits(T, H, K)
+    po = pm = None
+    if splits > 1:
+        po = torch.empty(T * H * splits * d, dtype=torch.float32, device=qkv.device)
+        pm = torch.empty(T * H * splits * 2, dtype=torch.float32, device=qkv.device)
+    _check(_get("air_decode_attention_tma_fresh")(
+        qkv.data_ptr(), parts, _ptr(bias), table.data_ptr(), 1 if write_kv else 0, cache.data_ptr(), cache.shape[0],
+        block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(),
+        _ptr(po), _ptr(pm), T, H, K, d, P, int(window or 0), float(scale), splits, _ptr(status), _stream()),
+        "decode_attention_tma")
+    if splits > 1:
+        global launches
         launches += 1
     return out
 

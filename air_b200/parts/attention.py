@@ -91,9 +91,18 @@ class Attention(Mixer):
             # this run reads another run's keys and values: only q is computed
             qkv = torch.zeros((T, (H + 2 * K) * d), dtype=torch.float32, device=x.device)
             qkv[:, : H * d] = self.q_only(x, torch.float32)
-        q = torch.empty((T, H, d), dtype=rt.dtype, device=x.device)
         bt = ctx.block_tables[pages.group]
-        ops.qkv_rope_store(qkv, self.bias, self.position.table(), ctx.positions, ctx.token_seq, bt, q, pages.kv,
+        table = self.position.table()
+        if (rt.dtype == torch.bfloat16 and ctx.all_decode
+                and ops.decode_attention_fresh_ok(qkv, table, pages.kv, d)):
+            # single next tokens only: the attention kernel itself adds the bias, rotates, writes the new keys
+            # and values and attends (one launch less, and the keys stream as soon as the product has ended)
+            out = torch.empty((T, H, d), dtype=rt.dtype, device=x.device)
+            ops.decode_attention_fresh(qkv, self.bias, table, pages.kv, bt, ctx.token_seq, ctx.positions, out, H,
+                                       self.window, self.scale, write_kv=owns_cache, status=ctx.status)
+            return self._project(out.view(T, H * d), ctx)
+        q = torch.empty((T, H, d), dtype=rt.dtype, device=x.device)
+        ops.qkv_rope_store(qkv, self.bias, table, ctx.positions, ctx.token_seq, bt, q, pages.kv,
                            H, K, d, write_kv=owns_cache, status=ctx.status)
         out = torch.empty_like(q)
         if rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.all_decode:
@@ -115,7 +124,9 @@ class Attention(Mixer):
                 ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
         else:
             ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
-        out = out.view(T, H * d)
+        return self._project(out.view(T, H * d), ctx)
+
+    def _project(self, out, ctx):
         if self.o.small(out):
             return self.o.partial(out)
         residual = getattr(ctx, "residual", None)

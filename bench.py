@@ -177,7 +177,7 @@ def decode_timeline(engine, requests, torch, Entry, LAST):
     # one layer from the middle of the step, kernel by kernel
     names = [ops.TRACE_NAMES[k] for _, k in step]
     for i in range(len(step) // 2, len(step) - 10):
-        if names[i:i + 3] == ["add_rmsnorm", "gemm_tc", "qkv_rope_store"]:
+        if names[i:i + 2] == ["add_rmsnorm", "gemm_tc"] and names[i + 2] in ("qkv_rope_store", "decode_attention"):
             j = next((j for j in range(i + 3, len(step) - 1) if names[j:j + 3] == names[i:i + 3]), None)
             if j is not None:
                 print("  one layer (us): " + " | ".join(f"{names[q]} {(step[q + 1][0] - step[q][0]) / 1e3:.1f}"

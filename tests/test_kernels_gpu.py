@@ -398,6 +398,57 @@ def test_decode_attention(H, K, d, P, window, splits, engine):
     assert (got[~keep] == 7.0).all()
 
 
+@pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (40, 2, 64, 32), (8, 1, 256, 16), (4, 4, 128, 128)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_decode_attention_from_the_product(H, K, d, P, window, splits):
+    """The decode kernel that takes the q/k/v product's partial sums (adds them and the bias, rotates, writes the
+    new keys and values, attends) against the two kernels that do the same one after the other; the place of
+    the new key in the cache holds other numbers beforehand, so a kernel that attended to what the copy
+    engine brought would show.  Contexts that end at a tile's first and last row and in the middle of a page."""
+    from air_b200.parts.rope import RopeHalf
+    from air_b200.parts.spec import PartSpec
+    from air_b200.parts.base import Runtime
+    lens = [700, 1, 64, 65, 333, 128, 17]
+    _, cache, bt, positions, seq_of, _, _ = paged_case(H, K, d, P, lens, [1] * len(lens), "bfloat16", seed=H + splits,
+                                                       num_pages=120)
+    positions = np.insert(positions, 2, 0).astype(np.int32)        # a padded token in the middle is skipped
+    seq_of = np.insert(seq_of, 2, -1).astype(np.int32)
+    T, width = len(positions), (H + 2 * K) * d
+    g = torch.Generator().manual_seed(d + window)
+    qkv = (torch.randn(3, T, width, generator=g) * 0.6).cuda()
+    bias = torch.randn(width, generator=g).cuda()
+    pe = RopeHalf(PartSpec("rope_half", {"rotary_dim": d, "theta": 10000.0, "max_positions": 1024}))
+    pe.load({}, Runtime(torch.device("cuda"), torch.bfloat16, P))
+    o = ops()
+    args = (dev(bt), dev(seq_of), dev(positions))
+    scale = 1.0 / math.sqrt(d)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # one after the other
+    cache_two = dev(cache, torch.bfloat16)
+    q = torch.zeros(T, H, d, dtype=torch.bfloat16, device="cuda")
+    o.qkv_rope_store(qkv, bias, pe.table(), args[2], args[1], args[0], q, cache_two, H, K, d, status=status)
+    want = torch.full((T, H, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    o.decode_attention(q, cache_two, *args, want, window, scale, splits=splits, status=status)
+    # in one
+    cache_one = dev(cache, torch.bfloat16)
+    got = torch.full((T, H, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    o.decode_attention_fresh(qkv, bias, pe.table(), cache_one, *args, got, H, window, scale, splits=splits, status=status)
+    assert status.item() == 0
+    assert float((cache_one.float() - cache_two.float()).abs().max()) <= 1e-2 * float(cache_two.float().abs().max())
+    assert not torch.equal(cache_one, dev(cache, torch.bfloat16))
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2 * max(1.0, float(want.float().abs().max()))
+    assert (got[2] == 7.0).all()
+    # a run that reads another run's cache: nothing is written, the keys are the ones that lie there
+    cache_read = cache_two.clone()
+    got2 = torch.empty((T, H, d), dtype=torch.bfloat16, device="cuda")
+    o.decode_attention_fresh(qkv, bias, pe.table(), cache_read, *args, got2, H, window, scale, write_kv=False,
+                             splits=splits, status=status)
+    assert torch.equal(cache_read, cache_two)
+    keep = torch.from_numpy(seq_of >= 0).cuda()
+    assert float((got2.float() - want.float())[keep].abs().max()) <= 2e-2 * max(1.0, float(want.float().abs().max()))
+
+
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 1000, 2047])
 def test_decode_attention_finds_one_far_key(far):
     H, K, d, P, n = 14, 2, 128, 64, 2048
