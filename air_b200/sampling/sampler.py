@@ -7,11 +7,12 @@
 sorted descending, cut to top_k, cut to the shortest prefix whose share reaches top_p, and one
 draw of std::uniform_real_distribution<double>(0, total) from std::mt19937_64(seed).
 
-On the device (air_b200/csrc/sampling.cu) the engine samples greedy and plain temperature
-requests without bringing logits to the host: the request's generator supplies the uniform
-number and the kernel walks the weights in index order instead of sorted order, which gives
-the same distribution but not the same token as AIR for a given seed.  Requests with top_k or
-top_p are sampled by `HostSampler` from logits copied to the host.
+On the device (air_b200/csrc/sampling.cu) the engine samples without bringing logits to the
+host: the request's generator supplies the uniform number, the kernel cuts to top_k and top_p
+as AIR does and draws.  Without a cut it walks the weights in index order instead of sorted
+order, and its weights are 32-bit, so the distribution is AIR's but the token for a given seed
+need not be.  With `SchedulerConfig.sample_cuts_on_device = False` requests with top_k or top_p
+are sampled by `HostSampler` from logits copied to the host, which gives AIR's token per seed.
 """
 from __future__ import annotations
 
