@@ -253,10 +253,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 }
 
 // Merges the splits of one (token, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
-// The kernel is a chain of latencies, so a thread asks for eight splits' values at once (and for the
-// token's slot beside them: a padding token has its place in the buffers too) and folds them into a
-// running maximum, sum and value, in the order of the splits.
-template <int D>
+// The kernel is a chain of latencies, so a thread asks for CHUNK splits' values at once (all of them, up
+// to 32; and for the token's slot beside them: a padding token has its place in the buffers too) and
+// folds them into a running maximum, sum and value, in the order of the splits.
+template <int D, int CHUNK>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       const int* __restrict__ token_seq, __nv_bfloat16* __restrict__ out, int H,
                                       int splits) {
@@ -266,10 +266,10 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
     const int slot = token_seq[t];
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
         float mm = -INFINITY, ll = 0.f, acc = 0.f;
-        for (int s0 = 0; s0 < splits; s0 += 8) {
-            float m[8], l[8], o[8];
+        for (int s0 = 0; s0 < splits; s0 += CHUNK) {
+            float m[CHUNK], l[CHUNK], o[CHUNK];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < CHUNK; ++i) {
                 const bool in = s0 + i < splits;
                 const float2 ml = in ? *reinterpret_cast<const float2*>(part_ml + (base + s0 + i) * 2)
                                      : make_float2(-INFINITY, 0.f);
@@ -279,13 +279,13 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
             }
             float top = mm;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) top = fmaxf(top, m[i]);
+            for (int i = 0; i < CHUNK; ++i) top = fmaxf(top, m[i]);
             if (top == -INFINITY) continue;            // nothing seen yet
             const float keep = exp2f(mm - top);         // 0 while mm is -inf
             ll *= keep;
             acc *= keep;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < CHUNK; ++i) {
                 if (m[i] == -INFINITY) continue;        // (its values are not looked at: they may be anything)
                 const float w = exp2f(m[i] - top);
                 ll += l[i] * w;
@@ -295,6 +295,21 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
         }
         if (slot >= 0) out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll);
     }
+}
+
+// The merge kernel with all of a thread's loads in one round where the splits are up to 32.
+template <int D>
+int launch_combine(const float* part_o, const float* part_ml, const int* token_seq, __nv_bfloat16* out, int T, int H,
+                   int splits, cudaStream_t stream) {
+    const int threads = D >= 128 ? 128 : 64;
+    if (splits <= 8)
+        return launch(decode_combine_kernel<D, 8>, dim3(H, T), threads, 0, stream, part_o, part_ml, token_seq, out, H,
+                      splits);
+    if (splits <= 16)
+        return launch(decode_combine_kernel<D, 16>, dim3(H, T), threads, 0, stream, part_o, part_ml, token_seq, out, H,
+                      splits);
+    return launch(decode_combine_kernel<D, 32>, dim3(H, T), threads, 0, stream, part_o, part_ml, token_seq, out, H,
+                  splits);
 }
 
 template <int D>
@@ -316,8 +331,7 @@ int launch_decode(const void* q, const void* cache, const int* block_table, int 
                     block_table, max_blocks, token_seq, positions, (__nv_bfloat16*)out, part_o, part_ml, H, K, P,
                     window, scale * 1.4426950408889634f);
     if (rc == 0 && splits > 1)
-        rc = launch(decode_combine_kernel<D>, dim3(H, T), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
-                    (const float*)part_ml, token_seq, (__nv_bfloat16*)out, H, splits);
+        rc = launch_combine<D>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream);
     return rc;
 }
 
@@ -351,17 +365,10 @@ AIR_API int air_decode_combine(const float* part_o, const float* part_ml, const 
                                int H, int D, int splits, cudaStream_t stream) {
     using namespace air;
     switch (D) {
-        case 64:
-            return launch(decode_combine_kernel<64>, dim3(H, T), 64, 0, stream, part_o, part_ml, token_seq,
-                          (__nv_bfloat16*)out, H, splits);
-        case 128:
-            return launch(decode_combine_kernel<128>, dim3(H, T), 128, 0, stream, part_o, part_ml, token_seq,
-                          (__nv_bfloat16*)out, H, splits);
-        case 256:
-            return launch(decode_combine_kernel<256>, dim3(H, T), 128, 0, stream, part_o, part_ml, token_seq,
-                          (__nv_bfloat16*)out, H, splits);
-        default:
-            return AIR_ERR_BAD_ARGUMENT;
+        case 64: return launch_combine<64>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream);
+        case 128: return launch_combine<128>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream);
+        case 256: return launch_combine<256>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream);
+        default: return AIR_ERR_BAD_ARGUMENT;
     }
 }
 
