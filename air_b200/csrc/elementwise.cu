@@ -151,6 +151,68 @@ __global__ void add_rmsnorm_vec4_many_kernel(float* __restrict__ h, const TD* __
     }
 }
 
+// For many rows of moderate width: a row is held in the registers of a small block (up to NV vectors of four
+// per thread), so that it is read once, there is one block-wide sum and many blocks fit on an SM.
+template <typename TD, typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(256) add_rmsnorm_vec4_held_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                                                    int parts, size_t part_stride,
+                                                                    const TW* __restrict__ w, TO* __restrict__ out,
+                                                                    const int* __restrict__ rows, int E, float eps) {
+    __shared__ float scratch[NV * 8];
+    pdl_enter(TR_NORM);
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * E;
+    float x[NV][4];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = (v * blockDim.x + threadIdx.x) * 4;
+        if (i < E) load4(h + src + i, x[v]);
+    }
+    for (int p = 0; p < parts; ++p) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const int i = (v * blockDim.x + threadIdx.x) * 4;
+            if (i < E) {
+                float d[4];
+                load4(delta + p * part_stride + src + i, d);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[v][j] += d[j];
+            }
+        }
+    }
+    // The sum of squares in the order of the kernel for few rows, so that a row's result does not depend on how
+    // many rows are beside it (up to 4,096 wide, where that kernel has one vector per thread): four squares per
+    // vector, a warp's 32 vectors by the shuffle tree, the warps one after the other.
+    const int warps = blockDim.x >> 5;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = (v * blockDim.x + threadIdx.x) * 4;
+        float sv = 0.f;
+        if (i < E) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sv += x[v][j] * x[v][j];
+            if (!rows && parts > 0) store4(h + src + i, x[v]);
+        }
+        sv = warp_sum(sv);
+        if ((threadIdx.x & 31) == 0) scratch[v * warps + (threadIdx.x >> 5)] = sv;
+    }
+    __syncthreads();
+    float total = 0.f;
+    for (int k = 0; k < (E / 4 + 31) / 32; ++k) total += scratch[k];
+    const float scale = rsqrtf(total / (float)E + eps);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = (v * blockDim.x + threadIdx.x) * 4;
+        if (i < E) {
+            float wv[4], y[4];
+            load4(w + i, wv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[j] = x[v][j] * scale * wv[j];
+            store4(out + (size_t)r * E + i, y);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- bias + rotary + cache write
 // qkv [T, (H + 2K) d] is the output of the fused projection.  For every token: add the
 // bias, rotate the heads of q and k with the table's cos/sin of the token's position
@@ -501,6 +563,12 @@ AIR_API int air_add_rmsnorm(float* h, const void* delta, int delta_dtype, int pa
     int threads = E >= 2048 ? 512 : 256;
     AIR_DISPATCH(delta_dtype, TD, AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
         if (E % 4 == 0) {
+            if (R > 64 && E <= 8192) {
+                // many rows: each held in the registers of 128 threads (up to 4,096 wide) or 256
+                const int held = E <= 4096 ? 128 : 256;
+                return launch(add_rmsnorm_vec4_held_kernel<TD, TW, TO, 8>, R, held, 0, stream, h, (const TD*)delta, parts,
+                              (size_t)h_rows * E, (const TW*)w, (TO*)out, rows, E, eps);
+            }
             if (R <= 64) threads = min(1024, max(128, (E / 4 + 31) / 32 * 32));   // few rows: one access per thread
             auto kernel = R <= 64 ? add_rmsnorm_vec4_kernel<TD, TW, TO> : add_rmsnorm_vec4_many_kernel<TD, TW, TO>;
             if (smem > 48 * 1024)
