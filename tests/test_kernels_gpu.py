@@ -103,24 +103,26 @@ def rope_reference(x, positions, theta, rot):
     return y
 
 
-@pytest.mark.parametrize("H,K,d,rot", [(5, 1, 48, 48), (6, 3, 80, 80), (4, 2, 128, 64), (3, 3, 16, 16)])
+@pytest.mark.parametrize("H,K,d,rot", [(5, 1, 48, 48), (6, 3, 80, 80), (4, 2, 128, 64), (3, 3, 16, 16), (28, 4, 128, 128),
+                                       (40, 8, 128, 128)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_qkv_rope_store(H, K, d, rot, dtype):
+@pytest.mark.parametrize("n0,n1", [(14, 9), (70, 40)])       # (few tokens and many take different kernels)
+def test_qkv_rope_store(H, K, d, rot, dtype, n0, n1):
     from air_b200.parts.rope import RopeHalf
     from air_b200.parts.spec import PartSpec
     from air_b200.parts.base import Runtime
-    P, T, theta = 16, 23, 12345.0
+    P, T, theta = 16, n0 + n1, 12345.0
     rng = np.random.default_rng(d)
     qkv = rng.standard_normal((T, (H + 2 * K) * d)).astype(np.float32)
     bias = rng.standard_normal((H + 2 * K) * d).astype(np.float32)
-    # two requests: tokens 0..13 of request 0 at positions 30..43, tokens 14..22 of request 1 at 0..8
-    positions = np.array(list(range(30, 44)) + list(range(9)), dtype=np.int32)
-    token_seq = np.array([0] * 14 + [1] * 9, dtype=np.int32)
-    block_table = np.array([[7, 2, 9], [4, -1, -1]], dtype=np.int32)
-    pe = RopeHalf(PartSpec("rope_half", {"rotary_dim": rot, "theta": theta, "max_positions": 64}))
+    # two requests: the first tokens are request 0's at positions 30.., the others request 1's at 0..
+    positions = np.array(list(range(30, 30 + n0)) + list(range(n1)), dtype=np.int32)
+    token_seq = np.array([0] * n0 + [1] * n1, dtype=np.int32)
+    block_table = np.array([[7, 2, 9, 0, 11, 5, 3], [4, 8, 1, -1, -1, -1, -1]], dtype=np.int32)
+    pe = RopeHalf(PartSpec("rope_half", {"rotary_dim": rot, "theta": theta, "max_positions": 128}))
     pe.load({}, Runtime(torch.device("cuda"), DT[dtype], P))
     q_out = torch.zeros(T, H, d, dtype=DT[dtype], device="cuda")
-    cache = torch.zeros(10, 2, K, P, d, dtype=DT[dtype], device="cuda")
+    cache = torch.zeros(12, 2, K, P, d, dtype=DT[dtype], device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     ops().qkv_rope_store(dev(qkv), dev(bias), pe.table(), dev(positions), dev(token_seq), dev(block_table),
                          q_out, cache, H, K, d, status=status)
