@@ -207,3 +207,37 @@ def test_cancellation_while_queued_and_while_active():
     assert svc.snapshot()["cancelled_requests"] == 2
     assert eng.cache.free_pages() == eng.cache.num_pages
     eng.cache.check()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_requests_and_settings_keep_every_promise(seed):
+    """Random settings (places, budget, portion size, pages, with and without reservation) and random
+    requests over the fake engine: every request gets exactly its tokens (the fake's next token is
+    predictable), no step exceeds the budget or the places, and every page and slot comes back."""
+    rng = np.random.default_rng(100 + seed)
+    places = int(rng.integers(1, 6))
+    budget = int(rng.integers(places, 40))
+    quantum = int(rng.integers(1, 24))
+    reserve = bool(rng.random() < 0.5)
+    reqs = []
+    for _ in range(int(rng.integers(3, 16))):
+        first = int(rng.integers(0, 40))
+        prompt = [int(t) for t in rng.integers(0, 48, size=int(rng.integers(0, 30)))] + [first]
+        reqs.append((prompt, GenerationConfig(max_new_tokens=int(rng.integers(0, 12)), stop_on_eos=False)))
+    largest = max(-(-(len(p) + g.max_new_tokens) // 16) for p, g in reqs)
+    eng = FakeEngine(pages=largest + int(rng.integers(0, 6)), slots=places)
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=places, token_budget_per_cycle=budget,
+                                                prefill_quantum_tokens=quantum, kv_page_tokens=16,
+                                                reserve_worst_case=reserve, decode_ahead=False))
+    out = svc.generate_cohort(reqs)
+    for (prompt, g), r in zip(reqs, out):
+        assert r.error is None
+        assert r.tokens == [(prompt[-1] + 1 + i) % 50 for i in range(g.max_new_tokens)]
+        assert r.metrics.prompt_tokens == len(prompt) and r.metrics.generated_tokens == g.max_new_tokens
+    for step in eng.steps:
+        assert sum(n for _, n, _ in step) <= budget and len(step) <= places
+        assert len({r for r, _, _ in step}) == len(step), "a request appears once in a step"
+    while svc.run_cycle():
+        pass
+    assert eng.cache.free_pages() == eng.cache.num_pages and not eng.cache.sequences
+    eng.cache.check()
