@@ -14,7 +14,8 @@ A "step" is one decode step of the whole batch.  It prints ONE JSON line:
   prefill    one step of 2,048 prompt tokens of one request; frac = flops / time / bf16 peak
   roofline   bytes the decode step has to read (every weight once, the live requests' cache)
              / its time, against the measured copy bandwidth
-  points     decode tokens per second at batch 1 and 64
+  points     decode tokens per second at batch 1 and 64 (points_roofline_frac: their share of the
+             copy bandwidth, counted as for roofline)
 The cache of the decoding requests is filled with random keys and values instead of running
 64 prompts of 8,192 tokens (data: synthetic); timing does not depend on the values.  Between
 timed steps nothing is flushed: a step reads its weights (over 14 GB at 28 layers), far more
@@ -341,8 +342,10 @@ def main():
 
     main_r = results[args.batch]
     ms = main_r["ms"]
-    live_kv = args.batch * (args.context - (args.steps + args.warmup + 2) // 2) * kv_bytes_per_token
-    achieved = (weight_bytes + live_kv) / (ms / 1e3) / 1e9
+    def bytes_a_second(batch):        # what a decode step at this batch has to read, over its time (GB/s)
+        live = batch * (args.context - (args.steps + args.warmup + 2) // 2) * kv_bytes_per_token
+        return (weight_bytes + live) / (results[batch]["ms"] / 1e3) / 1e9
+    achieved = bytes_a_second(args.batch)
     line = {
         "metric": "decode tok/s at batch 8 (Qwen2.5-7B shape, bf16, random weights)",
         "value": args.batch / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
@@ -360,6 +363,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": {f"decode_b{b}": b / (results[b]["ms"] / 1e3) for b in batches if b != args.batch},
+        "points_roofline_frac": {f"decode_b{b}": bytes_a_second(b) / pk["hbm_gbs"] for b in batches if b != args.batch},
     }
     print(json.dumps(line))
     return 0
