@@ -30,6 +30,7 @@ constexpr int DT_CONSUMERS = 4;
 constexpr int DT_THREADS = (DT_CONSUMERS + 1) * 32;
 constexpr int DT_TILE = 64;     // keys per stage
 constexpr int DT_STAGES = 3;
+constexpr int FRESH_PARTS = 4;  // partial sums of the q/k/v product that a thread asks for at once
 
 // The token's new q, k and v as the product left them (see the head of the file); qkv == nullptr: q is read
 // from `q`, and k and v are in the cache already.
@@ -172,27 +173,42 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
             for (int idx = threadIdx.x; idx < heads * PER_HEAD; idx += DT_CONSUMERS * 32) {
                 const int hh = idx / PER_HEAD, j = (idx % PER_HEAD) * 4;
                 const int col = (hh < nq ? kvh * G + hb * 16 + hh : (hh == nq ? H + kvh : H + K + kvh)) * D;
-                float a[4], b[4];
+                // all of the item's loads are asked for at once (up to FRESH_PARTS partial sums, the bias, the
+                // table's row): with few tiles to stream this chain of latencies is what the block waits for
+                float a[4], b[4], pa[FRESH_PARTS - 1][4], pb[FRESH_PARTS - 1][4];
+                float ba[4] = {0.f, 0.f, 0.f, 0.f}, bb[4] = {0.f, 0.f, 0.f, 0.f}, c[4], sn[4];
                 load4(in + col + j, a);
                 load4(in + col + HALF + j, b);
-                for (int part = 1; part < fresh.parts; ++part) {
+#pragma unroll
+                for (int part = 1; part < FRESH_PARTS; ++part)
+                    if (part < fresh.parts) {
+                        load4(in + part * fresh.part_stride + col + j, pa[part - 1]);
+                        load4(in + part * fresh.part_stride + col + HALF + j, pb[part - 1]);
+                    }
+                if (fresh.bias) {
+                    load4(fresh.bias + col + j, ba);
+                    load4(fresh.bias + col + HALF + j, bb);
+                }
+                if (hh <= nq) {
+                    load4(cs + j, c);
+                    load4(cs + HALF + j, sn);
+                }
+#pragma unroll
+                for (int part = 1; part < FRESH_PARTS; ++part)
+                    if (part < fresh.parts) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) { a[e] += pa[part - 1][e]; b[e] += pb[part - 1][e]; }
+                    }
+                for (int part = FRESH_PARTS; part < fresh.parts; ++part) {
                     float x[4], y[4];
                     load4(in + part * fresh.part_stride + col + j, x);
                     load4(in + part * fresh.part_stride + col + HALF + j, y);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
                 }
-                if (fresh.bias) {
-                    float x[4], y[4];
-                    load4(fresh.bias + col + j, x);
-                    load4(fresh.bias + col + HALF + j, y);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) { a[e] += x[e]; b[e] += y[e]; }
-                }
+                for (int e = 0; e < 4; ++e) { a[e] += ba[e]; b[e] += bb[e]; }
                 if (hh <= nq) {                       // q and k are rotated, v is not
-                    float c[4], sn[4];
-                    load4(cs + j, c);
-                    load4(cs + HALF + j, sn);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const float ra = a[e] * c[e] - b[e] * sn[e], rb = a[e] * sn[e] + b[e] * c[e];
