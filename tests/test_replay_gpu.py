@@ -111,6 +111,27 @@ def test_bfloat16_heads_of_64_and_128_take_the_tensor_core_kernels(name):
     assert {"decode_attention", "prefill_attention"} <= ran and "attention_ref" not in ran
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["K", "L"])
+def test_eighty_requests_decode_in_one_step(name, dtype):
+    """More single tokens in a step than the kernels for few rows take (64): the decode graph of the next
+    bucket with the library's products, the output and down products adding into the stream, the attention
+    kernel starting from the q/k/v product in one part."""
+    folder = util.model_folder(name)
+    streams = {f"r{i}": util.tokens_for(name, 9 + i % 5, 300 + i) for i in range(80)}
+    ids = list(streams)
+    steps, n = [], 0
+    for i in range(0, 80, 8):                      # the prompts, eight requests a step, all but the last 4 tokens
+        steps.append(util.step_line(n, [(r, streams[r][:-4], range(len(streams[r]) - 4)) for r in ids[i:i + 8]]))
+        n += 1
+    for k in range(4, 0, -1):                      # then four steps of 80 single tokens
+        steps.append(util.step_line(n, [(r, [streams[r][-k]], [0]) for r in ids], end=ids if k == 1 else []))
+        n += 1
+    got, _ = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps, page=16), page_tokens=16,
+                         max_requests=96)
+    util.check_against_plain(got, folder, streams, dtype)
+
+
 def random_configuration(rng):
     """A tiny configuration drawn at random: heads of 16 to 256 in groups of 1 to 7, widths that follow from
     them, any feed-forward width and vocabulary, with or without windowed layers."""
