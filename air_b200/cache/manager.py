@@ -5,9 +5,13 @@ AIR's CUDA cache allocates a device page per request on demand, all layers in on
 and keeps a table of page pointers per sequence (src/cuda/cuda_backend.cu:1186-1433).  Here
 the memory is one slab per layer made at start, pages are numbers, and:
 
-* Runs of layers with the same need (kv heads, head size, window) form a *group*.  A group
-  has its own pool of pages and its own block table per request; page n of a group is row
-  n of every run's slab in that group.
+* What a run keeps is described by its mixer's needs (air_b200.parts.base.CacheNeed).  The
+  manager knows no kinds of need: a paged need states the shape of one page of it and whether
+  old pages may go back (a window), a need that is not paged states the shape of its per-request
+  state; the mixer receives what the need's `view` makes of the memory.
+* Runs with paged needs of the same group key (for keys and values: kv heads, head size, window)
+  form a *group*.  A group has its own pool of pages and its own block table per request; page n
+  of a group is row n of every run's slab in that group.
 * A page belongs to one request from `reserve` until the request is closed, or, in a group
   with a window, until every key in it is older than the window of any future query.
   Freed pages go back on the pool's stack and are handed out again at once.
@@ -24,7 +28,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts.base import PagedKV, SlotState
+from ..parts.base import CacheNeed, PagedKV, PagedKVView, SlotState, SlotStateView  # noqa: F401 (views: old import path)
 
 
 class OutOfPages(RuntimeError):
@@ -90,24 +94,9 @@ class PagePool:
 
 
 @dataclass
-class PagedKVView:
-    """What a mixer gets for a PagedKV need: its slab [pages, 2, kv_heads, page_tokens, head_dim]
-    and the index of its group (for the step's block table)."""
-    kv: Optional[torch.Tensor]
-    group: int
-    need: PagedKV
-
-
-@dataclass
-class SlotStateView:
-    """What a mixer gets for a SlotState need: [slots, *shape]; row = the request's slot."""
-    state: Optional[torch.Tensor]
-    need: SlotState
-
-
-@dataclass
 class Group:
-    need: PagedKV
+    key: Hashable                 # the needs' group key
+    window: Optional[int]         # None: every page is kept until the request ends
     pool: PagePool
     runs: List[int] = field(default_factory=list)
 
@@ -140,23 +129,21 @@ class CacheManager:
         for run, needs in enumerate(needs_per_run):
             views = []
             for need in needs:
-                if isinstance(need, PagedKV):
+                if not isinstance(need, CacheNeed):
+                    raise CacheError(f"run {run}: {need!r} is not a cache need")
+                memory, g = None, None
+                if need.paged:
                     g = self._group_of(need)
-                    self.groups[g].runs.append(run)
-                    kv = None
+                    if run not in self.groups[g].runs:
+                        self.groups[g].runs.append(run)
                     if allocate:
-                        kv = torch.zeros((num_pages, 2, need.kv_heads, page_tokens, need.head_dim),
-                                         dtype=dtype, device=device)
-                    views.append(PagedKVView(kv, g, need))
-                elif isinstance(need, SlotState):
-                    st = None
-                    if allocate:
-                        st = torch.zeros((max_requests,) + tuple(need.shape), dtype=getattr(torch, need.dtype),
-                                         device=device)
-                        self._state_tensors.append(st)
-                    views.append(SlotStateView(st, need))
-                else:
-                    raise CacheError(f"run {run}: unknown cache need {need!r}")
+                        memory = torch.zeros((num_pages,) + tuple(need.page_shape(page_tokens)),
+                                             dtype=need.element_dtype(dtype), device=device)
+                elif allocate:
+                    memory = torch.zeros((max_requests,) + tuple(need.slot_shape()),
+                                         dtype=need.element_dtype(dtype), device=device)
+                    self._state_tensors.append(memory)
+                views.append(need.view(memory, g))
             self._views.append(tuple(views))
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.sequences: Dict[Hashable, Sequence_] = {}
@@ -173,12 +160,19 @@ class CacheManager:
                                if allocate else None)
             self._updates.append({})
 
-    def _group_of(self, need: PagedKV) -> int:
+    def _group_of(self, need: CacheNeed) -> int:
+        key = need.group_key()
         for i, g in enumerate(self.groups):
-            if g.need == need:
+            if g.key == key:
                 return i
-        self.groups.append(Group(need, PagePool(self.num_pages)))
+        self.groups.append(Group(key, need.window, PagePool(self.num_pages)))
         return len(self.groups) - 1
+
+    @staticmethod
+    def bytes_per_page(needs_per_run: Sequence[Sequence[object]], page_tokens: int, dtype: torch.dtype) -> int:
+        """Device bytes that one page number costs over all runs (every run has a slab of its own)."""
+        return sum(need.bytes_per_page(page_tokens, dtype) for needs in needs_per_run for need in needs
+                   if getattr(need, "paged", False))
 
     # ------------------------------------------------------------------ what mixers see
     def views(self, run: int):
@@ -210,11 +204,11 @@ class CacheManager:
     def pages_needed(self, tokens: int) -> int:
         return -(-tokens // self.page_tokens)
 
-    def _first_live_block(self, need: PagedKV, length: int) -> int:
-        """Blocks below this hold only keys that no query at position >= length can see."""
-        if need.window is None:
+    def _first_live_block(self, window: Optional[int], length: int) -> int:
+        """Blocks below this hold only tokens that no query at position >= length can see."""
+        if window is None:
             return 0
-        return max(0, length - need.window + 1) // self.page_tokens
+        return max(0, length - window + 1) // self.page_tokens
 
     def reserve(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
         """Makes room for `n` more tokens of each request in the batch: all of it or none."""
@@ -248,7 +242,7 @@ class CacheManager:
         if self.groups and seq.length > len(seq.pages[0]) * self.page_tokens:
             raise CacheError(f"request {request!r} holds fewer pages than its length needs")
         for gi, g in enumerate(self.groups):
-            first = self._first_live_block(g.need, seq.length)
+            first = self._first_live_block(g.window, seq.length)
             pages = seq.pages[gi]
             for b in range(min(first, len(pages))):
                 if pages[b] >= 0:

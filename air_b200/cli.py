@@ -4,7 +4,7 @@ place of text since the engine has no tokenizer:
   air-b200 inspect <model-dir> [--tensors]
   air-b200 cuda-info
   air-b200 cuda <model-dir> <ids,comma,separated> [--tokens N] [--device N] [--dtype bfloat16|float32]
-                [--temperature T] [--top-k K] [--top-p P] [--seed S] [--no-stop-on-eos]
+                [--temperature T] [--top-k K] [--top-p P] [--seed S] [--no-stop-on-eos] [--keep-float32]
   air-b200 cuda-compare <model-dir> <ids> [--device N] [--atol X]
   air-b200 random <config.json> <out-dir> [--seed S] [--dtype bfloat16|float32]
 
@@ -85,10 +85,10 @@ def _inspect(args) -> int:
         return 2
     try:
         cfg = load_config(rest[0])
-    except ConfigError as e:
+        model = Model(registry.architecture(cfg.architecture).build_spec(cfg))
+    except ValueError as e:       # ConfigError: a data error, or a size that the engine does not take
         print(e, file=sys.stderr)
         return 3
-    model = Model(registry.architecture(cfg.architecture).build_spec(cfg))
     specs = model.tensor_specs()
     params = sum(int(__import__("math").prod(s.shape)) for s in specs)
     print(json.dumps({"architecture": cfg.architecture, "config": cfg.to_dict(), "tensors": len(specs),
@@ -111,15 +111,20 @@ def _cuda_info() -> int:
     return 0
 
 
-def _load(folder, dtype, device, max_tokens):
+def _load(folder, dtype, device, max_tokens, keep_float32=False):
     from .config import ConfigError
     from .engine.engine import Engine, EngineConfig, parse_dtype
     from .weights.loader import WeightError
     from .weights.safetensors_io import SafetensorsError
     try:
-        return Engine.from_folder(folder, EngineConfig(dtype=parse_dtype(dtype), max_tokens=max_tokens,
-                                                       device=f"cuda:{device}"))
-    except (ConfigError, WeightError, SafetensorsError) as e:
+        engine = Engine.from_folder(folder, EngineConfig(dtype=parse_dtype(dtype), max_tokens=max_tokens,
+                                                         device=f"cuda:{device}", keep_float32=keep_float32))
+        if engine.load_report is not None and engine.load_report.summary():
+            print("note: " + engine.load_report.summary(), file=sys.stderr)
+        return engine
+    except (ConfigError, WeightError, SafetensorsError, ValueError) as e:
+        # a model that cannot be loaded: bad or missing geometry, tensors that do not fit, or sizes that
+        # the kernels do not take ("unsupported"), as air-cli's exit code 3
         print(e, file=sys.stderr)
         raise SystemExit(3)
     except RuntimeError as e:
@@ -132,12 +137,14 @@ def _cuda(args) -> int:
     from .sampling.sampler import GenerationConfig, SamplingConfig
     opts, rest = _options(args, {"--tokens": (int, 32), "--device": (int, 0), "--dtype": (str, "bfloat16"),
                                  "--temperature": (float, 0.0), "--top-k": (int, 0), "--top-p": (float, 1.0),
-                                 "--seed": (int, 0), "--no-stop-on-eos": (bool, False)})
+                                 "--seed": (int, 0), "--no-stop-on-eos": (bool, False),
+                                 "--keep-float32": (bool, False)})
     if len(rest) != 2:
         print(USAGE, file=sys.stderr)
         return 2
     prompt = _ids(rest[1])
-    engine = _load(rest[0], opts["--dtype"], opts["--device"], len(prompt) + opts["--tokens"] + 64)
+    engine = _load(rest[0], opts["--dtype"], opts["--device"], len(prompt) + opts["--tokens"] + 64,
+                   opts["--keep-float32"])
     service = InferenceService(engine, SchedulerConfig(max_active_requests=engine.config.max_requests))
     try:
         response = service.generate(prompt, GenerationConfig(
@@ -148,6 +155,11 @@ def _cuda(args) -> int:
         return 7
     if response.error:
         print(response.error, file=sys.stderr)
+        return 7
+    try:
+        engine.check_status()       # once more before anything is printed: the last step's word
+    except RuntimeError as e:
+        print(e, file=sys.stderr)
         return 7
     print(",".join(str(t) for t in response.tokens))
     m = response.metrics

@@ -8,6 +8,11 @@ from ..parts.spec import BlockSpec, ModelSpec, PartSpec, RunStep
 from .model_config import Qwen2Config
 
 
+# what follows "model.layers.N." in the names of each part's tensors
+QWEN2_NAMES = {"mixer_norm": "input_layernorm.", "mixer": "self_attn.",
+               "feed_forward_norm": "post_attention_layernorm.", "feed_forward": "mlp."}
+
+
 def qwen2_spec(config: Qwen2Config) -> ModelSpec:
     """Qwen2ForCausalLM as AIR defines it (src/model/qwen2_contract.cpp:33-139) and
     computes it (src/reference/reference_executor.cpp:325-428): every layer is a pre-norm
@@ -22,12 +27,14 @@ def qwen2_spec(config: Qwen2Config) -> ModelSpec:
         norm = PartSpec("rms", {"size": e, "eps": config.rms_norm_eps})
         layers.append(BlockSpec(
             kind="pre_norm", prefix=f"model.layers.{i}.",
-            mixer=PartSpec("attention", {
-                "hidden": e, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
-                "head_dim": d, "qkv_bias": config.attention_bias, "window": config.layer_window(i),
-                "position": position}),
-            feed_forward=PartSpec("swiglu", {"hidden": e, "intermediate": config.intermediate_size}),
-            mixer_norm=norm, feed_forward_norm=norm))
+            parts={"mixer_norm": norm,
+                   "mixer": PartSpec("attention", {
+                       "hidden": e, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+                       "head_dim": d, "qkv_bias": config.attention_bias, "window": config.layer_window(i),
+                       "position": position}),
+                   "feed_forward_norm": norm,
+                   "feed_forward": PartSpec("swiglu", {"hidden": e, "intermediate": config.intermediate_size})},
+            names=QWEN2_NAMES))
     return ModelSpec(
         architecture=config.architecture, hidden_size=e, vocab_size=config.vocab_size,
         max_positions=config.max_position_embeddings, layers=tuple(layers),

@@ -8,8 +8,6 @@ inconsistent is a *data error*; a feature that the engine does not compute is
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import dataclass, field, asdict
 from typing import Any, Mapping, Optional
 
@@ -105,21 +103,6 @@ class Qwen2Config:
         )
         cfg.validate(raw=d)
         return cfg
-
-    @classmethod
-    def from_json_file(cls, path: str) -> "Qwen2Config":
-        if os.path.isdir(path):
-            path = os.path.join(path, "config.json")
-        try:
-            with open(path) as f:
-                d = json.load(f)
-        except FileNotFoundError:
-            raise ConfigError("data_error", f"no config.json at {path}")
-        except json.JSONDecodeError as e:
-            raise ConfigError("data_error", f"config.json is not valid JSON: {e}")
-        if not isinstance(d, dict):
-            raise ConfigError("data_error", "config.json must hold an object")
-        return cls.from_dict(d)
 
     def to_dict(self) -> dict:
         d = asdict(self)

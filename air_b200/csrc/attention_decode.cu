@@ -429,7 +429,9 @@ AIR_API int air_decode_attention_static(const void* q, const void* cache, const 
                                         const int* token_seq, const int* positions, void* out, int T, int H, int K,
                                         int D, int P, int window, float scale, int splits, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (splits < 1 || H <= 0 || D <= 0) return AIR_ERR_BAD_ARGUMENT;
+    // sizes that the kernel does not take are a bad argument, whatever their scratch would be
+    if (splits < 1 || H <= 0 || K <= 0 || H % K || P <= 0 || P % 16 || T > 65535 || (D != 64 && D != 128 && D != 256))
+        return AIR_ERR_BAD_ARGUMENT;
     const long long need = air_decode_attention_static_need(T, H, D, splits);
     if (need > AIR_STATIC_SCRATCH_FLOATS) return AIR_ERR_STATIC_SCRATCH;
     float* scratch = nullptr;
@@ -438,7 +440,9 @@ AIR_API int air_decode_attention_static(const void* q, const void* cache, const 
         if (rc != 0) return rc;
     }
     // Layout in the scratch: outputs [T*H*splits*D], then (max, sum) pairs [T*H*splits*2].  Nothing
-    // has to be cleared: every entry that the merge reads is written by this call's first kernel.
+    // has to be cleared: for every token that is not padding, the entries that the merge uses are written
+    // by this call's first kernel (a padding token's entries are whatever an earlier call left; the merge
+    // loads them and stores nothing).
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)T * H * splits * D : nullptr;
     return air_decode_attention(q, cache, block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H,

@@ -12,7 +12,7 @@ namespace air {
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  const int* __restrict__ last_token, float* __restrict__ out, int E, int V,
-                                 int* status) {
+                                 float multiplier, int* status) {
     pdl_enter(TR_EMBED);
     const int t = blockIdx.x;
     int id = ids[t];
@@ -20,7 +20,36 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
     const bool ok = id >= 0 && id < V;
     if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
     const TT* row = table + (size_t)(ok ? id : 0) * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)t * E + i] = ok ? to_float(row[i]) : 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x)
+        out[(size_t)t * E + i] = ok ? (multiplier == 1.f ? to_float(row[i]) : to_float(row[i]) * multiplier) : 0.f;
+}
+
+// ---------------------------------------------------------------- h += delta
+// h[t, i] += sum over parts of delta[part, t, i], the parts added in order (float32 stream; delta float32
+// or bfloat16).  The norm kernel below does this sum on its way; this is the sum alone, for a norm of
+// another kind that wants the stream complete before it starts.
+template <typename TD>
+__global__ void add_parts_kernel(float* __restrict__ h, const TD* __restrict__ delta, int parts, size_t n) {
+    pdl_enter(TR_NORM);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float x = h[i];
+        for (int p = 0; p < parts; ++p) x += to_float(delta[(size_t)p * n + i]);
+        h[i] = x;
+    }
+}
+
+// ---------------------------------------------------------------- what follows the output matrix
+// logits[r, v] = (logits[r, v] + bias[v]) * scale, then cap * tanh(. / cap) where cap > 0.  In place, float32.
+__global__ void logits_post_kernel(float* __restrict__ logits, const float* __restrict__ bias, float scale, float cap,
+                                   int V, size_t n) {
+    pdl_enter(TR_CONVERT);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float x = logits[i];
+        if (bias) x += bias[i % (size_t)V];
+        x *= scale;
+        if (cap > 0.f) x = cap * tanhf(x / cap);
+        logits[i] = x;
+    }
 }
 
 // ---------------------------------------------------------------- add + RMSNorm
@@ -545,11 +574,27 @@ __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, 
 using namespace air;
 
 AIR_API int air_embedding(const void* table, int table_dtype, const int* ids, const int* last_token, float* out,
-                          int T, int E, int V, int* status, cudaStream_t stream) {
+                          int T, int E, int V, float multiplier, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     AIR_DISPATCH(table_dtype, TT, return launch(embedding_kernel<TT>, T, 256, 0, stream, (const TT*)table, ids,
-                                                last_token, out, E, V, status));
+                                                last_token, out, E, V, multiplier, status));
     return 0;
+}
+
+AIR_API int air_add_parts(float* h, const void* delta, int delta_dtype, int parts, long long n, cudaStream_t stream) {
+    if (n <= 0 || parts <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    AIR_DISPATCH(delta_dtype, TD, return launch(add_parts_kernel<TD>, blocks, 256, 0, stream, h, (const TD*)delta,
+                                                parts, (size_t)n));
+    return 0;
+}
+
+AIR_API int air_logits_post(float* logits, const float* bias, float scale, float cap, int R, int V,
+                            cudaStream_t stream) {
+    const long long n = (long long)R * V;
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    return launch(logits_post_kernel, blocks, 256, 0, stream, logits, bias, scale, cap, V, (size_t)n);
 }
 
 // delta: `parts` tensors [rows of h, E] one after the other (parts = 0 or delta = null: none).

@@ -15,7 +15,9 @@
  * Arguments and result are those of air_decode_attention without the two scratch pointers: the
  * caller still passes the inputs (q [T,H,D] bf16, cache [page,2,K,P,D] bf16, block_table
  * [slots,max_blocks] int32, token_seq [T], positions [T]) and the output (out [T,H,D] bf16), all
- * device pointers.  It returns 0, a cudaError_t, or one of the AIR_ERR_* codes below;
+ * device pointers.  Sizes that the kernel does not take (a head size other than 64, 128, 256, heads
+ * that are no multiple of the kv heads, a page size that is no multiple of 16) are AIR_ERR_BAD_ARGUMENT
+ * (100001) whatever scratch they would need.  It returns 0, a cudaError_t, or one of the AIR_ERR_* codes;
  * air_decode_attention_static_error(code) gives the text.
  *
  * The scratch is a file-scope device array of AIR_STATIC_SCRATCH_FLOATS floats (8 MiB) that every
@@ -29,8 +31,9 @@
  * current) and keeps it; make that first call outside any stream capture.
  *
  * All calls share the one array, and it keeps what the last call left in it.  Nothing in it has to
- * be zero at the start of a call, because the first kernel of a call writes every entry that its
- * second kernel reads.  But two calls whose kernels may overlap on the GPU (different streams, or
+ * be zero at the start of a call: for every token that is not padding (token_seq >= 0) the first
+ * kernel of a call writes every entry that its second kernel uses; for a padding token the second
+ * kernel reads what an earlier call left there and stores nothing.  But two calls whose kernels may overlap on the GPU (different streams, or
  * different host threads without ordering) race on the array and corrupt each other's results:
  * run them in one stream, or order them with events.
  */

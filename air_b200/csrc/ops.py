@@ -16,7 +16,9 @@ _DT = {torch.float32: 0, torch.bfloat16: 1}
 c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
 _SIGNATURES = {
-    "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "air_add_parts": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p],
+    "air_logits_post": [c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p],
     "air_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                         c_longlong, c_float, c_void_p],
     "air_qkv_rope_store": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
@@ -141,8 +143,8 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
-def embedding(table, ids, out, status=None, last_token=None):
-    """out[t] = table[ids[t]] as float32; an id -(s+1) is replaced by last_token[s]."""
+def embedding(table, ids, out, status=None, last_token=None, multiplier=1.0):
+    """out[t] = table[ids[t]] * multiplier as float32; an id -(s+1) is replaced by last_token[s]."""
     V, E = table.shape
     _req(table, "table", _FLOATS)
     _req(ids, "ids", _I32, (out.shape[0],))
@@ -150,8 +152,30 @@ def embedding(table, ids, out, status=None, last_token=None):
     if last_token is not None:
         _req(last_token, "last_token", _I32)
     _check(_get("air_embedding")(table.data_ptr(), _DT[table.dtype], ids.data_ptr(), _ptr(last_token),
-                                 out.data_ptr(), out.shape[0], E, V, _ptr(status), _stream()), "embedding")
+                                 out.data_ptr(), out.shape[0], E, V, float(multiplier), _ptr(status), _stream()),
+           "embedding")
     return out
+
+
+def add_parts(h, delta):
+    """h += delta in place (float32 h [T, E]); delta [T, E] or partial sums [parts, T, E], added in order."""
+    _req(h, "h", (torch.float32,))
+    parts = 1 if delta.dim() == h.dim() else delta.shape[0]
+    _req(delta, "delta", _FLOATS, tuple(h.shape) if delta.dim() == h.dim() else (parts,) + tuple(h.shape))
+    _check(_get("air_add_parts")(h.data_ptr(), delta.data_ptr(), _DT[delta.dtype], parts, h.numel(), _stream()),
+           "add_parts")
+    return h
+
+
+def logits_post(logits, bias=None, scale=1.0, softcap=0.0):
+    """In place: logits = (logits + bias) * scale, then softcap * tanh(logits / softcap) where softcap > 0."""
+    R, V = logits.shape
+    _req(logits, "logits", (torch.float32,))
+    if bias is not None:
+        _req(bias, "bias", (torch.float32,), (V,))
+    _check(_get("air_logits_post")(logits.data_ptr(), _ptr(bias), float(scale), float(softcap), R, V, _stream()),
+           "logits_post")
+    return logits
 
 
 def add_rmsnorm(h, delta, weight, eps, out, rows=None):

@@ -12,10 +12,13 @@ pages through its slot.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence, Tuple
+from types import SimpleNamespace
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
+
+from ..parts.base import HostBatch
 
 
 LAST_SAMPLED = -1   # as a token: "the token that the device sampled last for this request"
@@ -50,46 +53,34 @@ class StepContext:
     max_kv_len: int = 0
     all_decode: bool = False
     last_token: Optional[torch.Tensor] = None   # [slots] int32: the device's last choice per request
-    tiles: Optional[torch.Tensor] = None        # [16n, 4] int32: (slot, first token, its position, rows <= 16),
-                                                # in groups of 16 per request, filled up with rows = 0
-    decode_prefix: int = 0                      # so many leading tokens are single next tokens of their requests;
-                                                # the tiles cover the tokens after them
+    plans: Dict[Hashable, SimpleNamespace] = field(default_factory=dict)
+                                                # what the parts planned for this step (Part.plan), by plan key:
+                                                # their int32 arrays as device tensors, their host values
     residual: Optional[torch.Tensor] = None     # [T, hidden] float32, set by the block that runs: a mixer or a
                                                 # feed-forward may add its output into it (in 32-bit) and return
                                                 # None instead of returning the output for the next norm to add
 
 
-def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepContext:
+def build_context(entries: Sequence[Entry], cache, device, status=None, planners=()) -> StepContext:
     """Packs the batch.  `cache` is the CacheManager; every request is open and has its pages
-    reserved for this step."""
+    reserved for this step.  `planners`: the parts of the model that plan on the host, one per plan
+    key (Model.planners()); their arrays travel in the same copy as the batch."""
     ids: List[np.ndarray] = []
     pos: List[np.ndarray] = []
     tseq: List[np.ndarray] = []
-    tiles: List[np.ndarray] = []
     q_start = [0]
     kv_len: List[int] = []
     slots: List[int] = []
+    lengths: List[int] = []
     rows: List[int] = []
     row_slots: List[int] = []
-    decode_prefix = 0
-    for index, e in enumerate(entries):
+    for e in entries:
         seq = cache.sequences[e.request]
         n = len(e.tokens)
-        if n == 1 and decode_prefix == index:
-            decode_prefix += 1      # single tokens at the head of the batch go to the decode kernels
         t = np.asarray(e.tokens, dtype=np.int64)
         ids.append(np.where(t >= 0, t, -(seq.slot + 1)).astype(np.int32))
         pos.append(np.arange(seq.length, seq.length + n, dtype=np.int32))
         tseq.append(np.full(n, seq.slot, dtype=np.int32))
-        # 16-token tiles in groups of 16 per request, filled up with empty ones
-        count = 0 if decode_prefix == index + 1 else -(-n // 16)
-        tile = np.zeros((-(-count // 16) * 16, 4), dtype=np.int32)
-        tile[:, 0] = seq.slot
-        first = np.arange(count, dtype=np.int32) * 16
-        tile[:count, 1] = q_start[-1] + first
-        tile[:count, 2] = seq.length + first
-        tile[:count, 3] = np.minimum(16, n - first)
-        tiles.append(tile.reshape(-1))
         for w in e.want:
             if not (0 <= w < n):
                 raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
@@ -97,13 +88,27 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
             row_slots.append(seq.slot)
         q_start.append(q_start[-1] + n)
         kv_len.append(seq.length + n)
+        lengths.append(seq.length)
         slots.append(seq.slot)
     T, S = q_start[-1], len(entries)
     cache.flush_tables()
     empty = np.zeros(0, dtype=np.int32)
     sections = [np.concatenate(x) if x else empty for x in (ids, pos, tseq)]
     sections += [np.asarray(x, dtype=np.int32) for x in (q_start, kv_len, slots, rows, row_slots)]
-    sections.append(np.concatenate(tiles) if tiles else empty)
+    planned = []      # (plan key, name, shape, section index), and the plans' host values
+    values = {}
+    if planners:
+        batch = HostBatch(counts=[len(e.tokens) for e in entries], lengths=lengths, slots=slots, q_start=q_start)
+        for part in planners:
+            plan = part.plan(batch)
+            if plan is None:
+                continue
+            key = part.plan_key()
+            values[key] = dict(plan.values)
+            for name, array in plan.arrays.items():
+                array = np.ascontiguousarray(array, dtype=np.int32)
+                planned.append((key, name, array.shape, len(sections)))
+                sections.append(array.reshape(-1))
     total = sum(len(x) for x in sections)
     host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
     view = host.numpy()
@@ -119,10 +124,13 @@ def build_context(entries: Sequence[Entry], cache, device, status=None) -> StepC
         o, n = spans[i]
         return dev[o:o + n]
 
+    plans = {key: SimpleNamespace(**v) for key, v in values.items()}
+    for key, name, shape, i in planned:
+        setattr(plans[key], name, cut(i).view(shape))
     return StepContext(
         num_tokens=T, num_seqs=S, token_ids=cut(0), positions=cut(1), token_seq=cut(2), q_start=cut(3),
         kv_len=cut(4), slots=cut(5), logit_rows=cut(6), row_slots=cut(7),
-        block_tables=list(cache.tables), tiles=cut(8).view(-1, 4),
+        block_tables=list(cache.tables), plans=plans,
         status=status, q_start_host=q_start, kv_len_host=kv_len, slots_host=slots,
         max_q_len=max((len(e.tokens) for e in entries), default=0), max_kv_len=max(kv_len, default=0),
-        all_decode=all(len(e.tokens) == 1 for e in entries), decode_prefix=decode_prefix)
+        all_decode=all(len(e.tokens) == 1 for e in entries))

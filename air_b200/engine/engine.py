@@ -12,10 +12,10 @@ from typing import Hashable, List, Optional, Sequence
 import torch
 
 from ..cache.manager import CacheManager, OutOfPages
-from ..config import load_config
+from ..config import ConfigError, load_config
 from ..parts import registry
 from ..parts.base import Runtime
-from ..weights.loader import load_tensors, random_tensors, write_model_folder
+from ..weights.loader import LoadReport, load_tensors, random_tensors, write_model_folder
 from ..csrc import ops
 from .batch import Entry, StepContext, build_context, LAST_SAMPLED
 from .model import Model
@@ -38,15 +38,21 @@ class StepError(RuntimeError):
 @dataclass
 class EngineConfig:
     """page_tokens: tokens per cache page.  max_tokens: how many tokens the cache pool holds
-    over all live requests (each request's count rounded up to whole pages).  max_requests:
-    live requests (state slots).  AIR: KvPolicy.page_tokens (include/air/execution.hpp:103-105)
-    and SchedulerConfig.max_active_requests (include/air/serving.hpp:46-62)."""
+    over all live requests (each request's count rounded up to whole pages); None sizes the pool
+    from the device memory that is free once the weights are resident, of which it takes the share
+    `memory_fraction` (AIR admits against free device memory plus pool bytes,
+    src/runtime/backend.cpp:538-556).  max_requests: live requests (state slots).  AIR:
+    KvPolicy.page_tokens (include/air/execution.hpp:103-105) and SchedulerConfig.max_active_requests
+    (include/air/serving.hpp:46-62).  keep_float32: matrices that the checkpoint stores in 32 bits stay
+    so in a bfloat16 engine (and run the CUDA-core product) instead of being rounded to bfloat16."""
     dtype: torch.dtype = torch.bfloat16
     page_tokens: int = 64
-    max_tokens: int = 8192
+    max_tokens: Optional[int] = 8192
     max_requests: int = 8
     device: str = "cuda:0"
     cuda_graphs: bool = True      # decode-only steps replay a captured graph
+    memory_fraction: float = 0.9
+    keep_float32: bool = False
 
 
 _BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -110,12 +116,19 @@ class DecodeGraph:
 
 class Engine:
     feeds_back_tokens = True     # Entry(request, [LAST_SAMPLED]) takes the device's last choice for the request
+    graph_sizes = _BUCKETS       # decode-only steps of up to so many requests replay a graph of the next size
 
     def __init__(self, model: Model, config: EngineConfig, model_config=None):
         self.model, self.config, self.model_config = model, config, model_config
         self.rt = model.rt
-        num_pages = max(1, -(-config.max_tokens // config.page_tokens))
+        self.load_report = None
+        if config.page_tokens <= 0 or config.page_tokens % 16:
+            raise ConfigError("unsupported", f"page size {config.page_tokens}: the cache takes positive multiples of 16")
         max_blocks = -(-model.spec.max_positions // config.page_tokens)
+        if config.max_tokens is None:
+            num_pages = self._pages_that_fit(model, config)
+        else:
+            num_pages = max(1, -(-config.max_tokens // config.page_tokens))
         self.cache = CacheManager(model.cache_needs(), config.page_tokens, num_pages, config.max_requests,
                                   dtype=self.rt.dtype, device=self.rt.device, max_blocks=max_blocks)
         self.status = self.rt.status if self.rt.status is not None else \
@@ -125,9 +138,24 @@ class Engine:
         self.steps = 0
         self.graph_kernel_launches = 0
         self.graphs = {}
-        self.use_graphs = config.cuda_graphs and all(
-            getattr(b.mixer, "graph_safe", False) and getattr(b.feed_forward, "graph_safe", False)
-            for b in model.blocks)
+        self.use_graphs = config.cuda_graphs and model.graph_safe
+
+    @staticmethod
+    def _pages_that_fit(model: Model, config: EngineConfig) -> int:
+        """The pool's size from the memory that is left: free bytes (with the allocator's unused blocks given
+        back first) times memory_fraction, over what a page number costs in all runs; at most what
+        max_requests requests of the longest context could hold."""
+        torch.cuda.empty_cache()
+        free, _ = torch.cuda.mem_get_info(model.rt.device)
+        per_page = CacheManager.bytes_per_page(model.cache_needs(), config.page_tokens, model.rt.dtype)
+        if per_page == 0:
+            return 1
+        pages = int(free * config.memory_fraction) // per_page
+        most = config.max_requests * -(-model.spec.max_positions // config.page_tokens)
+        if pages < 1:
+            raise RuntimeError(f"air_b200: {free >> 20} MiB of device memory are free after the weights, "
+                               f"a cache page takes {per_page >> 10} KiB")
+        return min(pages, most)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -139,9 +167,14 @@ class Engine:
         device = _device(config.device)
         rt = Runtime(device=device, dtype=parse_dtype(config.dtype), page_tokens=config.page_tokens,
                      status=torch.zeros(1, dtype=torch.int32, device=device))
-        tensors = load_tensors(folder, model.tensor_specs(), rt.dtype, device)
+        report = LoadReport()
+        tensors = load_tensors(folder, model.tensor_specs(), rt.dtype, device, keep_float32=config.keep_float32,
+                               report=report)
         model.load(tensors, rt)
-        return cls(model, config, model_config)
+        del tensors
+        engine = cls(model, config, model_config)
+        engine.load_report = report
+        return engine
 
     @classmethod
     def from_random(cls, model_config, seed: int = 0, config: Optional[EngineConfig] = None) -> "Engine":
@@ -197,7 +230,8 @@ class Engine:
                     and len(entries) <= _BUCKETS[-1]:
                 logits, ctx = self._decode_step(entries)
             else:
-                ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+                ctx = build_context(entries, self.cache, self.rt.device, status=self.status,
+                                    planners=self.model.planners())
                 ctx.last_token = self.last_token
                 logits = self.model.forward(ctx, self.cache)
         except Exception:
@@ -264,20 +298,29 @@ class Engine:
         """The request is over: its pages and its slot are free for others."""
         self.cache.close(request)
 
+    STATUS_TEXT = {1: "a token outside the vocabulary reached the embedding kernel",
+                   2: "a token was to be written to a page that its request does not hold",
+                   3: "non-finite logits",
+                   4: "a wait inside the matrix-product kernel ran out",
+                   5: "a wait inside the decode attention kernel ran out",
+                   6: "a wait inside the prefill attention kernel ran out",
+                   7: "a wait inside the tcgen05 prefill attention kernel ran out",
+                   8: "the tile list of the tcgen05 prefill attention kernel is not in pairs of one request"}
+
+    def read_status(self) -> int:
+        """The device's error word (a synchronisation): 0, or the code of what a kernel could not do."""
+        return int(self.status.item())
+
+    def clear_status(self, code: int) -> str:
+        """Zeroes the word after `code` was read from it; returns the message for that code."""
+        self.status.zero_()
+        return self.STATUS_TEXT.get(code, f"device status {code}")
+
     def check_status(self) -> None:
-        """Reads the device's error word (a synchronisation)."""
-        code = int(self.status.item())
+        """Reads the device's error word (a synchronisation) and raises StepError if it is set."""
+        code = self.read_status()
         if code:
-            self.status.zero_()
-            raise StepError({1: "a token outside the vocabulary reached the embedding kernel",
-                             2: "a token was to be written to a page that its request does not hold",
-                             3: "non-finite logits",
-                             4: "a wait inside the matrix-product kernel ran out",
-                             5: "a wait inside the decode attention kernel ran out",
-                             6: "a wait inside the prefill attention kernel ran out",
-                             7: "a wait inside the tcgen05 prefill attention kernel ran out",
-                             8: "the tile list of the tcgen05 prefill attention kernel is not in pairs of one request",
-                             }.get(code, f"device status {code}"))
+            raise StepError(self.clear_status(code))
 
 
 def _device(name) -> torch.device:

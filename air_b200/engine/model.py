@@ -33,6 +33,8 @@ class Model:
         specs += self.final_norm.tensor_specs()
         if s.output_name is not None:
             specs.append(TensorSpec(s.output_name, (s.vocab_size, s.hidden_size)))
+        if s.output_bias_name is not None:
+            specs.append(TensorSpec(s.output_bias_name, (s.vocab_size,), init="zeros", wide=True))
         seen = set()
         for t in specs:
             if t.name in seen:
@@ -48,6 +50,26 @@ class Model:
         self.final_norm.load(tensors, rt)
         out = self.embedding if self.spec.output_name is None else tensors[self.spec.output_name]
         self.output = Linear(out, rt.status)
+        bias = None if self.spec.output_bias_name is None else tensors[self.spec.output_bias_name]
+        self.output_bias = None if bias is None else bias.to(torch.float32)
+        self._planners = None
+
+    def planners(self):
+        """The parts that plan on the host, one for every plan key (Part.plan_key)."""
+        if self._planners is None:
+            found = {}
+            for b in self.blocks:
+                for part in b.parts():
+                    key = part.plan_key()
+                    if key is not None and key not in found:
+                        found[key] = part
+            self._planners = tuple(found.values())
+        return self._planners
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step may be captured in a CUDA graph: no part reads the batch on the host."""
+        return all(b.graph_safe for b in self.blocks) and getattr(self.final_norm, "graph_safe", False)
 
     def cache_needs(self):
         """Per run of the order list: the needs of the layer's mixer, or nothing for a run that
@@ -83,7 +105,8 @@ class Model:
         and returns float32 logits [wanted rows, vocab]."""
         rt = self.rt
         h = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=torch.float32, device=rt.device)
-        ops.embedding(self.embedding, ctx.token_ids, h, status=ctx.status, last_token=ctx.last_token)
+        ops.embedding(self.embedding, ctx.token_ids, h, status=ctx.status, last_token=ctx.last_token,
+                      multiplier=self.spec.embedding_multiplier)
         pending = None
         for i, run in enumerate(self.spec.order):
             owner = i if run.cache_from is None else run.cache_from
@@ -93,4 +116,8 @@ class Model:
         if R == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         y = self.final_norm.forward(h, pending, rows=ctx.logit_rows)
-        return self.output.full(y) if self.output.small(y) else self.output(y, torch.float32)
+        logits = self.output.full(y) if self.output.small(y) else self.output(y, torch.float32)
+        s = self.spec
+        if self.output_bias is not None or s.logit_scale != 1.0 or s.logit_softcap > 0.0:
+            ops.logits_post(logits, self.output_bias, s.logit_scale, s.logit_softcap)
+        return logits

@@ -36,10 +36,10 @@ def run_trace(engine: Engine, lines, out_dir: str, done=None) -> int:
         entries = [Entry(e["id"], e["tokens"], e.get("want", ())) for e in rec.get("entries", ())]
         if entries:
             logits = engine.step(entries)
-            if logits.shape[0]:
-                data = logits.to("cpu").contiguous().numpy().astype("<f4", copy=False)
+            data = logits.to("cpu").contiguous().numpy().astype("<f4", copy=False) if logits.shape[0] else None
+            engine.check_status()       # before anything is written: a step that faulted leaves no file
+            if data is not None:
                 data.tofile(os.path.join(out_dir, f"{rec['step']}.f32"))
-            engine.check_status()
         for r in rec.get("end", ()):
             engine.finish(r)
         steps += 1

@@ -1,110 +1,126 @@
-"""The scheduler's decisions, as pure logic without a device.
+"""What the next step holds, and who may join: decisions without a device.
 
-Two small classes carry AIR's two decisions (src/runtime/scheduler.{hpp,cpp}):
+The policy is AIR's (src/runtime/scheduler.cpp, src/runtime/serving.cpp:1684-1700, 1796-1810):
+a request becomes active only if its worst case (prompt plus max_new_tokens) fits beside what the
+active requests have reserved, and while fewer than `max_active` are active; in a step every decoding
+request comes first with its one token, then prompt portions, each at most `portion_limit` tokens and
+what is left of the step's token budget; where the budget does not reach everybody, the start of each
+walk moves on from step to step so that nobody starves.
 
-* `CapacityScheduler.evaluate`: may the request at the head of the queue become active?  It is
-  refused while as many requests are active as allowed, and while its worst case (prompt plus
-  max_new_tokens, in whole pages) does not fit beside what the active requests have reserved.
-  AIR reserves bytes (scheduler.cpp:8-41); here the unit is the cache page.
-* `MicrobatchScheduler.schedule`: which tokens run in this cycle?  Decoding requests first, one
-  token each, then prompt portions, each at most its own limit and what is left of the cycle's
-  token budget; within each phase a cursor rotates the order from cycle to cycle, so that a small
-  budget does not always serve the same request (scheduler.cpp:62-139).
+The form is this engine's.  A cycle here is ONE step of one flat batch, so the plan is the batch itself: a
+list of `Entry` that `Engine.step` takes as it is.  Reservations are counted in cache pages.  A portion
+that the budget or the limit cuts (not the prompt's end) is shortened so that the next portion of the
+request starts on a row tile of the prefill kernels (`row_tile` positions), or at least on a page of the
+cache: the later portions' first key tile and first page are then whole.  A step that only decodes says which
+captured graph it will replay (`StepPlan.graph_size`; a step of 65 tokens runs the graph made for 96).
 """
 from __future__ import annotations
 
-import enum
 from dataclasses import dataclass, field
-from typing import Hashable, List, Sequence
+from typing import Hashable, List, Optional, Sequence, Tuple
 
-
-class WorkPhase(enum.Enum):
-    prefill = 0
-    decode = 1
+from .batch import Entry
 
 
 @dataclass
-class SchedulableSequence:
-    slot: Hashable
-    phase: WorkPhase = WorkPhase.prefill
-    max_tokens: int = 1     # decode: 1; prefill: min(rest of the prompt, quantum)
-
-
-@dataclass
-class ScheduledSlice:
-    slot: Hashable
-    phase: WorkPhase
-    token_count: int
-
-
-@dataclass
-class ScheduledBatch:
-    slices: List[ScheduledSlice] = field(default_factory=list)
-    token_count: int = 0
-    decode_tokens: int = 0
-    prefill_tokens: int = 0
-    prefill_sequences: int = 0
-
-
-@dataclass
-class CapacityDecision:
+class Admission:
     admit: bool
-    reservation_pages: int
-    reason: str
+    pages: int          # the worst case of the request, in pages
+    reason: str         # "admitted", "max-active-requests", "device-capacity"
 
 
-class CapacityScheduler:
-    def __init__(self, max_active_requests: int):
-        self.max_active_requests = max_active_requests
+@dataclass
+class Runnable:
+    """An active request as the planner sees it.  `done` tokens of `prompt` are in the cache; when all
+    are, the request decodes: its next input is `last_token`.  `wants_token`: the prompt's last portion
+    asks for logits (the first generated token comes from them)."""
+    request: Hashable
+    prompt: Sequence[int]
+    done: int
+    last_token: Optional[int] = None
+    wants_token: bool = True
 
-    def evaluate(self, active_requests: int, active_reserved_pages: int, capacity_pages: int,
-                 page_tokens: int, requested_tokens: int) -> CapacityDecision:
-        if active_requests >= self.max_active_requests:
-            return CapacityDecision(False, 0, "max-active-requests")
-        reservation = -(-requested_tokens // page_tokens)
-        if reservation > capacity_pages or active_reserved_pages > capacity_pages - reservation:
-            return CapacityDecision(False, reservation, "device-capacity")
-        return CapacityDecision(True, reservation, "admitted")
+    @property
+    def decoding(self) -> bool:
+        return self.done >= len(self.prompt)
 
 
-class MicrobatchScheduler:
-    def __init__(self):
-        self._decode_cursor = 0
-        self._prefill_cursor = 0
+@dataclass
+class StepPlan:
+    entries: List[Entry] = field(default_factory=list)
+    decode_tokens: int = 0
+    prompt_tokens: int = 0
+    portions: List[Tuple[Hashable, int]] = field(default_factory=list)    # (request, tokens of its prompt)
+    graph_size: Optional[int] = None      # decode-only steps: the size of the captured graph that runs
 
-    def order(self, candidates: Sequence[SchedulableSequence]) -> List[SchedulableSequence]:
-        decode = [c for c in candidates if c.phase == WorkPhase.decode]
-        prefill = [c for c in candidates if c.phase != WorkPhase.decode]
+    @property
+    def tokens(self) -> int:
+        return self.decode_tokens + self.prompt_tokens
 
-        def rotate(phase, cursor):
-            if not phase:
-                return phase, 0
-            cursor %= len(phase)
-            return phase[cursor:] + phase[:cursor], (cursor + 1) % len(phase)
 
-        decode, self._decode_cursor = rotate(decode, self._decode_cursor)
-        prefill, self._prefill_cursor = rotate(prefill, self._prefill_cursor)
-        return decode + prefill
+class StepScheduler:
+    def __init__(self, max_active: int, token_budget: int, portion_limit: int, page_tokens: int,
+                 row_tile: int = 128, graph_sizes: Sequence[int] = ()):
+        if min(max_active, token_budget, portion_limit, page_tokens) <= 0:
+            raise ValueError("the scheduler's limits must be greater than zero")
+        self.max_active, self.token_budget, self.portion_limit = max_active, token_budget, portion_limit
+        self.page_tokens, self.row_tile = page_tokens, row_tile
+        self.graph_sizes = tuple(sorted(graph_sizes))
+        self._decode_turn = 0      # where the walk over the decoding requests starts
+        self._prompt_turn = 0
 
-    def schedule(self, candidates: Sequence[SchedulableSequence], token_budget: int) -> ScheduledBatch:
-        batch = ScheduledBatch()
-        if token_budget <= 0 or not candidates:
-            return batch
-        remaining = token_budget
-        for c in self.order(candidates):
-            if remaining == 0:
-                break
-            if c.max_tokens <= 0:
-                continue
-            tokens = 1 if c.phase == WorkPhase.decode else min(c.max_tokens, remaining)
-            if tokens <= 0 or tokens > remaining:
-                continue
-            batch.slices.append(ScheduledSlice(c.slot, c.phase, tokens))
-            batch.token_count += tokens
-            remaining -= tokens
-            if c.phase == WorkPhase.decode:
-                batch.decode_tokens += 1
-            else:
-                batch.prefill_tokens += tokens
-                batch.prefill_sequences += 1
-        return batch
+    # ------------------------------------------------------------------ who may join
+    def pages_for(self, tokens: int) -> int:
+        return -(-tokens // self.page_tokens)
+
+    def admit(self, active: int, reserved_pages: int, pool_pages: int, worst_case_tokens: int) -> Admission:
+        pages = self.pages_for(worst_case_tokens)
+        if active >= self.max_active:
+            return Admission(False, 0, "max-active-requests")
+        if pages + reserved_pages > pool_pages:
+            return Admission(False, pages, "device-capacity")
+        return Admission(True, pages, "admitted")
+
+    # ------------------------------------------------------------------ what runs
+    def _cut(self, position: int, count: int) -> int:
+        """A portion of `count` tokens from `position` that does not end its prompt: shortened to end
+        on a row tile, else on a page, where that leaves it any tokens."""
+        end = position + count
+        for edge in (self.row_tile, self.page_tokens):
+            aligned = end - end % edge
+            if aligned > position:
+                return aligned - position
+        return count
+
+    def plan(self, runnable: Sequence[Runnable]) -> StepPlan:
+        plan = StepPlan()
+        left = self.token_budget
+        decoding = [r for r in runnable if r.decoding]
+        prompts = [r for r in runnable if not r.decoding]
+        if decoding and left > 0:
+            start = self._decode_turn % len(decoding)
+            served = (decoding[start:] + decoding[:start])[:left]
+            for r in served:
+                plan.entries.append(Entry(r.request, [r.last_token], [0]))
+            plan.decode_tokens = len(served)
+            left -= len(served)
+            self._decode_turn = (start + len(served)) % len(decoding)
+        if prompts and left > 0:
+            start = self._prompt_turn % len(prompts)
+            self._prompt_turn = (start + 1) % len(prompts)
+            for r in prompts[start:] + prompts[:start]:
+                if left <= 0:
+                    break
+                rest = len(r.prompt) - r.done
+                count = min(rest, self.portion_limit, left)
+                if count < rest:
+                    count = self._cut(r.done, count)
+                last = count == rest
+                plan.entries.append(Entry(r.request, r.prompt[r.done:r.done + count],
+                                          [count - 1] if last and r.wants_token else []))
+                plan.portions.append((r.request, count))
+                plan.prompt_tokens += count
+                left -= count
+        if plan.entries and not plan.portions:
+            plan.graph_size = next((g for g in self.graph_sizes if g >= plan.decode_tokens), None)
+        return plan

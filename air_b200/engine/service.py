@@ -36,7 +36,7 @@ from typing import Deque, Dict, Hashable, List, Optional, Sequence
 from ..cache.manager import OutOfPages
 from ..sampling.sampler import GenerationConfig, HostSampler, SamplingConfig
 from .batch import LAST_SAMPLED, Entry
-from .scheduler import (CapacityScheduler, MicrobatchScheduler, SchedulableSequence, WorkPhase)
+from .scheduler import Runnable, StepScheduler
 
 
 @dataclass
@@ -133,15 +133,15 @@ class _WorkItem:
     cancellation: CancellationToken = field(default_factory=CancellationToken)
 
     @property
-    def phase(self) -> WorkPhase:
-        return WorkPhase.prefill if self.prompt_position < len(self.prompt) else WorkPhase.decode
+    def decoding(self) -> bool:
+        return self.prompt_position >= len(self.prompt)
 
 
 @dataclass
 class _InFlight:
     """A decode step that has been launched and whose tokens are on their way to the host."""
     items: List[_WorkItem]          # in the order of the rows
-    tokens: object                  # pinned int32 tensor [rows]
+    tokens: object                  # pinned int32 tensor [rows + 1]: the chosen tokens, then the device's status word
     event: object                   # recorded after the copy
 
 
@@ -153,8 +153,9 @@ class InferenceService:
                      "prefill_quantum_tokens"):
             if getattr(self.config, name) <= 0:
                 raise ValueError(f"scheduler {name} must be greater than zero")
-        self.capacity = CapacityScheduler(self.config.max_active_requests)
-        self.micro = MicrobatchScheduler()
+        self.scheduler = StepScheduler(
+            self.config.max_active_requests, self.config.token_budget_per_cycle, self.config.prefill_quantum_tokens,
+            engine.cache.page_tokens, graph_sizes=getattr(engine, "graph_sizes", ()))
         self.queued: Deque[_WorkItem] = collections.deque()
         self.active: List[_WorkItem] = []
         self.finished: Dict[int, InferenceResponse] = {}
@@ -162,15 +163,17 @@ class InferenceService:
         self.cycles = 0
         self.preemptions = 0
         self.cancelled_requests = 0
-        self.last_batch = None
+        self.last_plan = None
+        self.failed_steps = 0
         self._inflight: Optional[_InFlight] = None
         self._pinned = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def create(cls, model: str, dtype="bfloat16", scheduler: Optional[SchedulerConfig] = None,
-               max_tokens: int = 65536, device: str = "cuda:0") -> "InferenceService":
-        """Loads the model folder and makes its cache for `max_tokens` tokens."""
+               max_tokens: Optional[int] = None, device: str = "cuda:0") -> "InferenceService":
+        """Loads the model folder and makes its cache for `max_tokens` tokens; None takes the device memory
+        that is left once the weights are resident (EngineConfig.memory_fraction of it)."""
         from .engine import Engine, EngineConfig, parse_dtype
         scheduler = scheduler or SchedulerConfig()
         engine = Engine.from_folder(model, EngineConfig(
@@ -260,12 +263,11 @@ class InferenceService:
             worst = len(item.prompt) + max(0, item.generation.max_new_tokens - len(item.generated))
             if self.config.reserve_worst_case:
                 reserved = sum(i.reservation_pages for i in self.active)
-                decision = self.capacity.evaluate(len(self.active), reserved, cache.num_pages,
-                                                  cache.page_tokens, worst)
+                decision = self.scheduler.admit(len(self.active), reserved, cache.num_pages, worst)
             else:
                 first = min(len(item.prompt), self.config.prefill_quantum_tokens)
-                decision = self.capacity.evaluate(len(self.active), cache.num_pages - cache.free_pages(),
-                                                  cache.num_pages, cache.page_tokens, first)
+                decision = self.scheduler.admit(len(self.active), cache.num_pages - cache.free_pages(),
+                                                cache.num_pages, first)
                 if decision.admit and cache.pages_needed(worst) > cache.num_pages:
                     decision.admit, decision.reason = False, "device-capacity"
             if not decision.admit:
@@ -277,23 +279,9 @@ class InferenceService:
                     continue
                 break
             self.queued.popleft()
-            item.reservation_pages = decision.reservation_pages if self.config.reserve_worst_case else 0
+            item.reservation_pages = decision.pages if self.config.reserve_worst_case else 0
             item.admitted = time.perf_counter()
             self.active.append(item)
-
-    def _entries(self, batch) -> List[Entry]:
-        by_id = {i.request_id: i for i in self.active}
-        entries = []
-        for s in batch.slices:
-            item = by_id[s.slot]
-            if s.phase == WorkPhase.prefill:
-                tokens = item.prompt[item.prompt_position:item.prompt_position + s.token_count]
-                last = item.prompt_position + s.token_count >= len(item.prompt)
-                wants_token = last and len(item.generated) < item.generation.max_new_tokens
-                entries.append(Entry(item.request_id, tokens, [len(tokens) - 1] if wants_token else []))
-            else:
-                entries.append(Entry(item.request_id, [item.generated[-1]], [0]))
-        return entries
 
     def run_cycle(self) -> bool:
         """Admission, one micro-batch, one engine step, sampling, finishing.  Returns False when
@@ -306,17 +294,12 @@ class InferenceService:
             return True
         if not self.active:
             return False
-        candidates = []
-        for item in self.active:
-            if item.phase == WorkPhase.prefill:
-                limit = min(len(item.prompt) - item.prompt_position, self.config.prefill_quantum_tokens)
-                candidates.append(SchedulableSequence(item.request_id, WorkPhase.prefill, limit))
-            else:
-                candidates.append(SchedulableSequence(item.request_id, WorkPhase.decode, 1))
-        batch = self.micro.schedule(candidates, self.config.token_budget_per_cycle)
-        if not batch.slices:
+        plan = self.scheduler.plan([
+            Runnable(i.request_id, i.prompt, i.prompt_position, i.generated[-1] if i.generated else None,
+                     wants_token=len(i.generated) < i.generation.max_new_tokens) for i in self.active])
+        if not plan.entries:
             return False
-        entries = self._entries(batch)
+        entries = plan.entries
         while True:
             try:
                 logits = self.engine.step(entries)
@@ -326,7 +309,7 @@ class InferenceService:
                 entries = [e for e in entries if e.request != victim]
                 if not entries:
                     return True
-        self.last_batch = batch
+        self.last_plan = plan
         self.cycles += 1
         if self._may_decode_ahead(entries):
             items = self._items(entries)
@@ -348,7 +331,7 @@ class InferenceService:
             return False
         if len(entries) != len(self.active):
             return False
-        return all(i.phase == WorkPhase.decode and self._on_device(i) for i in self.active) and \
+        return all(i.decoding and self._on_device(i) for i in self.active) and \
             all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
 
     def _on_device(self, item: _WorkItem) -> bool:
@@ -367,15 +350,31 @@ class InferenceService:
         return self.engine.sample(logits)
 
     def _read_later(self, items: List[_WorkItem], ids) -> _InFlight:
+        """Starts the copy of the chosen tokens, and of the device's status word behind them, into pinned
+        memory; the step's tokens and its faults arrive together, with one wait."""
         import torch
         n = len(items)
-        ring = self._pinned.setdefault(n, [[torch.empty(n, dtype=torch.int32).pin_memory(), torch.cuda.Event()]
-                                           for _ in range(2)])
+        ring = self._pinned.get(n)
+        if ring is None:
+            ring = self._pinned[n] = [[torch.empty(n + 1, dtype=torch.int32).pin_memory(), torch.cuda.Event()]
+                                      for _ in range(2)]
         ring.append(ring.pop(0))
         host, event = ring[0]
-        host.copy_(ids, non_blocking=True)
+        host[:n].copy_(ids, non_blocking=True)
+        host[n:].copy_(self.engine.status, non_blocking=True)
         event.record()
         return _InFlight(list(items), host, event)
+
+    def _fault(self, code: int, items: Sequence[_WorkItem]) -> None:
+        """The device reported a fault during a step (a bounded wait that ran out, a page that the request
+        does not hold, logits that are not finite): its word is cleared, and the step's requests fail with the
+        engine's message for it, as AIR fails the item whose logits are not finite
+        (src/runtime/serving.cpp:1037-1040)."""
+        message = self.engine.clear_status(code)
+        self.failed_steps += 1
+        for item in items:
+            if not item.done:
+                item.done, item.error = True, message
 
     def _launch_ahead(self, flying: _InFlight) -> Optional[_InFlight]:
         """The step after the one in flight, for the requests that go on whatever it brings; None
@@ -397,7 +396,9 @@ class InferenceService:
         """Reads the tokens of a launched step and accepts them.  (A request that ended meanwhile, by
         an end-of-sequence token of the step before, had one token too many computed: dropped.)"""
         flying.event.synchronize()
-        chosen = flying.tokens.tolist()
+        *chosen, status = flying.tokens.tolist()
+        if status:
+            self._fault(status, flying.items)
         now = time.perf_counter()
         for item, token in zip(flying.items, chosen):
             if not item.done:
@@ -441,16 +442,20 @@ class InferenceService:
             else:
                 host = logits.float().cpu().numpy()
                 chosen = [i.sampler.sample(host[r]) for r, i in enumerate(rows)]
+        status = self.engine.read_status() if hasattr(self.engine, "read_status") else 0
+        if status:      # (the tokens were read above, so the step has ended and the word is final)
+            self._fault(status, [by_id[e.request] for e in entries])
+            return
         now = time.perf_counter()
         r = 0
         for e in entries:
             item = by_id[e.request]
-            if item.phase == WorkPhase.prefill:
+            if not item.decoding:
                 item.prompt_position += len(e.tokens)
             if e.want:
                 self._accept_token(item, chosen[r], now)
                 r += 1
-            elif item.phase == WorkPhase.decode and len(item.generated) >= item.generation.max_new_tokens:
+            elif item.decoding and len(item.generated) >= item.generation.max_new_tokens:
                 item.done = True  # max_new_tokens == 0, or a recomputed request that had finished
 
     def _accept_token(self, item: _WorkItem, token: int, now: float) -> None:
@@ -487,4 +492,4 @@ class InferenceService:
                 "reserved_pages": sum(i.reservation_pages for i in self.active),
                 "kv_pages_total": cache.num_pages, "kv_pages_free": cache.free_pages(),
                 "cycles": self.cycles, "preemptions": self.preemptions,
-                "cancelled_requests": self.cancelled_requests}
+                "cancelled_requests": self.cancelled_requests, "failed_steps": self.failed_steps}

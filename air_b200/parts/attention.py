@@ -3,11 +3,13 @@ from __future__ import annotations
 
 import math
 
+import numpy as np
 import torch
 
+from ..config.model_config import ConfigError
 from ..csrc import ops
 from ..weights.loader import TensorSpec
-from .base import Mixer, PagedKV
+from .base import HostBatch, Mixer, PagedKV, Plan
 from .linear import Linear
 from .registry import register_mixer, POSITION_ENCODINGS
 
@@ -39,14 +41,43 @@ class Attention(Mixer):
         self.window = p.get("window")
         self.qkv_bias = bool(p.get("qkv_bias", False))
         if self.heads % self.kv_heads:
-            raise ValueError("attention: heads must be a multiple of kv_heads")
+            raise ConfigError("data_error", "attention: heads must be a multiple of kv_heads")
         if self.head_dim % 16 or self.head_dim > 256:
-            raise ValueError(f"attention: head size {self.head_dim} is not a multiple of 16 up to 256")
+            raise ConfigError("unsupported", f"attention: head size {self.head_dim} is not a multiple of 16 up to "
+                                             "256, which is what the attention kernels take")
         pos = p["position"]
         self.position = POSITION_ENCODINGS.get(pos.kind)(pos)
 
     def cache_needs(self):
         return (PagedKV(self.kv_heads, self.head_dim, self.window),)
+
+    # ------------------------------------------------------------------ the step's plan
+    PLAN = "attention.tiles"
+
+    def plan_key(self):
+        return self.PLAN
+
+    def plan(self, batch: HostBatch) -> Plan:
+        """What the tile kernels want to know of a step, worked out once for all attention layers:
+        `decode_prefix`, the number of leading entries that bring a single next token (they take the
+        decode kernel), and for the tokens after them `tiles` [16n, 4] int32 = (slot, first row, its
+        position, rows <= 16): 16-token tiles in groups of 16 per request, filled up with rows = 0."""
+        prefix = 0
+        while prefix < len(batch.counts) and batch.counts[prefix] == 1:
+            prefix += 1
+        tiles = []
+        for i in range(prefix, len(batch.counts)):
+            n = batch.counts[i]
+            count = -(-n // 16)
+            tile = np.zeros((-(-count // 16) * 16, 4), dtype=np.int32)
+            tile[:, 0] = batch.slots[i]
+            first = np.arange(count, dtype=np.int32) * 16
+            tile[:count, 1] = batch.q_start[i] + first
+            tile[:count, 2] = batch.lengths[i] + first
+            tile[:count, 3] = np.minimum(16, n - first)
+            tiles.append(tile)
+        tiles = np.concatenate(tiles) if tiles else np.zeros((0, 4), dtype=np.int32)
+        return Plan(arrays={"tiles": tiles}, values={"decode_prefix": prefix})
 
     def tensor_specs(self):
         d, p = self.head_dim, self.prefix
@@ -55,9 +86,9 @@ class Attention(Mixer):
                  TensorSpec(p + "v_proj.weight", (self.kv_heads * d, self.hidden)),
                  TensorSpec(p + "o_proj.weight", (self.hidden, self.heads * d))]
         if self.qkv_bias:
-            specs += [TensorSpec(p + "q_proj.bias", (self.heads * d,), optional=True),
-                      TensorSpec(p + "k_proj.bias", (self.kv_heads * d,), optional=True),
-                      TensorSpec(p + "v_proj.bias", (self.kv_heads * d,), optional=True)]
+            specs += [TensorSpec(p + "q_proj.bias", (self.heads * d,), optional=True, wide=True),
+                      TensorSpec(p + "k_proj.bias", (self.kv_heads * d,), optional=True, wide=True),
+                      TensorSpec(p + "v_proj.bias", (self.kv_heads * d,), optional=True, wide=True)]
         return specs + self.position.tensor_specs()
 
     def load(self, tensors, rt):
@@ -107,21 +138,22 @@ class Attention(Mixer):
         out = torch.empty_like(q)
         if rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.all_decode:
             ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
-        elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.tiles is not None
+        elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and self.PLAN in ctx.plans
               and ops.tile_pages(pages.kv.shape[3])):
             # a mixed step: the single next tokens at the head of the batch take the decode kernel (a row
             # tile of 128 queries for one token would read its request's whole context for one row), the
             # prompt portions the tile kernels
-            n = ctx.decode_prefix
+            plan = ctx.plans[self.PLAN]
+            n = plan.decode_prefix
             if n:
                 ops.decode_attention(q[:n], pages.kv, bt, ctx.token_seq[:n], ctx.positions[:n], out[:n], self.window,
                                      self.scale)
-            if ctx.tiles.shape[0] == 0:
+            if plan.tiles.shape[0] == 0:
                 pass
             elif d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
-                ops.prefill_attention_tc(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
+                ops.prefill_attention_tc(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status)
             else:
-                ops.prefill_attention(q, pages.kv, bt, ctx.tiles, out, self.window, self.scale, status=ctx.status)
+                ops.prefill_attention(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status)
         else:
             ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
         return self._project(out.view(T, H * d), ctx)

@@ -5,10 +5,43 @@ from .registry import register_block, MIXERS, FEED_FORWARDS, NORMS
 from .spec import BlockSpec
 
 
+class Block:
+    """What an arrangement offers to the model: its parts, their tensors, what the layer keeps per
+    request, and forward(h, pending, ctx, cache, owns_cache) -> (h, pending).  A subclass builds its
+    parts from `spec.part(role)` with the registry of the role's kind and `spec.name(role)` as the
+    prefix of their tensors."""
+
+    def __init__(self, spec: BlockSpec):
+        self.spec = spec
+
+    def parts(self):
+        raise NotImplementedError
+
+    def tensor_specs(self):
+        return [s for part in self.parts() for s in part.tensor_specs()]
+
+    def load(self, tensors, rt):
+        for part in self.parts():
+            part.load(tensors, rt)
+
+    def cache_needs(self):
+        """What the layer keeps per request (CacheNeed objects); forward() receives their views as `cache`,
+        in the same order."""
+        return ()
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self.parts())
+
+    def forward(self, h, pending, ctx, cache, owns_cache=True):
+        raise NotImplementedError
+
+
 @register_block("pre_norm")
-class PreNormBlock:
+class PreNormBlock(Block):
     """h = h + mixer(norm1(h)); h = h + feed_forward(norm2(h))
     (AIR: src/reference/reference_executor.cpp:343-413).
+    Roles: mixer_norm, mixer, feed_forward_norm, feed_forward.
 
     The residual stream h is float32.  Each addition is fused into the norm that follows
     it: the block receives the previous block's output still pending, and hands its own
@@ -18,22 +51,16 @@ class PreNormBlock:
     that follows reads the stream alone."""
 
     def __init__(self, spec: BlockSpec):
-        self.spec = spec
-        p, n = spec.prefix, spec.names
-        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, p + n["mixer_norm"])
-        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, p + n["mixer"])
-        self.ff_norm = NORMS.get(spec.feed_forward_norm.kind)(spec.feed_forward_norm, p + n["feed_forward_norm"])
-        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, p + n["feed_forward"])
+        super().__init__(spec)
+        self.mixer_norm = NORMS.get(spec.part("mixer_norm").kind)(spec.part("mixer_norm"), spec.name("mixer_norm"))
+        self.mixer = MIXERS.get(spec.part("mixer").kind)(spec.part("mixer"), spec.name("mixer"))
+        self.ff_norm = NORMS.get(spec.part("feed_forward_norm").kind)(spec.part("feed_forward_norm"),
+                                                                      spec.name("feed_forward_norm"))
+        self.feed_forward = FEED_FORWARDS.get(spec.part("feed_forward").kind)(spec.part("feed_forward"),
+                                                                              spec.name("feed_forward"))
 
     def parts(self):
         return (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward)
-
-    def tensor_specs(self):
-        return [s for part in self.parts() for s in part.tensor_specs()]
-
-    def load(self, tensors, rt):
-        for part in self.parts():
-            part.load(tensors, rt)
 
     def cache_needs(self):
         return self.mixer.cache_needs()

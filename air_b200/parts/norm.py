@@ -16,8 +16,10 @@ class RMSNorm(Norm):
     params: size, eps.  Tensor: <prefix>weight [size].  The sum of squares and the residual
     sum are 32-bit."""
 
+    graph_safe = True
+
     def tensor_specs(self):
-        return [TensorSpec(self.prefix + "weight", (self.spec["size"],), init="one_plus_normal")]
+        return [TensorSpec(self.prefix + "weight", (self.spec["size"],), init="one_plus_normal", wide=True)]
 
     def load(self, tensors, rt):
         super().load(tensors, rt)

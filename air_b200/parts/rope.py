@@ -16,7 +16,8 @@ class RopeHalf(PositionEncoding):
     The angles are evaluated once, in 64-bit like AIR's CPU executor, and kept as float32
     cos|sin [max_positions, rotary_dim]; the mixer's kernel reads a token's row by its
     position.  Another frequency rule (scaled, interpolated) is another table of the same
-    shape."""
+    shape.  Layers whose encodings have equal parameters share one table (Runtime.shared), so a
+    step reads one row per token whatever the number of layers."""
 
     def load(self, tensors, rt):
         super().load(tensors, rt)
@@ -24,10 +25,14 @@ class RopeHalf(PositionEncoding):
         if rot % 2:
             raise ValueError("rope_half needs an even rotary width")
         self.rotary_dim = rot
-        i = torch.arange(rot // 2, dtype=torch.float64)
-        inv_freq = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float64), (2.0 * i) / rot)
-        angle = torch.arange(n, dtype=torch.float64)[:, None] * inv_freq[None, :]
-        self._table = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).to(torch.float32).to(rt.device)
+        key = ("rope_half", rot, theta, n)
+        table = rt.shared.get(key)
+        if table is None:
+            i = torch.arange(rot // 2, dtype=torch.float64)
+            inv_freq = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float64), (2.0 * i) / rot)
+            angle = torch.arange(n, dtype=torch.float64)[:, None] * inv_freq[None, :]
+            table = rt.shared[key] = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).to(torch.float32).to(rt.device)
+        self._table = table
 
     def table(self):
         return self._table

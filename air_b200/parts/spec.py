@@ -27,18 +27,27 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """One layer: how its parts are arranged (kind), the parts, and the prefix of its
-    tensors' names in the checkpoint."""
+    """One layer: how its parts are arranged (kind: a registered block class), the parts by the
+    role they have in that arrangement, the prefix of the layer's tensors in the checkpoint and
+    what follows the prefix for each role.  The block class decides which roles it wants (the
+    pre-norm block: mixer_norm, mixer, feed_forward_norm, feed_forward); another arrangement
+    (norms after the parts, a third sub-layer, parts side by side) is another block class with
+    roles of its own and needs no change here."""
     kind: str
     prefix: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    # what follows the prefix in the names of each part's tensors
-    names: Mapping[str, str] = field(default_factory=lambda: {
-        "mixer_norm": "input_layernorm.", "mixer": "self_attn.",
-        "feed_forward_norm": "post_attention_layernorm.", "feed_forward": "mlp."})
+    parts: Mapping[str, PartSpec]
+    names: Mapping[str, str] = field(default_factory=dict)
+
+    def part(self, role: str) -> PartSpec:
+        try:
+            return self.parts[role]
+        except KeyError:
+            raise ValueError(f"block '{self.kind}' at '{self.prefix}' needs a part in the role '{role}' "
+                             f"(it has: {', '.join(sorted(self.parts))})") from None
+
+    def name(self, role: str) -> str:
+        """Prefix of the tensors of the part in this role."""
+        return self.prefix + self.names.get(role, role + ".")
 
 
 @dataclass(frozen=True)
@@ -62,6 +71,11 @@ class ModelSpec:
     final_norm_prefix: str
     output_name: Optional[str]  # None: the output matrix is the embedding table (tied)
     eos_token_id: Optional[int] = None
+    # Off for the Qwen2 decoder; other decoders of the same skeleton differ in them:
+    embedding_multiplier: float = 1.0        # the embedding rows are multiplied by this (in 32-bit)
+    output_bias_name: Optional[str] = None   # a float32 [vocab] tensor added to the logits
+    logit_scale: float = 1.0                 # logits = (x W^T + bias) * logit_scale
+    logit_softcap: float = 0.0               # > 0: logits = cap * tanh(logits / cap), after the scale
 
     def validate(self) -> None:
         for i, run in enumerate(self.order):

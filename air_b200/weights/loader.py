@@ -6,16 +6,23 @@ module finds them in a folder's safetensors file(s), checks them all, and raises
 that lists every missing tensor, every unexpected one and every wrong shape, in the manner
 of AIR's messages (src/model/qwen2_contract.cpp:14-29).
 
-Precision: in a bfloat16 engine a tensor stored in 16 bits is kept as bfloat16, a tensor
-stored in 32 bits stays in 32 bits, integer tables become int32.  In a float32 engine every
-floating tensor becomes float32 (exact for bfloat16 and float16).
+Precision.  In a float32 engine every floating tensor becomes float32 (exact for bfloat16
+and float16).  In a bfloat16 engine a tensor stored in 16 bits is kept as bfloat16 (float16 is
+rounded to it), integer tables become int32, and a tensor stored in 32 bits stays in 32 bits
+where its part computes with it in 32 bits (``TensorSpec.wide``: norm weights, biases, router
+weights).  A matrix that feeds the tensor cores is another matter: kept in 32 bits it would run
+the CUDA-core product at a few percent of the speed, so a float32-stored operand of a matrix
+product is rounded to bfloat16 (to nearest even), as AIR executes float32, float16 and bfloat16
+checkpoints through one path (src/reference/tensor_reader.cpp:251-255), unless the caller asks
+for ``keep_float32``.  Either way the load says what it did: ``LoadReport`` lists the rounded and
+the kept tensors, and the engine keeps it (``Engine.load_report``).
 """
 from __future__ import annotations
 
 import json
 import os
 import zlib
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -31,6 +38,7 @@ class TensorSpec:
     init: str = "normal"        # "normal": N(0, std);  "one_plus_normal": 1 + N(0, std);  "zeros"
     std: float = 0.02
     integer: bool = False
+    wide: bool = False          # the part computes with this tensor in 32 bits: stored in 32 bits it stays so
 
 
 class WeightError(ValueError):
@@ -64,31 +72,62 @@ def _open_files(folder: str) -> Dict[str, SafetensorsFile]:
         f = SafetensorsFile(single)
         return {n: f for n in f.names()}
     if os.path.exists(index):
-        with open(index) as fh:
-            weight_map = json.load(fh).get("weight_map", {})
+        try:
+            with open(index) as fh:
+                weight_map = json.load(fh).get("weight_map")
+        except json.JSONDecodeError as e:
+            raise SafetensorsError(f"{index} is not valid JSON: {e}") from None
+        if not isinstance(weight_map, dict) or not weight_map:
+            raise SafetensorsError(f"{index} has no 'weight_map'")
         opened: Dict[str, SafetensorsFile] = {}
         for name, shard in weight_map.items():
             if shard not in opened:
-                opened[shard] = SafetensorsFile(os.path.join(folder, shard))
+                path = os.path.join(folder, shard)
+                if not os.path.exists(path):
+                    raise SafetensorsError(f"{index} names the shard {shard}, which is not in {folder}")
+                opened[shard] = SafetensorsFile(path)
             if name not in opened[shard]._entries:
-                raise SafetensorsError(f"{index}: '{name}' is not in {shard}")
+                where = [s for s, f in opened.items() if name in f._entries]
+                raise SafetensorsError(f"{index}: '{name}' is not in {shard}" +
+                                       (f" (it is in {where[0]})" if where else ""))
             files[name] = opened[shard]
+        # a tensor that lies in a shard but that the index does not name is reported as unexpected by the load
+        for shard, f in opened.items():
+            for name in f.names():
+                files.setdefault(name, f)
         return files
     raise SafetensorsError(f"no model.safetensors in {folder}")
 
 
-def stored_dtype_for(engine_dtype: torch.dtype, file_dtype: torch.dtype) -> torch.dtype:
+@dataclass
+class LoadReport:
+    """What a load did to precisions in a bfloat16 engine."""
+    rounded: List[str] = field(default_factory=list)     # stored in 32 bits (or float16), now bfloat16
+    kept_float32: List[str] = field(default_factory=list)
+
+    def summary(self) -> str:
+        out = []
+        if self.rounded:
+            out.append(f"{len(self.rounded)} tensors stored in float32 or float16 were rounded to bfloat16 "
+                       f"(first: {self.rounded[0]}); keep_float32 keeps float32 ones, at the CUDA-core product's speed")
+        if self.kept_float32:
+            out.append(f"{len(self.kept_float32)} tensors stay in float32 (first: {self.kept_float32[0]})")
+        return "; ".join(out)
+
+
+def stored_dtype_for(engine_dtype: torch.dtype, file_dtype: torch.dtype, wide: bool = False,
+                     keep_float32: bool = False) -> torch.dtype:
     if not file_dtype.is_floating_point:
         return torch.int32
     if engine_dtype == torch.float32:
         return torch.float32
-    if file_dtype in (torch.float32, torch.float64):
+    if file_dtype in (torch.float32, torch.float64) and (wide or keep_float32):
         return torch.float32
     return torch.bfloat16
 
 
 def load_tensors(folder: str, specs: Sequence[TensorSpec], engine_dtype: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
+                 device, keep_float32: bool = False, report: Optional[LoadReport] = None) -> Dict[str, torch.Tensor]:
     files = _open_files(folder)
     missing, wrong, found = [], [], {}
     wanted = set()
@@ -103,14 +142,17 @@ def load_tensors(folder: str, specs: Sequence[TensorSpec], engine_dtype: torch.d
         if tuple(shape) != tuple(s.shape):
             wrong.append((s.name, tuple(shape), tuple(s.shape)))
             continue
-        found[s.name] = (f, dt)
+        found[s.name] = (f, dt, s)
     unexpected = sorted(n for n in files if n not in wanted)
     if missing or wrong or unexpected:
         raise WeightError(folder, missing, unexpected, wrong)
     out = {}
-    for name, (f, dt) in found.items():
+    for name, (f, dt, spec) in found.items():
         t = f.tensor(name)
-        out[name] = t.to(device=device, dtype=stored_dtype_for(engine_dtype, dt)).contiguous()
+        target = stored_dtype_for(engine_dtype, dt, spec.wide, keep_float32)
+        if report is not None and engine_dtype != torch.float32 and dt.is_floating_point and dt != torch.bfloat16:
+            (report.rounded if target == torch.bfloat16 else report.kept_float32).append(name)
+        out[name] = t.to(device=device, dtype=target).contiguous()
     return out
 
 

@@ -1,8 +1,13 @@
 #!/usr/bin/env python3
-"""Makes tests/golden/air_reference_tiny.npz: logits of EmersonDowell/AIR's own compiled
-CPU reference executor for a tiny random Qwen2 model.
+"""Makes tests/golden/air_reference_*.npz: logits of EmersonDowell/AIR's own compiled
+CPU reference executor for tiny random Qwen2 models.
 
-    python tests/golden/make_golden.py --reference /path/to/AIR
+    python tests/golden/make_golden.py --reference /path/to/AIR [--config tiny|a|b]
+
+`tiny` (air_reference_tiny.npz) has a head size of 12, which the engine's kernels refuse: it anchors
+the plain implementation alone.  `a` and `b` (air_reference_tiny_a.npz, ..._b.npz) are the two tiny
+configurations that the engine's tests use (head sizes 16 and 32; tied and separate output matrix):
+the GPU tests compare the engine's own float32 logits with AIR's on them.
 
 It draws the weights (numpy, seed 0, rounded to values that bfloat16 holds, so that the
 file stores them as 16-bit words), writes them in the raw form that air_driver.cpp reads,
@@ -30,6 +35,15 @@ CONFIG = {
     "tie_word_embeddings": False, "hidden_act": "silu", "use_sliding_window": False,
 }
 TOKENS = [5, 17, 3, 95, 0, 42, 42, 7, 61, 88, 13, 2, 30, 77, 9, 54, 21, 66, 1, 90, 33, 12, 48, 6]
+BASE = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "use_sliding_window": False}
+CONFIG_A = dict(BASE, num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+                intermediate_size=128, vocab_size=256, max_position_embeddings=128, rope_theta=10000.0,
+                rms_norm_eps=1e-6, tie_word_embeddings=True)
+CONFIG_B = dict(BASE, num_hidden_layers=3, hidden_size=128, num_attention_heads=4, num_key_value_heads=1,
+                intermediate_size=352, vocab_size=384, max_position_embeddings=256, rope_theta=1e6,
+                rms_norm_eps=1e-5, tie_word_embeddings=False)
+CONFIGS = {"tiny": (CONFIG, 0, "air_reference_tiny.npz"), "a": (CONFIG_A, 1, "air_reference_tiny_a.npz"),
+           "b": (CONFIG_B, 2, "air_reference_tiny_b.npz")}
 
 AIR_SOURCES = [
     "src/model/model.cpp", "src/model/storage.cpp", "src/model/qwen2_contract.cpp",
@@ -59,6 +73,8 @@ def draw_weights(config, seed):
 
     t = {"model.embed_tokens.weight": w(v, e, std=1.0), "model.norm.weight": 1 + w(e),
          "lm_head.weight": w(v, e, std=0.1)}
+    if config.get("tie_word_embeddings"):
+        del t["lm_head.weight"]        # AIR ties the output matrix when output.weight is absent
     t["model.norm.weight"] = from_bf16_bits(to_bf16_bits(t["model.norm.weight"]))
     for l in range(config["num_hidden_layers"]):
         p = f"model.layers.{l}."
@@ -98,11 +114,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("AIR_REFERENCE_DIR"), required="AIR_REFERENCE_DIR" not in os.environ,
                     help="a checkout of EmersonDowell/AIR (or set AIR_REFERENCE_DIR)")
-    ap.add_argument("--out", default=os.path.join(HERE, "air_reference_tiny.npz"))
+    ap.add_argument("--config", default="tiny", choices=sorted(CONFIGS))
+    ap.add_argument("--out", default=None)
     args = ap.parse_args()
     ref = args.reference
-    c = CONFIG
-    tensors = draw_weights(c, 0)
+    c, seed, file_name = CONFIGS[args.config]
+    args.out = args.out or os.path.join(HERE, file_name)
+    tensors = draw_weights(c, seed)
+    tokens = TOKENS if args.config == "tiny" else \
+        [int(t) for t in np.random.default_rng(100 + seed).integers(0, c["vocab_size"], size=40)]
     with tempfile.TemporaryDirectory() as tmp:
         exe = os.path.join(tmp, "air_driver")
         cmd = ["g++", "-std=c++20", "-O2", "-I", os.path.join(ref, "include"), "-I", os.path.join(ref, "src"),
@@ -126,11 +146,11 @@ def main():
             f.write("\n".join(lines) + "\n")
         out_bin = os.path.join(tmp, "logits.bin")
         subprocess.check_call([exe, os.path.join(tmp, "manifest.txt"), os.path.join(tmp, "data.bin"), out_bin]
-                              + [str(t) for t in TOKENS])
-        logits = np.fromfile(out_bin, dtype="<f4").reshape(len(TOKENS), c["vocab_size"])
+                              + [str(t) for t in tokens])
+        logits = np.fromfile(out_bin, dtype="<f4").reshape(len(tokens), c["vocab_size"])
     names = sorted(tensors)
     np.savez_compressed(
-        args.out, logits=logits, tokens=np.array(TOKENS, dtype=np.int32), names=np.array(names),
+        args.out, logits=logits, tokens=np.array(tokens, dtype=np.int32), names=np.array(names),
         **{f"w{n}": to_bf16_bits(tensors[name]) for n, name in enumerate(names)},
         **{f"s{n}": np.array(tensors[name].shape) for n, name in enumerate(names)})
     print("wrote", args.out, logits.shape, "max |logit|", float(np.abs(logits).max()))

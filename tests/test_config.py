@@ -68,7 +68,7 @@ def test_window_field_without_the_switch_is_ignored():
 def test_spec_chooses_parts_layer_by_layer():
     w = load_config(util.TINY_W)
     spec = registry.architecture(w.architecture).build_spec(w)
-    assert [b.mixer["window"] for b in spec.layers] == [None, 40, 40]
+    assert [b.part("mixer")["window"] for b in spec.layers] == [None, 40, 40]
     assert [r.layer for r in spec.order] == [0, 1, 2] and spec.output_name == "lm_head.weight"
     model = Model(spec)
     needs = model.cache_needs()

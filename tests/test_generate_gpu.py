@@ -282,3 +282,115 @@ def test_smoke_entry():
     sys.path.insert(0, util.ROOT)
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+@pytest.mark.parametrize("name", ["K", "L"])
+def test_bfloat16_through_the_service_follows_the_plain_implementation(name):
+    """What serving runs and the benchmark times: bfloat16, the tcgen05 products and the tensor-core attention
+    kernels, CUDA graphs, decoding one step ahead with the device's own choice fed back.  Greedy: every produced
+    token is the plain implementation's choice at its place, or lies within twice the tolerance of it (then the
+    comparison ends: the continuations differ).  Several requests of different lengths run together, so the
+    decode graph sees batches that shrink."""
+    from air_b200 import GenerationConfig
+    folder = util.model_folder(name)
+    cfg, tensors = util.plain_model(folder)
+    svc = service(name, "bfloat16", page_tokens=64, max_tokens=4096, decode_ahead=True)
+    assert svc.engine.use_graphs
+    prompts = [util.tokens_for(name, n, 900 + n) for n in (3, 70, 150, 33)]
+    new = [40, 25, 12, 40]
+    out = svc.generate_cohort([(p, GenerationConfig(max_new_tokens=m, stop_on_eos=False)) for p, m in zip(prompts, new)])
+    svc.engine.check_status()
+    assert svc.engine.graphs, "decode steps replayed CUDA graphs"
+    agreed = 0
+    for prompt, m, r in zip(prompts, new, out):
+        assert r.error is None and len(r.tokens) == m
+        ref = util.plain_logits(folder, prompt + r.tokens)           # the logits along the produced tokens
+        scale = max(1.0, float(np.abs(ref).max()))
+        for i, t in enumerate(r.tokens):
+            row = ref[len(prompt) - 1 + i]
+            best = int(row.argmax())
+            assert row[best] - row[t] <= 2 * util.BF16_MAX_TOL * scale, (name, i, t, best)
+            agreed += t == best
+    assert agreed >= 0.9 * sum(new), "nearly every token is the plain implementation's own choice"
+    assert svc.engine.cache.free_pages() == svc.engine.cache.num_pages
+
+
+@pytest.mark.parametrize("ahead", [True, False])
+def test_bfloat16_temperature_runs_repeat_per_seed(ahead):
+    from air_b200 import GenerationConfig, SamplingConfig
+    prompt = util.tokens_for("K", 20, 950)
+    runs = []
+    for seed in (5, 5, 6):
+        svc = service("K", "bfloat16", page_tokens=64, decode_ahead=ahead)
+        g = GenerationConfig(max_new_tokens=30, stop_on_eos=False, sampling=SamplingConfig(0.9, 0, 1.0, seed))
+        runs.append(svc.generate(prompt, g).tokens)
+        svc.engine.check_status()
+    assert runs[0] == runs[1] and runs[0] != runs[2]
+
+
+@pytest.mark.parametrize("ahead", [True, False])
+def test_a_fault_on_the_device_reaches_the_caller(ahead):
+    """The device's status word travels with every step's tokens.  Here it is set from the host between two
+    cycles, as a kernel whose bounded wait ran out would set it: the requests of the step that is read next end
+    with the engine's message for that code, their pages come back, the word is cleared, and the service goes on
+    serving."""
+    from air_b200 import GenerationConfig
+    svc = service("K", "bfloat16", page_tokens=64, decode_ahead=ahead)
+    ids = [svc.submit(util.tokens_for("K", n, 960 + n), GenerationConfig(max_new_tokens=20, stop_on_eos=False))
+           for n in (9, 30)]
+    for _ in range(6):
+        svc.run_cycle()
+    assert len(svc.active) == 2
+    svc.engine.status.fill_(5)
+    for _ in range(3):
+        svc.run_cycle()
+    assert all(svc.finished[i].error == "a wait inside the decode attention kernel ran out" for i in ids)
+    assert all(0 < len(svc.finished[i].tokens) < 20 for i in ids)
+    assert svc.engine.read_status() == 0 and svc.snapshot()["failed_steps"] >= 1
+    assert not svc.active and svc.engine.cache.free_pages() == svc.engine.cache.num_pages
+    r = svc.generate(util.tokens_for("K", 12, 970), GenerationConfig(max_new_tokens=5, stop_on_eos=False))
+    assert r.error is None and len(r.tokens) == 5
+
+
+def test_sizes_that_the_kernels_refuse_are_unsupported_with_exit_code_3(tmp_path):
+    """A head size that config.json allows and the attention kernels do not take (24): "unsupported" when the
+    model is built, exit code 3 from the command line (air-cli's code for a model that cannot be loaded), no
+    traceback."""
+    from air_b200.config import ConfigError
+    from air_b200.engine.engine import Engine, EngineConfig
+    cfg = dict(util.TINY_A, hidden_size=96, num_attention_heads=4, num_key_value_heads=2)
+    folder = str(tmp_path / "m")
+    os.makedirs(folder)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    with pytest.raises(ConfigError, match="unsupported.*head size 24"):
+        Engine.from_folder(folder, EngineConfig(dtype="bfloat16"))
+    with pytest.raises(ConfigError, match="unsupported.*page size"):
+        Engine.from_folder(util.model_folder("A"), EngineConfig(dtype="bfloat16", page_tokens=24))
+    for cmd in (["inspect", folder], ["cuda", folder, "1,2,3"]):
+        p = subprocess.run([sys.executable, os.path.join(util.ROOT, "bin", "air-b200")] + cmd, capture_output=True,
+                           text=True, timeout=300)
+        assert p.returncode == 3 and "unsupported" in p.stderr and "Traceback" not in p.stderr, p.stderr[-500:]
+
+
+def test_a_float32_checkpoint_in_the_bfloat16_engine_runs_the_tensor_core_products(tmp_path):
+    """A checkpoint stored in float32, loaded by the bfloat16 engine: matrices are rounded to bfloat16 at load
+    (and the load says so), so every product runs the kernels of the bfloat16 path; keep_float32 keeps them and
+    runs the CUDA-core product; both agree with the plain implementation on the rounded weights."""
+    from air_b200.engine.batch import Entry
+    from air_b200.engine.engine import Engine, EngineConfig, write_random_model
+    folder = str(tmp_path / "m")
+    write_random_model(folder, util.TINY_K, 3, "float32")
+    rounded = str(tmp_path / "r")
+    write_random_model(rounded, util.TINY_K, 3, "bfloat16")         # the same draws, rounded: what the oracle reads
+    tokens = util.tokens_for("K", 90, 5)
+    want = util.plain_logits(rounded, tokens)
+    engine = Engine.from_folder(folder, EngineConfig(dtype="bfloat16", page_tokens=64, max_tokens=256))
+    assert len(engine.load_report.rounded) > 0 and "rounded to bfloat16" in engine.load_report.summary()
+    assert all(b.mixer.qkv.tc_ok and b.feed_forward.down.tc_ok for b in engine.model.blocks)
+    got = np.concatenate([engine.step([Entry("r", tokens[:80], range(80))]).cpu().numpy()] +
+                         [engine.step([Entry("r", [t], [0])]).cpu().numpy() for t in tokens[80:]])
+    scale = max(1.0, float(np.abs(want).max()))
+    assert np.abs(got - want).max() < util.BF16_MAX_TOL * scale
+    kept = Engine.from_folder(folder, EngineConfig(dtype="bfloat16", page_tokens=64, max_tokens=256, keep_float32=True))
+    assert not kept.model.blocks[0].mixer.qkv.tc_ok and len(kept.load_report.rounded) == 0

@@ -37,6 +37,35 @@ def test_embedding_gathers_rows_and_feeds_back_sampled_tokens(dtype):
     assert torch.equal(out.cpu(), want) and status.item() == 0
     ops().embedding(dev(table), dev(torch.tensor([1000], dtype=torch.int32)), out[:1], status=status)
     assert status.item() == 1 and float(out[0].abs().sum()) == 0.0
+    ops().embedding(dev(table), dev(ids), out, last_token=dev(last), multiplier=14.25)       # rows times a constant
+    assert torch.equal(out.cpu(), want * 14.25)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("parts", [0, 1, 5])
+def test_add_parts_adds_every_form_of_delta_in_order(parts, dtype):
+    """h += delta for a plain [T, E] delta (parts 0) and for partial sums [parts, T, E], added in order."""
+    g = torch.Generator().manual_seed(parts)
+    T, E = 37, 203
+    h = torch.randn(T, E, generator=g)
+    shape = (T, E) if parts == 0 else (parts, T, E)
+    delta = (torch.randn(shape, generator=g) * 100).to(DT[dtype])
+    got = ops().add_parts(dev(h.clone()), dev(delta)).cpu()
+    want = h.clone()
+    for part in (delta.float() if parts else delta.float()[None]):
+        want = want + part                  # float32 additions in the order of the parts
+    assert torch.equal(got, want)
+
+
+def test_logits_post_adds_scales_and_caps():
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(9, 1001, generator=g) * 20
+    bias = torch.randn(1001, generator=g)
+    got = ops().logits_post(dev(logits.clone()), dev(bias), 0.125, 3.0).cpu().double()
+    want = 3.0 * torch.tanh((logits.double() + bias.double()) * 0.125 / 3.0)
+    assert float((got - want).abs().max()) < 2e-6 and float(got.abs().max()) <= 3.0
+    plain_scale = ops().logits_post(dev(logits.clone()), None, 0.5, 0.0).cpu()
+    assert torch.equal(plain_scale, logits * 0.5)
 
 
 @pytest.mark.parametrize("E", [200, 1000, 3584, 5120, 9000])
@@ -569,30 +598,50 @@ def test_prefill_attention_tc_reports_a_list_that_is_not_in_pairs():
     assert status.item() == 8
 
 
-@pytest.mark.parametrize("kernel", ["decode", "prefill", "prefill_tc"])
+@pytest.mark.parametrize("kernel", ["decode", "decode_ldg", "fresh", "prefill", "prefill_tc"])
 @pytest.mark.parametrize("n,w", [(300, 37), (300, 64), (257, 129), (200, 200), (70, 1), (129, 2)])
-def test_window_edge_is_exact_in_the_tensor_core_kernels(kernel, n, w):
+@pytest.mark.parametrize("P,holes", [(64, False), (16, True), (32, True)])
+def test_window_edge_is_exact_in_the_tensor_core_kernels(kernel, n, w, P, holes):
     """The key at distance w - 1 from the last query counts, the key at distance w does not: one of them
     at a time is made to stand out, and the last token's output either is its value or is not.  The
-    window's edge falls inside a tile of keys, on a tile's first key and on a page's first key."""
-    H, K, d, P = 4, 2, 128 if kernel != "prefill" else 256, 64
-    q_len = 1 if kernel == "decode" else 40
-    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [q_len], "bfloat16", seed=n + w, num_pages=8)
+    window's edge falls inside a tile of keys, on a tile's first key and on a page's first key.  With
+    `holes` the table has -1 where the cache manager has taken pages back: below the first block that the
+    query can see.  Every kernel that generation runs is here: the decode kernel fed by the copy engine and
+    the one whose warps load the keys themselves, the decode kernel that starts from the q/k/v product, and
+    the two tile kernels."""
+    H, K, d = 4, 2, 128 if kernel != "prefill" else 256
+    q_len = 1 if kernel in ("decode", "decode_ldg", "fresh") else 40
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [q_len], "bfloat16", seed=n + w,
+                                                         num_pages=-(-n // P) + 3)
     q[:] = 0.5
     last = n - 1
+    if holes:       # what the manager gives back: blocks that no query of this step can see
+        first_query = n - q_len
+        bt[0, : max(0, first_query - w + 1) // P] = -1
+    scale = 1.0 / math.sqrt(d)
     for key, visible in ((last - w + 1, True), (last - w, False)):
-        if key < 0:
+        if key < 0 or bt[0, key // P] < 0:
             continue
         c = cache.copy()
         c[bt[0, key // P], 0, :, key % P, :] = 8.0
         out = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
         args = (dev(q, torch.bfloat16), dev(c, torch.bfloat16), dev(bt))
-        if kernel == "decode":
-            ops().decode_attention(*args, dev(seq_of), dev(positions), out, w, 1.0 / math.sqrt(d))
+        if kernel in ("decode", "decode_ldg"):
+            ops().decode_attention(*args, dev(seq_of), dev(positions), out, w, scale,
+                                   engine="tma" if kernel == "decode" else "ldg")
+        elif kernel == "fresh":
+            # the product's output: q, and the last token's own key and value, which the kernel writes itself;
+            # a table that rotates by nothing, so that q and the keys stay what they are
+            own_k = np.full((K, d), 8.0, dtype=np.float32) if key == last else ks[0][last]
+            qkv = np.concatenate([q[0].reshape(-1), own_k.reshape(-1), vs[0][last].reshape(-1)])[None, :]
+            table = np.concatenate([np.ones((n, d // 2)), np.zeros((n, d // 2))], axis=1)     # cos | sin
+            c[bt[0, last // P], :, :, last % P, :] = -3.0          # what lies at the new token's place beforehand
+            ops().decode_attention_fresh(dev(qkv.astype(np.float32)), None, dev(table.astype(np.float32)),
+                                         dev(c, torch.bfloat16), dev(bt), dev(seq_of), dev(positions), out, H, w, scale)
         elif kernel == "prefill":
-            ops().prefill_attention(*args, dev(tiles_for([n], [q_len])), out, w, 1.0 / math.sqrt(d))
+            ops().prefill_attention(*args, dev(tiles_for([n], [q_len])), out, w, scale)
         else:
-            ops().prefill_attention_tc(*args, dev(tiles_for([n], [q_len])), out, w, 1.0 / math.sqrt(d))
+            ops().prefill_attention_tc(*args, dev(tiles_for([n], [q_len])), out, w, scale)
         hit = np.abs(out.float().cpu().numpy()[-1, 0] - vs[0][key, 0]).max() < 3e-2
         assert hit == visible, (key, visible)
 

@@ -5,21 +5,26 @@ import os
 import numpy as np
 
 from plain import qwen2_plain as plain
-from golden.make_golden import CONFIG, from_bf16_bits
+import pytest
+
+from golden.make_golden import CONFIG, CONFIGS, from_bf16_bits
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "air_reference_tiny.npz")
 
 
-def load_golden():
-    z = np.load(GOLDEN)
+def load_golden(which="tiny"):
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", CONFIGS[which][2]))
     names = [str(n) for n in z["names"]]
     tensors = {name: from_bf16_bits(z[f"w{i}"]).reshape(z[f"s{i}"]) for i, name in enumerate(names)}
     return tensors, z["tokens"].tolist(), z["logits"]
 
 
-def test_plain_matches_air_reference_executor():
-    tensors, tokens, golden = load_golden()
-    logits = plain.forward(CONFIG, tensors, tokens)
+@pytest.mark.parametrize("which", ["tiny", "a", "b"])
+def test_plain_matches_air_reference_executor(which):
+    """AIR's own compiled CPU executor, token by token, on three tiny models: one of odd sizes, and the two
+    tiny configurations of the engine's tests (tied and separate output matrix, groups of 2 and of 4)."""
+    tensors, tokens, golden = load_golden(which)
+    logits = plain.forward(CONFIGS[which][0], tensors, tokens)
     assert logits.shape == golden.shape
     assert np.abs(logits - golden).max() <= 2e-6 * max(1.0, np.abs(golden).max())
     assert (logits.argmax(-1) == golden.argmax(-1)).all()
@@ -82,3 +87,47 @@ def test_mt19937_64_first_outputs():
     for _ in range(9999):
         g.next()
     assert g.next() == 9981545732273789042
+
+
+def test_the_replay_models_would_show_a_missing_rotation_and_a_window_off_by_one():
+    """A test of the tests.  The replay suite compares bfloat16 logits with the plain implementation within
+    BF16_MAX_TOL / BF16_MEAN_TOL.  That can only catch a fault whose effect is larger than the tolerance, so for
+    every configuration of that suite: the plain implementation without any position encoding, and (where layers
+    have a window) with a window one key too wide, differs from itself by at least three times one of the two
+    tolerances (a replay fails when either is exceeded).
+    (With q and k drawn at N(0, 0.02) like the other matrices it does not: tests/util.py sharpen_attention.)"""
+    import util
+    for name in ("A", "B", "W", "K", "L", "M"):
+        folder = util.model_folder(name)
+        config, tensors = plain.read_model(folder)
+        tokens = util.tokens_for(name, 150, 1)
+        ref = plain.forward(config, tensors, tokens)
+        scale = max(1.0, float(np.abs(ref).max()))
+        rotate = plain.rope
+        try:
+            plain.rope = lambda x, positions, theta: x
+            faulty = [("no rotation", plain.forward(config, tensors, tokens))]
+        finally:
+            plain.rope = rotate
+        if config.get("use_sliding_window"):
+            wider = dict(config, sliding_window=config["sliding_window"] + 1)
+            faulty.append(("window + 1", plain.forward(wider, tensors, tokens)))
+        for what, logits in faulty:
+            diff = np.abs(logits - ref)
+            assert (diff.max() > 3 * util.BF16_MAX_TOL * scale or
+                    diff.mean(1).max() > 3 * util.BF16_MEAN_TOL * scale), (name, what, float(diff.max()),
+                                                                           float(diff.mean(1).max()))
+        # attention has something to look at: the largest probability is many times the uniform one
+        p = f"model.layers.0.self_attn."
+        heads, kv = config["num_attention_heads"], config["num_key_value_heads"]
+        d = config["hidden_size"] // heads
+        x = plain.rms_norm(plain.embed(tensors["model.embed_tokens.weight"], np.asarray(tokens)),
+                           tensors["model.layers.0.input_layernorm.weight"], config["rms_norm_eps"])
+        pos = np.arange(len(tokens))
+        q = plain.rope(plain.linear(x, tensors[p + "q_proj.weight"], tensors[p + "q_proj.bias"]).reshape(-1, heads, d),
+                       pos, config["rope_theta"])
+        k = plain.rope(plain.linear(x, tensors[p + "k_proj.weight"], tensors[p + "k_proj.bias"]).reshape(-1, kv, d),
+                       pos, config["rope_theta"])
+        scores = (q[-1, 0].astype(np.float64) @ k[:, 0].astype(np.float64).T) / np.sqrt(d)
+        prob = np.exp(scores - scores.max())
+        assert prob.max() / prob.sum() > 5.0 / len(tokens), name

@@ -160,6 +160,7 @@ def test_random_configurations_and_traces(seed, dtype):
     cfg = random_configuration(rng)
     with tempfile.TemporaryDirectory() as folder:
         write_random_model(folder, cfg, seed, "bfloat16")
+        util.sharpen_attention(folder, cfg)
         lengths = [int(x) for x in rng.integers(1, 330, size=int(rng.integers(3, 8)))]
         streams = {f"r{i}": rng.integers(0, cfg["vocab_size"], size=m).tolist() for i, m in enumerate(lengths)}
         steps = util.trace_mixed(streams, seed=seed, live=int(rng.integers(1, 5)), tail=int(rng.integers(1, 20)),
@@ -209,3 +210,91 @@ def test_out_of_pages_is_an_error_that_changes_nothing():
     got = engine.step([Entry("a", toks[40:45], [4])]).cpu().numpy()
     ref = util.plain_logits(folder, toks[:45])
     assert np.abs(got[0] - ref[44]).max() < util.FP32_TOL * max(1, np.abs(ref).max())
+
+
+# ------------------------------------------------------------------ the widths of a large model
+WIDE = dict(util.BASE, num_hidden_layers=2, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+            intermediate_size=18944, vocab_size=2999, max_position_embeddings=1024, rope_theta=1e6,
+            rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False)
+_wide = {}
+
+
+def wide_model():
+    """Two layers with the layer sizes of the 7-billion-parameter shape that the benchmark runs (hidden 3584,
+    28 query heads of 128 in 4 groups, feed-forward 18944) under a small vocabulary that is no multiple of
+    anything: the engine's choices at these sizes (tile widths, parts of k, gate and up rows interleaved in
+    blocks of 128, 256-row tiles, the decode kernel that starts from the q/k/v product at 7 heads a group) meet
+    the plain implementation here and nowhere else."""
+    if not _wide:
+        from air_b200.engine.engine import write_random_model
+        d = tempfile.TemporaryDirectory(prefix="air_b200_wide_")
+        write_random_model(d.name, WIDE, 11, "bfloat16")
+        util.sharpen_attention(d.name, WIDE)
+        rng = np.random.default_rng(77)
+        _wide["folder"], _wide["keep"] = d.name, d
+        _wide["streams"] = {f"w{i}": rng.integers(0, WIDE["vocab_size"], size=n).tolist()
+                            for i, n in enumerate((150, 67, 3, 200))}
+    return _wide["folder"], _wide["streams"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("regime", ["whole", "bulk_tail", "portions", "mixed"])
+def test_the_layer_sizes_of_the_benchmark_shape(regime, dtype):
+    folder, streams = wide_model()
+    steps = {"whole": util.trace_whole, "bulk_tail": util.trace_bulk_tail, "portions": util.trace_portions,
+             "mixed": lambda s: util.trace_mixed(s, seed=2, live=3)}[regime](streams)
+    got, engine = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps), page_tokens=64)
+    util.check_against_plain(got, folder, streams, dtype)
+    if dtype == "bfloat16":
+        block = engine.model.blocks[0]
+        assert block.feed_forward.gate_up.gate_up_block == 128 and block.mixer.qkv.tc_ok
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_of_more_than_4096_rows(dtype):
+    """A prompt portion longer than the largest step that the fused gate/up product takes (4,096 rows): the
+    library's product and the activation kernel over the interleaved rows; then a second portion and single
+    tokens on top of that context.  K with room for 5,000 positions."""
+    from air_b200.engine.engine import write_random_model
+    cfg = dict(util.TINY_K, max_position_embeddings=5120)
+    with tempfile.TemporaryDirectory() as folder:
+        write_random_model(folder, cfg, 21, "bfloat16")
+        util.sharpen_attention(folder, cfg)
+        toks = np.random.default_rng(5).integers(0, cfg["vocab_size"], size=4300).tolist()
+        want_rows = [0, 1, 63, 64, 2047, 4095, 4096, 4199]
+        steps = [util.step_line(0, [("r", toks[:4200], want_rows)]),
+                 util.step_line(1, [("r", toks[4200:4290], [0, 89])])]
+        steps += [util.step_line(2 + i, [("r", [toks[4290 + i]], [0])], end=["r"] if i == 9 else []) for i in range(10)]
+        got, _ = util.replay(folder, dtype, steps, max_tokens=4352, page_tokens=64)
+        from plain import qwen2_plain as plain
+        pcfg, tensors = plain.read_model(folder)
+        ref = plain.forward(pcfg, tensors, toks)
+        scale = max(1.0, float(np.abs(ref).max()))
+        for (rid, p), row in got.items():
+            diff = np.abs(row - ref[p])
+            if dtype == "float32":
+                assert diff.max() <= util.FP32_TOL * scale, p
+            else:
+                assert diff.max() <= util.BF16_MAX_TOL * scale and diff.mean() <= util.BF16_MEAN_TOL * scale, p
+        assert sorted(p for _, p in got) == want_rows + [4200, 4289] + list(range(4290, 4300))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_three_hundred_requests_decode_in_one_step(dtype):
+    """More single tokens in one step than the largest captured graph holds (256): the step's kernels are launched
+    one by one."""
+    name = "K"
+    folder = util.model_folder(name)
+    streams = {f"r{i}": util.tokens_for(name, 6 + i % 7, 2000 + i) for i in range(300)}
+    ids = list(streams)
+    steps, n = [], 0
+    for i in range(0, 300, 30):
+        steps.append(util.step_line(n, [(r, streams[r][:-2], range(len(streams[r]) - 2)) for r in ids[i:i + 30]]))
+        n += 1
+    for k in (2, 1):
+        steps.append(util.step_line(n, [(r, [streams[r][-k]], [0]) for r in ids], end=ids if k == 1 else []))
+        n += 1
+    got, engine = util.replay(folder, dtype, steps, max_tokens=util.peak_tokens(steps, page=16), page_tokens=16,
+                              max_requests=300)
+    util.check_against_plain(got, folder, streams, dtype)
+    assert all(size <= 256 for size in engine.graphs)

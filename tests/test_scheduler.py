@@ -6,45 +6,93 @@ import pytest
 import torch
 
 from air_b200.cache.manager import CacheManager, OutOfPages
-from air_b200.engine.scheduler import (CapacityScheduler, MicrobatchScheduler, SchedulableSequence as Seq,
-                                       WorkPhase)
+from air_b200.engine.scheduler import Runnable, StepScheduler
 from air_b200.engine.service import InferenceService, QueueFull, SchedulerConfig
 from air_b200.parts.base import PagedKV
 from air_b200.sampling.sampler import GenerationConfig, SamplingConfig
 
-P, D = WorkPhase.prefill, WorkPhase.decode
+
+def prompt(request, tokens, done=0):
+    return Runnable(request, list(range(tokens)), done)
 
 
-def test_capacity_arithmetic():
-    c = CapacityScheduler(max_active_requests=2)
-    assert c.evaluate(0, 0, 10, 16, 160).admit                      # exact fit
-    assert c.evaluate(0, 0, 10, 16, 161).reason == "device-capacity"
-    assert c.evaluate(1, 6, 10, 16, 64).admit and not c.evaluate(1, 7, 10, 16, 64).admit
-    assert c.evaluate(2, 0, 10, 16, 1).reason == "max-active-requests"
-    assert c.evaluate(0, 0, 10, 16, 17).reservation_pages == 2
+def decoding(request, last=7):
+    return Runnable(request, [1, 2], 2, last_token=last)
+
+
+def shape(plan):
+    return [(e.request, len(e.tokens), list(e.want)) for e in plan.entries]
+
+
+def test_admission_arithmetic():
+    s = StepScheduler(max_active=2, token_budget=64, portion_limit=64, page_tokens=16)
+    assert s.admit(0, 0, 10, 160).admit                                   # exact fit
+    assert s.admit(0, 0, 10, 161).reason == "device-capacity"
+    assert s.admit(1, 6, 10, 64).admit and not s.admit(1, 7, 10, 64).admit
+    assert s.admit(2, 0, 10, 1).reason == "max-active-requests"
+    assert s.admit(0, 0, 10, 17).pages == 2
+    with pytest.raises(ValueError):
+        StepScheduler(0, 1, 1, 16)
 
 
 def test_decode_first_then_prompts_under_the_budget():
-    s = MicrobatchScheduler()
-    batch = s.schedule([Seq("p1", P, 4), Seq("d1", D, 1), Seq("p2", P, 4), Seq("d2", D, 1)], 5)
-    assert [(x.slot, x.token_count) for x in batch.slices] == [("d1", 1), ("d2", 1), ("p1", 3)]
-    assert (batch.token_count, batch.decode_tokens, batch.prefill_tokens, batch.prefill_sequences) == (5, 2, 3, 1)
+    s = StepScheduler(8, token_budget=5, portion_limit=4, page_tokens=16)
+    plan = s.plan([prompt("p1", 4), decoding("d1", 30), prompt("p2", 4), decoding("d2", 31)])
+    assert shape(plan) == [("d1", 1, [0]), ("d2", 1, [0]), ("p1", 3, [])]
+    assert plan.entries[0].tokens == [30] and plan.entries[2].tokens == [0, 1, 2]
+    assert (plan.tokens, plan.decode_tokens, plan.prompt_tokens, plan.portions) == (5, 2, 3, [("p1", 3)])
+    assert plan.graph_size is None                       # a step with a prompt portion replays no graph
 
 
-def test_per_sequence_caps_and_zero_limits():
-    s = MicrobatchScheduler()
-    batch = s.schedule([Seq("a", P, 4), Seq("z", P, 0), Seq("b", P, 4), Seq("c", P, 4)], 9)
-    assert [(x.slot, x.token_count) for x in batch.slices] == [("a", 4), ("b", 4), ("c", 1)]
-    assert s.schedule([Seq("a", P, 4)], 0).slices == [] and s.schedule([], 9).slices == []
+def test_portion_limits_last_portions_and_empty_plans():
+    s = StepScheduler(8, token_budget=9, portion_limit=4, page_tokens=16)
+    plan = s.plan([prompt("a", 4), prompt("b", 9), prompt("c", 4)])
+    # a's portion ends its prompt and wants its logits; b is cut by the limit; c by what is left of the budget
+    assert shape(plan) == [("a", 4, [3]), ("b", 4, []), ("c", 1, [])]
+    assert s.plan([]).entries == []
+    no_token = Runnable("z", [5, 6], 0, wants_token=False)        # max_new_tokens == 0: nothing is asked for
+    assert shape(StepScheduler(8, 9, 4, 16).plan([no_token])) == [("z", 2, [])]
 
 
-def test_rotation_under_a_budget_of_one():
-    s = MicrobatchScheduler()
-    cands = [Seq("a", D, 1), Seq("b", D, 1), Seq("c", D, 1)]
-    assert [s.schedule(cands, 1).slices[0].slot for _ in range(6)] == ["a", "b", "c", "a", "b", "c"]
-    s = MicrobatchScheduler()
-    cands = [Seq("x", P, 8), Seq("y", P, 8)]
-    assert [s.schedule(cands, 8).slices[0].slot for _ in range(4)] == ["x", "y", "x", "y"]
+def test_rotation_when_the_budget_does_not_reach_everybody():
+    s = StepScheduler(8, token_budget=1, portion_limit=8, page_tokens=16)
+    cands = [decoding("a"), decoding("b"), decoding("c")]
+    assert [s.plan(cands).entries[0].request for _ in range(6)] == ["a", "b", "c", "a", "b", "c"]
+    s = StepScheduler(8, token_budget=2, portion_limit=8, page_tokens=16)
+    served = [tuple(e.request for e in s.plan(cands).entries) for _ in range(3)]
+    assert served == [("a", "b"), ("c", "a"), ("b", "c")]         # everybody twice in three steps
+    s = StepScheduler(8, token_budget=8, portion_limit=8, page_tokens=16)
+    cands = [prompt("x", 100), prompt("y", 100)]
+    assert [s.plan(cands).entries[0].request for _ in range(4)] == ["x", "y", "x", "y"]
+
+
+def test_cut_portions_end_on_a_row_tile_or_a_page():
+    s = StepScheduler(8, token_budget=300, portion_limit=300, page_tokens=16, row_tile=128)
+    # 300 tokens from position 40 would end at 340: shortened to end at 256, a row tile
+    assert s.plan([prompt("a", 1000, done=40)]).portions == [("a", 216)]
+    # a portion that ends its prompt is not shortened
+    assert s.plan([prompt("a", 340, done=40)]).portions == [("a", 300)]
+    s = StepScheduler(8, token_budget=50, portion_limit=50, page_tokens=16, row_tile=128)
+    assert s.plan([prompt("a", 1000, done=100)]).portions == [("a", 28)]      # ends at 128
+    assert s.plan([prompt("a", 1000, done=130)]).portions == [("a", 46)]      # no tile edge within reach: page edge 176
+    s = StepScheduler(8, token_budget=6, portion_limit=6, page_tokens=16, row_tile=128)
+    assert s.plan([prompt("a", 1000, done=2)]).portions == [("a", 6)]         # no edge within reach: as it is
+    # whatever the cuts, a prompt is run completely and in order
+    s = StepScheduler(8, token_budget=77, portion_limit=53, page_tokens=16, row_tile=128)
+    done, seen = 0, []
+    while done < 1000:
+        (entry,) = s.plan([prompt("a", 1000, done=done)]).entries
+        seen += entry.tokens
+        done += len(entry.tokens)
+        assert entry.want == ([len(entry.tokens) - 1] if done == 1000 else [])
+    assert seen == list(range(1000))
+
+
+def test_a_decode_step_names_the_graph_it_replays():
+    s = StepScheduler(128, token_budget=128, portion_limit=8, page_tokens=16, graph_sizes=(1, 2, 4, 8, 64, 96))
+    assert s.plan([decoding(i) for i in range(3)]).graph_size == 4
+    assert s.plan([decoding(i) for i in range(65)]).graph_size == 96
+    assert s.plan([decoding(i) for i in range(100)]).graph_size is None     # beyond the last graph: launched one by one
 
 
 # ------------------------------------------------------------------ the service over a fake engine
@@ -91,6 +139,15 @@ class FakeEngine:
 
     def finish(self, request):
         self.cache.close(request)
+
+    status_word = 0          # what a kernel would have left in the device's status word
+
+    def read_status(self):
+        return self.status_word
+
+    def clear_status(self, code):
+        self.status_word = 0
+        return f"device fault {code}"
 
 
 def test_prompt_in_portions_then_decode_and_pages_back():
@@ -142,6 +199,26 @@ def test_admission_waits_for_reserved_pages_and_fails_what_never_fits():
     assert svc.finished[a].tokens == list(range(30, 40)) and svc.finished[b].tokens == list(range(20, 30))
     assert svc.finished[c].error == "insufficient KV pages for one sequence" and svc.finished[c].tokens == []
     assert eng.cache.free_pages() == 4
+
+
+def test_a_fault_that_the_device_reports_fails_the_requests_of_that_step():
+    """The status word is read with every step's tokens.  When a kernel has set it, the requests of that
+    step end with the fault's message (and the tokens they had), their pages go back, the word is cleared,
+    and requests that come later are served."""
+    eng = FakeEngine(pages=16)
+    svc = InferenceService(eng, SchedulerConfig(max_active_requests=4))
+    a = svc.submit([1, 2, 3], GenerationConfig(max_new_tokens=8))
+    b = svc.submit([4, 5], GenerationConfig(max_new_tokens=8))
+    for _ in range(3):
+        svc.run_cycle()
+    assert len(svc.active) == 2 and all(len(i.generated) == 3 for i in svc.active)
+    eng.status_word = 3
+    svc.run_cycle()
+    assert svc.finished[a].error == "device fault 3" and svc.finished[b].error == "device fault 3"
+    assert svc.finished[a].tokens == [4, 5, 6] and eng.status_word == 0
+    assert not svc.active and eng.cache.free_pages() == 16 and svc.snapshot()["failed_steps"] == 1
+    r = svc.generate([7], GenerationConfig(max_new_tokens=3))
+    assert r.error is None and r.tokens == [8, 9, 10]
 
 
 def test_queue_is_bounded_and_requests_are_checked():

@@ -63,19 +63,86 @@ def test_absent_biases_are_allowed_as_in_air(tmp_path):
     assert not any(n.endswith(".bias") for n in got)
 
 
-def test_precision_kept_as_stored(tmp_path):
+def test_precision_rule_of_a_bfloat16_engine(tmp_path):
+    """float32 engine: everything float32.  bfloat16 engine: a 32-bit tensor that its part computes with in 32
+    bits (norm weights, biases) stays 32-bit; a 32-bit matrix is rounded to bfloat16 (to nearest even) and the
+    load says so, unless the caller asks to keep it; float16 is rounded to bfloat16."""
+    from air_b200.weights.loader import LoadReport
     write_random_model(str(tmp_path), util.TINY_A, 0, "bfloat16")
     f = SafetensorsFile(str(tmp_path / "model.safetensors"))
     tensors = {n: f.tensor(n).clone() for n in f.names()}
+    del f
+    wide = tensors["model.layers.0.mlp.down_proj.weight"].float() + 1e-4       # not representable in bfloat16
     tensors["model.norm.weight"] = tensors["model.norm.weight"].float()
+    tensors["model.layers.0.self_attn.q_proj.bias"] = tensors["model.layers.0.self_attn.q_proj.bias"].float()
+    tensors["model.layers.0.mlp.down_proj.weight"] = wide
+    tensors["model.layers.1.mlp.down_proj.weight"] = tensors["model.layers.1.mlp.down_proj.weight"].to(torch.float16)
     write_safetensors(str(tmp_path / "model.safetensors"), tensors)
     specs = specs_for(util.TINY_A)
-    bf = load_tensors(str(tmp_path), specs, torch.bfloat16, "cpu")
-    assert bf["model.norm.weight"].dtype == torch.float32          # stored in 32 bits: stays
+    report = LoadReport()
+    bf = load_tensors(str(tmp_path), specs, torch.bfloat16, "cpu", report=report)
+    assert bf["model.norm.weight"].dtype == torch.float32                    # computed with in 32 bits: stays
+    assert bf["model.layers.0.self_attn.q_proj.bias"].dtype == torch.float32
     assert bf["model.embed_tokens.weight"].dtype == torch.bfloat16
+    assert bf["model.layers.0.mlp.down_proj.weight"].dtype == torch.bfloat16  # a matrix: rounded, never a silent slow path
+    assert torch.equal(bf["model.layers.0.mlp.down_proj.weight"], wide.to(torch.bfloat16))
+    assert bf["model.layers.1.mlp.down_proj.weight"].dtype == torch.bfloat16
+    assert sorted(report.rounded) == ["model.layers.0.mlp.down_proj.weight", "model.layers.1.mlp.down_proj.weight"]
+    assert sorted(report.kept_float32) == ["model.layers.0.self_attn.q_proj.bias", "model.norm.weight"]
+    assert "rounded to bfloat16" in report.summary()
+    kept = load_tensors(str(tmp_path), specs, torch.bfloat16, "cpu", keep_float32=True)
+    assert kept["model.layers.0.mlp.down_proj.weight"].dtype == torch.float32
+    assert torch.equal(kept["model.layers.0.mlp.down_proj.weight"], wide)
     fp = load_tensors(str(tmp_path), specs, torch.float32, "cpu")
     assert all(t.dtype == torch.float32 for t in fp.values())
     assert torch.equal(fp["model.embed_tokens.weight"], bf["model.embed_tokens.weight"].float())
+
+
+def test_a_folder_of_shards_with_an_index(tmp_path):
+    """model.safetensors.index.json maps every tensor to its shard, the form that large checkpoints have.  The
+    load finds tensors by name whatever the files are (AIR: src/model/model.cpp:75-87); an index that puts a
+    tensor in the wrong shard, or names a shard that is missing, is an error that says which."""
+    folder = tmp_path / "m"
+    write_random_model(str(folder), util.TINY_B, 1, "bfloat16")
+    specs = specs_for(util.TINY_B)
+    whole = load_tensors(str(folder), specs, torch.bfloat16, "cpu")
+    f = SafetensorsFile(str(folder / "model.safetensors"))
+    names = sorted(f.names())
+    shards = {"model-00001-of-00002.safetensors": names[: len(names) // 2],
+              "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for shard, members in shards.items():
+        write_safetensors(str(folder / shard), {n: f.tensor(n).clone() for n in members})
+    del f
+    (folder / "model.safetensors").unlink()
+    index = {"metadata": {}, "weight_map": {n: shard for shard, members in shards.items() for n in members}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    got = load_tensors(str(folder), specs, torch.bfloat16, "cpu")
+    assert got.keys() == whole.keys() and all(torch.equal(got[k], whole[k]) for k in whole)
+    # the index puts a tensor into the wrong shard
+    wrong = dict(index["weight_map"])
+    moved = shards["model-00001-of-00002.safetensors"][0]
+    wrong[moved] = "model-00002-of-00002.safetensors"
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wrong}))
+    with pytest.raises(SafetensorsError, match=f"'{moved}' is not in model-00002-of-00002.safetensors"):
+        load_tensors(str(folder), specs, torch.bfloat16, "cpu")
+    # a shard is missing
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    (folder / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(SafetensorsError, match="names the shard model-00002-of-00002.safetensors"):
+        load_tensors(str(folder), specs, torch.bfloat16, "cpu")
+    # a tensor that the index does not name: missing for the model, in ONE error with the rest
+    write_safetensors(str(folder / "model-00002-of-00002.safetensors"),
+                      {n: whole[n] for n in shards["model-00002-of-00002.safetensors"]})
+    fewer = {k: v for k, v in index["weight_map"].items() if k != "model.norm.weight"}
+    write_safetensors(str(folder / "model-00001-of-00002.safetensors"),
+                      {n: whole[n] for n in shards["model-00001-of-00002.safetensors"] if n != "model.norm.weight"})
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": fewer}))
+    if "model.norm.weight" in shards["model-00002-of-00002.safetensors"]:
+        write_safetensors(str(folder / "model-00002-of-00002.safetensors"),
+                          {n: whole[n] for n in shards["model-00002-of-00002.safetensors"] if n != "model.norm.weight"})
+    with pytest.raises(WeightError) as e:
+        load_tensors(str(folder), specs, torch.bfloat16, "cpu")
+    assert e.value.missing == ["model.norm.weight"]
 
 
 def test_malformed_files(tmp_path):

@@ -73,26 +73,54 @@ def reference(q, cache, table, positions, P):
     return out
 
 
+def free_bytes():
+    """Free device memory as the driver counts it (cudaMemGetInfo): any allocation, by whatever route, shows."""
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]
+
+
 def test_two_calls_in_a_row_match_the_allocating_entry_point():
     from air_b200.csrc import ops
     lib = library()
     H, K, d, P, splits = 14, 2, 128, 16, 5
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, lens in ((1, [300, 17, 1, 64, 129]), (2, [40, 500, 33])):
+    for call, (seed, lens) in enumerate(((1, [300, 17, 1, 64, 129]), (2, [40, 500, 33, 7]))):
         q, cache, table, slots, positions = case(seed, H, K, d, P, lens)
-        want = torch.empty_like(q)
+        if call == 1:
+            slots[2] = -1         # a padding token: skipped; its place in the shared scratch holds the first call's numbers
+        want = torch.full_like(q, 3.0)
         ops.decode_attention(q, cache, table, slots, positions, want, 0, 1 / math.sqrt(d), splits=splits)
         got = torch.full_like(q, 3.0)
         assert lib.air_decode_attention_static_need(len(lens), H, d, splits) <= lib.air_decode_attention_static_capacity()
+        before = free_bytes()
         rc = lib.air_decode_attention_static(q.data_ptr(), cache.data_ptr(), table.data_ptr(), table.shape[1],
                                              slots.data_ptr(), positions.data_ptr(), got.data_ptr(), len(lens), H, K,
                                              d, P, 0, 1 / math.sqrt(d), splits, stream)
         assert rc == 0, lib.air_decode_attention_static_error(rc).decode()
+        if call == 1:     # (the first call on a device may load the kernels' code; the second finds everything there)
+            assert free_bytes() == before, "the entry point obtained device memory"
         torch.cuda.synchronize()
         ref = reference(q, cache, table, positions, P)
+        live = (slots >= 0).cpu()
         scale = max(1.0, float(ref.abs().max()))
-        assert float((got.double().cpu() - want.double().cpu()).abs().max()) <= 1e-2 * scale
-        assert float((got.double().cpu() - ref).abs().max()) <= 1e-2 * scale
+        assert float((got.double().cpu() - want.double().cpu())[live].abs().max()) <= 1e-2 * scale
+        assert float((got.double().cpu() - ref)[live].abs().max()) <= 1e-2 * scale
+        assert bool((got[~live.cuda()] == 3.0).all()), "nothing is stored for a padding token"
+
+
+def test_sizes_that_the_kernel_does_not_take_are_a_bad_argument_not_a_scratch_error():
+    lib = library()
+    H, K, d, P = 8, 2, 128, 16
+    q, cache, table, slots, positions = case(4, H, K, d, P, [20] * 4)
+    out = torch.full_like(q, 5.0)
+    stream = torch.cuda.current_stream().cuda_stream
+    for h, k, dd, pp, splits in ((8, 2, 96, 16, 4), (8, 3, 128, 16, 4), (8, 2, 128, 24, 4), (8, 2, 4096, 16, 32)):
+        rc = lib.air_decode_attention_static(q.data_ptr(), cache.data_ptr(), table.data_ptr(), table.shape[1],
+                                             slots.data_ptr(), positions.data_ptr(), out.data_ptr(), 4, h, k, dd, pp,
+                                             0, 0.1, splits, stream)
+        assert rc == 100001, (h, k, dd, pp, rc)
+    torch.cuda.synchronize()
+    assert bool((out == 5.0).all())
 
 
 def test_a_call_beyond_the_built_in_scratch_is_refused():

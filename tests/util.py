@@ -13,12 +13,15 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 BASE = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu"}
 
-# Two tiny configurations that differ in every size and option, and a third with a window.
+# Two tiny configurations that differ in every size and option, and a third with a window.  A and B are the
+# two tiny configurations that this engine's target names (2 layers / 64 / 4 heads of 16 in 2 groups / 128 / 256,
+# tied; 3 layers / 128 / 4 heads of 32 in 1 group / 352 / 384, separate output matrix), but for A's
+# max_position_embeddings, which is 512 here instead of 128 because the replay tests run longer requests.
 TINY_A = dict(BASE, num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
               intermediate_size=128, vocab_size=256, max_position_embeddings=512, rope_theta=10000.0,
               rms_norm_eps=1e-6, tie_word_embeddings=True, use_sliding_window=False)
-TINY_B = dict(BASE, num_hidden_layers=3, hidden_size=192, num_attention_heads=6, num_key_value_heads=1,
-              intermediate_size=352, vocab_size=387, max_position_embeddings=640, rope_theta=1e6,
+TINY_B = dict(BASE, num_hidden_layers=3, hidden_size=128, num_attention_heads=4, num_key_value_heads=1,
+              intermediate_size=352, vocab_size=384, max_position_embeddings=256, rope_theta=1e6,
               rms_norm_eps=1e-5, tie_word_embeddings=False, use_sliding_window=False, sliding_window=4096)
 TINY_W = dict(BASE, num_hidden_layers=3, hidden_size=96, num_attention_heads=3, num_key_value_heads=3,
               intermediate_size=208, vocab_size=301, max_position_embeddings=512, rope_theta=50000.0,
@@ -43,10 +46,38 @@ _folders = {}
 _tmp = []
 
 
-def model_folder(name, dtype="bfloat16", scale=None):
+SCORE_STD = 2.5     # standard deviation of the attention scores that the test models are drawn for
+
+
+def sharpen_attention(folder, cfg):
+    """Rewrites a random model's q and k projections so that attention is far from uniform.
+
+    Drawn at N(0, 0.02) like every other matrix, q and k give attention scores with a standard deviation of
+    0.02 to 0.15: softmax is then all but flat, and a model without any position encoding, with a window that
+    is one key too wide or with two swapped keys computes the same logits within bfloat16's tolerance.  Here q and
+    k weights are scaled so that scores have a standard deviation of SCORE_STD (the largest probability among
+    150 keys is then 10 to 40 times the uniform one), and their biases to N(0, 0.3).  tests/test_plain.py
+    checks that this is so, for every configuration.  The numbers stay values that bfloat16 holds."""
+    import torch
+    from air_b200.weights.safetensors_io import SafetensorsFile, write_safetensors
+    path = os.path.join(folder, "model.safetensors")
+    f = SafetensorsFile(path)
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    weight = (SCORE_STD ** 0.5) / (0.02 * cfg["hidden_size"] ** 0.5)
+    for n, t in tensors.items():
+        if n.endswith(("q_proj.weight", "k_proj.weight")):
+            tensors[n] = (t.float() * weight).to(t.dtype)
+        elif n.endswith(("q_proj.bias", "k_proj.bias")):
+            tensors[n] = (t.float() * 15.0).to(t.dtype)
+    del f
+    write_safetensors(path, tensors, metadata={"format": "pt"})
+
+
+def model_folder(name, dtype="bfloat16"):
     """A folder with config.json and model.safetensors for a tiny configuration, made once per
     session in a temporary place.  Weights are stored as bfloat16 values (also for the float32
-    tests, so that both precisions and the plain implementation read the same numbers)."""
+    tests, so that both precisions and the plain implementation read the same numbers); q and k are
+    scaled so that attention has something to look at (sharpen_attention)."""
     key = (name, dtype)
     if key not in _folders:
         from air_b200.engine.engine import write_random_model
@@ -54,6 +85,7 @@ def model_folder(name, dtype="bfloat16", scale=None):
         d = tempfile.TemporaryDirectory(prefix=f"air_b200_{name}_")
         _tmp.append(d)
         write_random_model(d.name, cfg, seed, dtype)
+        sharpen_attention(d.name, cfg)
         _folders[key] = d.name
     return _folders[key]
 
