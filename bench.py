@@ -1,25 +1,34 @@
 #!/usr/bin/env python3
-"""Benchmark of the decode step (and of a 2,048-token prefill) at the Qwen2.5-7B shape with
-random bfloat16 weights, on one GPU.
+"""Benchmark of the decode step, a 2,048-token prefill and a mixed step at the shapes of Qwen2.5-7B, 14B
+and 32B with random bfloat16 weights, on one GPU.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--shape 7b|14b|32b|config.json] [--batch 8]
+                    [--context N] [--layers L] [--repeats R] [--mixed D,P] [--output FILE]
 
-A "step" is one decode step of the whole batch.  It prints ONE JSON line:
-  value      decoded tokens per second, timed on the device with CUDA events over exactly K
-             steps after W warm-up steps; every request holds `context` tokens in the cache and
-             feeds its last sampled token back on the device (no host round trip)
-  e2e        the same through the Python entry point (InferenceService.run_cycle): every step
-             copies the step's token ids and tables from pinned host memory and reads the
-             sampled ids back
-  prefill    one step of 2,048 prompt tokens of one request; frac = flops / time / bf16 peak
-  roofline   bytes the decode step has to read (every weight once, the live requests' cache)
-             / its time, against the measured copy bandwidth
-  points     decode tokens per second at batch 1 and 64 (points_roofline_frac: their share of the
-             copy bandwidth, counted as for roofline)
-The cache of the decoding requests is filled with random keys and values instead of running
-64 prompts of 8,192 tokens (data: synthetic); timing does not depend on the values.  Between
-timed steps nothing is flushed: a step reads its weights (over 14 GB at 28 layers), far more
-than the 126 MB of L2.
+With no flags it runs the 7B shape (28 layers, batch 8, 8,192 tokens of context).  A "step" is one decode
+step of the whole batch.  It prints ONE JSON line:
+  value      decoded tokens per second: the median of R repeats, each timed on the device with CUDA events
+             over exactly K steps after W warm-up steps; every request holds `context` tokens in the cache at
+             the end of a repeat and feeds its last sampled token back on the device (no host round trip);
+             `repeat_ms_per_step` lists all repeats
+  e2e        the same through the Python entry point (InferenceService.run_cycle): every step copies the
+             step's token ids from pinned host memory and reads the sampled ids and the status word back
+  prefill    one step of 2,048 prompt tokens of one request, the median of R timed steps;
+             frac = flops / time / bf16 peak
+  roofline   bytes the decode step has to read (every weight once, the live requests' cache) / its time,
+             against the measured copy bandwidth
+  points     decode tokens per second at batch 1 and 64 (points_roofline_frac: their share of the copy
+             bandwidth, counted as for roofline)
+  mixed      with --mixed D,P: ONE Engine.step of D decoding requests at the context beside one P-token
+             portion of a prompt that has (context - P) / 2 tokens in the cache: device_ms (CUDA events around
+             the step), host_ms (the host's clock from the call of Engine.step to its return, i.e. packing and
+             launching, nothing waited for), and the shares of the copy bandwidth and of the bf16 peak
+The pool of cache pages is sized from the device memory that is free once the weights are resident.  The cache
+of the decoding requests is filled with random keys and values instead of running 64 prompts (data: synthetic);
+timing does not depend on the values.  Between timed steps nothing is flushed: a step reads its weights (over
+14 GB at 28 layers), far more than the 126 MB of L2.
+--impl reference runs EmersonDowell/AIR's own CUDA executor, built from its unmodified sources (baseline/),
+on the same shape, batch and context, and prints the same line with "impl": "reference".
 For --gpus N > 1 it prints one line that says so and exits with 2: this engine runs on one GPU.
 """
 import argparse
@@ -33,12 +42,18 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN25_7B = {
-    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 28, "hidden_size": 3584,
-    "num_attention_heads": 28, "num_key_value_heads": 4, "intermediate_size": 18944, "vocab_size": 152064,
-    "max_position_embeddings": 32768, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
-    "sliding_window": 131072, "use_sliding_window": False, "max_window_layers": 28, "hidden_act": "silu",
+_QWEN = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": 152064,
+         "max_position_embeddings": 32768, "rope_theta": 1000000.0, "tie_word_embeddings": False,
+         "sliding_window": 131072, "use_sliding_window": False, "hidden_act": "silu"}
+SHAPES = {
+    "7b": dict(_QWEN, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+               intermediate_size=18944, rms_norm_eps=1e-6, max_window_layers=28),
+    "14b": dict(_QWEN, num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                intermediate_size=13824, rms_norm_eps=1e-5, max_window_layers=48),
+    "32b": dict(_QWEN, num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                intermediate_size=27648, rms_norm_eps=1e-5, max_window_layers=64),
 }
+CONTEXTS = {"7b": 8192, "14b": 8192, "32b": 4096}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -118,12 +133,8 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def fill_cache(engine, requests, context, torch):
-    """Opens the requests with `context` tokens each and random keys and values in the pages."""
-    for r in requests:
-        engine.cache.open(r)
-        engine.cache.reserve([(r, context)])
-        engine.cache.commit(r, context)
+def randomize_cache(engine, torch):
+    """Random keys and values in every page of every run (once: pages keep them when they change hands)."""
     g = torch.Generator(device=engine.rt.device)
     g.manual_seed(1234)
     seen = set()
@@ -135,32 +146,57 @@ def fill_cache(engine, requests, context, torch):
                 kv.normal_(0.0, 0.5, generator=g)
 
 
-def decode_device(engine, requests, steps, warmup, torch, Entry, LAST):
-    """K decode steps timed with CUDA events; tokens are fed back on the device."""
-    first = [Entry(r, [17 + i], [0]) for i, r in enumerate(requests)]
-    engine.sample(engine.step(first))
-    again = [Entry(r, [LAST], [0]) for r in requests]
-    for _ in range(warmup):
-        engine.sample(engine.step(again))
-    torch.cuda.synchronize()
-    launches0 = engine.kernel_launches()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clocks = ClockSampler()
-    torch.cuda.synchronize()
-    start.record()
-    for _ in range(steps):
-        engine.sample(engine.step(again))
-    end.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(end)
-    return ms / steps, clocks.stop(), engine.kernel_launches() - launches0
+def open_requests(engine, requests, tokens):
+    """Opens the requests with `tokens` tokens each (whatever lies in their pages)."""
+    for r in requests:
+        engine.cache.open(r)
+        engine.cache.reserve([(r, tokens)])
+        engine.cache.commit(r, tokens)
 
 
-def decode_timeline(engine, requests, torch, Entry, LAST):
+def release(engine, requests):
+    for r in requests:
+        if r in engine.cache.sequences:
+            engine.finish(r)
+
+
+def decode_device(engine, requests, context, steps, warmup, repeats, torch, Entry, LAST):
+    """R repeats of K decode steps timed with CUDA events; tokens are fed back on the device.  Every repeat
+    starts from the same length, so that its last step runs at `context` tokens."""
+    times, clocks, launches = [], None, 0
+    start_len = context - (steps + warmup + 2)
+    for rep in range(repeats):
+        open_requests(engine, requests, start_len)
+        first = [Entry(r, [17 + i], [0]) for i, r in enumerate(requests)]
+        engine.sample(engine.step(first))
+        again = [Entry(r, [LAST], [0]) for r in requests]
+        for _ in range(warmup):
+            engine.sample(engine.step(again))
+        torch.cuda.synchronize()
+        launches0 = engine.kernel_launches()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler() if rep == 0 else None
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            engine.sample(engine.step(again))
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) / steps)
+        if sampler is not None:
+            clocks = sampler.stop()
+            launches = engine.kernel_launches() - launches0
+        release(engine, requests)
+    return times, clocks, launches
+
+
+def decode_timeline(engine, requests, context, torch, Entry, LAST):
     """Spans of the kernels of one decode step as they run inside the CUDA graph (from the moment a
     kernel has passed the wait on its predecessor to the moment the next one has), by kernel."""
     import collections
     from air_b200.csrc import ops
+    open_requests(engine, requests, context - 8)
+    engine.sample(engine.step([Entry(r, [17 + i], [0]) for i, r in enumerate(requests)]))
     again = [Entry(r, [LAST], [0]) for r in requests]
     buf = torch.zeros(1 + 2 * 16384, dtype=torch.int64, device=engine.rt.device)
     ops.set_trace(buf)
@@ -168,6 +204,7 @@ def decode_timeline(engine, requests, torch, Entry, LAST):
         engine.sample(engine.step(again))
     torch.cuda.synchronize()
     ops.set_trace(None)
+    release(engine, requests)
     b = buf.cpu().tolist()
     events = sorted((b[2 + 2 * i], b[1 + 2 * i]) for i in range(min(b[0], 16384)) if b[1 + 2 * i] < 100)
     start = [i for i, e in enumerate(events) if e[1] == 1][-1]           # the last step's embedding
@@ -193,8 +230,7 @@ def decode_timeline(engine, requests, torch, Entry, LAST):
 
 def prefill_timeline(engine, prompt, torch, Entry):
     """Spans between the starts of this package's kernels in one prefill step.  A library product has
-    no trace point: its time is part of the span of the kernel before it (add_rmsnorm before the QKV
-    and gate/up products, prefill_attention before the output product, and so on)."""
+    no trace point: its time is part of the span of the kernel before it."""
     import collections
     from air_b200.csrc import ops
     buf = torch.zeros(1 + 2 * 16384, dtype=torch.int64, device=engine.rt.device)
@@ -220,10 +256,11 @@ def prefill_timeline(engine, prompt, torch, Entry):
         print(f"  {key:42s} {n:4d} times {us:9.1f} us  {100 * us / total:5.1f} %  {us / n:7.1f} us each")
 
 
-def decode_e2e(engine, requests, steps, warmup, torch):
+def decode_e2e(engine, requests, context, steps, warmup, torch):
     """The same through InferenceService.run_cycle, host tokens in and out every step."""
     from air_b200.engine.service import InferenceService, SchedulerConfig
     from air_b200.sampling.sampler import GenerationConfig
+    open_requests(engine, requests, context - (steps + warmup + 2))
     service = InferenceService(engine, SchedulerConfig(max_active_requests=max(len(requests), 1),
                                                        token_budget_per_cycle=max(len(requests), 1)))
     for i, r in enumerate(requests):
@@ -236,30 +273,105 @@ def decode_e2e(engine, requests, steps, warmup, torch):
         service.run_cycle()
     torch.cuda.synchronize()
     sec = time.perf_counter() - t0
-    ctx = engine.last_context
-    # per step: 4 ints per token of the decode graph's batch from pinned memory; sampled ids back
-    size = next(iter(engine.graphs.values())).size if engine.graphs else len(requests)
+    release(engine, requests)
+    # per step: 4 ints per token of the decode graph's batch from pinned memory; sampled ids and the status word back
     sizes = [g.size for g in engine.graphs.values() if g.size >= len(requests)]
     h2d = 16 * (min(sizes) if sizes else len(requests))
-    return sec / steps, h2d, 4 * len(requests)
+    return sec / steps, h2d, 4 * (len(requests) + 1)
 
 
-def release(engine, requests):
-    for r in requests:
-        if r in engine.cache.sequences:
-            engine.finish(r)
+def mixed_step(engine, decoders, portion, context, repeats, torch, Entry):
+    """One Engine.step that holds `decoders` single next tokens of requests with `context` tokens and one portion of
+    `portion` prompt tokens of a request that has (context - portion) / 2 tokens in the cache."""
+    requests = [f"m{i}" for i in range(decoders)]
+    prior = max(0, (context - portion) // 2 // 64 * 64)
+    vocab = engine.model.spec.vocab_size
+    g = torch.Generator().manual_seed(11)
+    tokens = torch.randint(0, vocab, (portion,), generator=g).tolist()
+    device_ms, host_ms = [], []
+    for rep in range(repeats + 2):                 # the first two are warm-up
+        open_requests(engine, requests, context - 1)
+        open_requests(engine, ["portion"], prior)
+        entries = [Entry(r, [5 + i], [0]) for i, r in enumerate(requests)] + [Entry("portion", tokens, [])]
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        t0 = time.perf_counter()
+        logits = engine.step(entries)
+        engine.sample(logits)
+        t1 = time.perf_counter()
+        end.record()
+        torch.cuda.synchronize()
+        if rep >= 2:
+            device_ms.append(start.elapsed_time(end))
+            host_ms.append((t1 - t0) * 1e3)
+        release(engine, requests + ["portion"])
+    return statistics.median(device_ms), statistics.median(host_ms), prior
+
+
+def reference_arm(args, cfg, context):
+    """EmersonDowell/AIR's CUDA executor on the same shape: its own prefill and step_greedy_batch."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ref
+    try:
+        if args.batch > 8:
+            raise ref.Unavailable("AIR decodes at most 8 sequences together (kMaxNativeDecodeBatch)")
+        ref.build()
+        clocks = ClockSampler()
+        r = ref.bench(layers=args.layers or cfg["num_hidden_layers"], hidden=cfg["hidden_size"],
+                      ffn=cfg["intermediate_size"], heads=cfg["num_attention_heads"],
+                      kv_heads=cfg["num_key_value_heads"], vocab=cfg["vocab_size"],
+                      max_positions=cfg["max_position_embeddings"], theta=cfg["rope_theta"], eps=cfg["rms_norm_eps"],
+                      batch=args.batch, context=context, prefill=args.prefill_tokens, steps=args.steps,
+                      warmup=args.warmup, fill="fork")
+        clocks = clocks.stop()
+    except ref.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}))
+        return 0
+    ms = r["decode_ms_per_step"]
+    value = args.batch / (ms / 1e3)
+    line = {
+        "metric": f"decode tok/s at batch {args.batch} (Qwen2.5-{args.shape.upper()} shape, bf16 weights, random weights)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "reference",
+        "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": args.layers or cfg["num_hidden_layers"],
+                   "layers_of_model": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
+                   "seq_len": context, "context": context, "page_tokens": 16, "prefill_tokens": args.prefill_tokens,
+                   "parallelism": "single GPU",
+                   "same_config": "same shape, batch, context and bf16 weights; AIR keeps activations and cache in "
+                                  "float32 and runs its own scalar kernels; the context is one computed prompt, "
+                                  "forked (CudaKvCache::fork) for the other sequences",
+                   "timing": "host clock around AIR's blocking calls (step_greedy_batch, prefill_greedy)"},
+        # AIR's call takes host tokens and returns host tokens: it is end to end by construction
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+                "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": None, "clocks": clocks,
+        "prefill": {"value": r["prefill_tokens"] / (r["prefill_ms"] / 1e3) if r["prefill_ms"] > 0 else None,
+                    "tokens": r["prefill_tokens"], "ms": r["prefill_ms"]},
+        "reference_record": r,
+    }
+    print(json.dumps(line))
+    return 0
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--shape", default="7b", help="7b, 14b, 32b, or a config.json of the architecture")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--layers", type=int, default=QWEN25_7B["num_hidden_layers"])
+    ap.add_argument("--context", type=int, default=0, help="tokens per request (default: 8192; 4096 at 32b)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (for profiling)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--repeats", type=int, default=5, help="timed repeats of K decode steps and of the prefill step")
+    ap.add_argument("--mixed", default="", help="D,P: also time one step of D decoding requests beside a P-token portion")
+    ap.add_argument("--max-tokens", type=int, default=0, help="tokens in the cache pool (default: what device memory is left)")
+    ap.add_argument("--output", default="", help="also write the JSON line to this file")
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling the decode step alone")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling the decode step alone")
@@ -267,59 +379,72 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
     ap.add_argument("--timeline", action="store_true", help="also print the kernels' spans inside the decode graph and in the prefill step")
     args = ap.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "EmersonDowell/AIR is a CMake C++ project without setup.py or pyproject.toml (pip cannot "
-                          "install it), reads GGUF files only and ships no sm_100 code path"}))
-        return 0
     if args.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {args.gpus} is not supported",
                           "n_gpus": args.gpus}))
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.shape in SHAPES:
+        cfg, context = dict(SHAPES[args.shape]), args.context or CONTEXTS[args.shape]
+    else:
+        with open(args.shape) as f:
+            cfg = json.load(f)
+        context = args.context or 8192
+        args.shape = os.path.splitext(os.path.basename(args.shape))[0]
+    if args.impl == "reference":
+        return reference_arm(args, cfg, context)
+    layers_of_model = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+        if "max_window_layers" in cfg:
+            cfg["max_window_layers"] = args.layers
 
     import torch
     from air_b200.engine.batch import Entry, LAST_SAMPLED
     from air_b200.engine.engine import Engine, EngineConfig
     pk = peaks()
-    cfg = dict(QWEN25_7B, num_hidden_layers=args.layers)
+    mixed = tuple(int(x) for x in args.mixed.split(",")) if args.mixed else None
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
+    most = max(batches + ([mixed[0] + 1] if mixed else []))
     page = 64
-    per_request = -(-(args.context + 8) // page) * page
-    max_tokens = max(batches) * per_request + 4096
     engine = Engine.from_random(cfg, seed=0, config=EngineConfig(
-        dtype=torch.bfloat16, page_tokens=page, max_tokens=max_tokens, max_requests=max(batches) + 1,
+        dtype=torch.bfloat16, page_tokens=page, max_tokens=args.max_tokens or None, max_requests=most + 1,
         cuda_graphs=not args.no_graphs))
     mc = engine.model_config
+    pool_tokens = engine.cache.num_pages * page
+    per_request = -(-(context + 8) // page) * page
+    batches = [b for b in batches if b * per_request <= pool_tokens] or [1]
+    if args.batch not in batches:
+        print(json.dumps({"error": f"the cache pool holds {pool_tokens} tokens: too few for batch {args.batch} at "
+                                   f"{context} tokens"}))
+        return 1
     weight_bytes = engine.model.weight_bytes()
-    kv_bytes_per_token = 2 * mc.num_key_value_heads * mc.head_dim * 2 * len(engine.model.spec.order)
+    kv_bytes_per_token = engine.cache.bytes_per_page(engine.model.cache_needs(), page, torch.bfloat16) // page
+    randomize_cache(engine, torch)
 
     results = {}
     if args.skip_decode:
         batches, args.skip_e2e = [], True
-        results[args.batch] = {"ms": float("nan"), "clocks": None, "launches": 0}
+        results[args.batch] = {"times": [float("nan")], "ms": float("nan"), "clocks": None, "launches": 0}
     for b in batches:
         requests = [f"r{i}" for i in range(b)]
-        start_len = args.context - (args.steps + args.warmup + 2)
-        fill_cache(engine, requests, start_len, torch)
-        ms, clocks, launches = decode_device(engine, requests, args.steps, args.warmup, torch, Entry, LAST_SAMPLED)
-        results[b] = {"ms": ms, "clocks": clocks, "launches": launches}
+        times, clocks, launches = decode_device(engine, requests, context, args.steps, args.warmup,
+                                                args.repeats if b == args.batch else max(1, min(3, args.repeats)),
+                                                torch, Entry, LAST_SAMPLED)
+        results[b] = {"times": times, "ms": statistics.median(times), "clocks": clocks, "launches": launches}
         if args.timeline and b == args.batch:
-            decode_timeline(engine, requests, torch, Entry, LAST_SAMPLED)
-        release(engine, requests)
+            decode_timeline(engine, requests, context, torch, Entry, LAST_SAMPLED)
         if b == args.batch and not args.skip_e2e:
-            fill_cache(engine, requests, start_len, torch)
-            sec, h2d, d2h = decode_e2e(engine, requests, args.steps, args.warmup, torch)
+            sec, h2d, d2h = decode_e2e(engine, requests, context, args.steps, args.warmup, torch)
             results[b]["e2e"] = {"value": b / sec, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                                  "d2h_bytes_per_step": d2h}
-            release(engine, requests)
 
     # prefill of one request, one step
     T = args.prefill_tokens
     g = torch.Generator().manual_seed(7)
     prompt = torch.randint(0, mc.vocab_size, (T,), generator=g).tolist()
     times = []
-    for i in range(0 if args.skip_prefill else 3):
+    for i in range(0 if args.skip_prefill else 2 + max(1, args.repeats)):
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
@@ -328,34 +453,48 @@ def main():
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e))
         engine.finish("p")
-    pre_ms = min(times[1:]) if times else float("nan")
+    pre_ms = statistics.median(times[2:]) if times else float("nan")       # (the first two steps are warm-up)
     if args.timeline and not args.skip_prefill:
         prefill_timeline(engine, prompt, torch, Entry)
     L, E, I, V = len(engine.model.spec.order), mc.hidden_size, mc.intermediate_size, mc.vocab_size
     H, K, d = mc.num_attention_heads, mc.num_key_value_heads, mc.head_dim
     gemm_params = L * (E * (H + 2 * K) * d + H * d * E + 3 * E * I)
     flops = 2 * T * gemm_params + L * 4 * H * d * (T * (T + 1) // 2) + 2 * E * V
-    prefill = {"value": T / (pre_ms / 1e3), "tokens": T, "ms": pre_ms,
+    prefill = {"value": T / (pre_ms / 1e3), "tokens": T, "ms": pre_ms, "repeat_ms": times[2:],
                "frac": flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
     if "bf16_tflops_sustained" in pk:      # the step is tens of milliseconds long: also against the figure under the power cap
         prefill["frac_sustained"] = flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12)
 
+    mixed_record = None
+    if mixed:
+        D, P = mixed
+        dev_ms, host_ms, prior = mixed_step(engine, D, P, context, max(5, args.repeats), torch, Entry)
+        live = (D * context + prior + P) * kv_bytes_per_token
+        step_flops = 2 * (D + P) * gemm_params + L * 4 * H * d * (P * prior + P * (P + 1) // 2) + 2 * E * V * D
+        mixed_record = {"decode": D, "portion": P, "portion_prior_tokens": prior, "device_ms": dev_ms,
+                        "host_ms": host_ms, "tokens_per_s": (D + P) / (dev_ms / 1e3),
+                        "bytes_frac": (weight_bytes + live) / (dev_ms / 1e3) / 1e9 / pk["hbm_gbs"],
+                        "flops_frac": step_flops / (dev_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
     main_r = results[args.batch]
     ms = main_r["ms"]
+
     def bytes_a_second(batch):        # what a decode step at this batch has to read, over its time (GB/s)
-        live = batch * (args.context - (args.steps + args.warmup + 2) // 2) * kv_bytes_per_token
+        live = batch * (context - (args.steps + 2) // 2) * kv_bytes_per_token
         return (weight_bytes + live) / (results[batch]["ms"] / 1e3) / 1e9
     achieved = bytes_a_second(args.batch)
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen2.5-7B shape, bf16, random weights)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen2.5-{args.shape.upper()} shape, bf16, random weights)",
         "value": args.batch / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Qwen2.5-7B shape", "layers": L, "layers_of_model": QWEN25_7B["num_hidden_layers"],
+        "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": L, "layers_of_model": layers_of_model,
                    "hidden": E, "heads": H, "kv_heads": K, "head_dim": d, "intermediate": I, "vocab": V,
-                   "global_batch": args.batch, "seq_len": args.context, "context": args.context,
-                   "page_tokens": page, "prefill_tokens": T, "parallelism": "single GPU",
+                   "global_batch": args.batch, "seq_len": context, "context": context,
+                   "page_tokens": page, "pool_tokens": pool_tokens, "prefill_tokens": T, "repeats": args.repeats,
+                   "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights read every step)", "peaks": pk["source"]},
+        "repeat_ms_per_step": main_r["times"],
         "e2e": main_r.get("e2e"),
         "gpu_launches": main_r["launches"],
         "clocks": main_r["clocks"],
@@ -365,7 +504,13 @@ def main():
         "points": {f"decode_b{b}": b / (results[b]["ms"] / 1e3) for b in batches if b != args.batch},
         "points_roofline_frac": {f"decode_b{b}": bytes_a_second(b) / pk["hbm_gbs"] for b in batches if b != args.batch},
     }
-    print(json.dumps(line))
+    if mixed_record:
+        line["mixed"] = mixed_record
+    text = json.dumps(line)
+    print(text)
+    if args.output:
+        with open(args.output, "w") as f:
+            f.write(text + "\n")
     return 0
 
 
