@@ -38,6 +38,60 @@ __global__ void add_parts_kernel(float* __restrict__ h, const TD* __restrict__ d
     }
 }
 
+// ---------------------------------------------------------------- add + the next norm's rows, short of their scale
+// For few rows (a decode step).  h[t, i] += sum over parts of delta[part, t, i]; xg[t, i] = bfloat16(h[t, i] * w[i]);
+// ss[chunk, t] = the sum of h[t, i]^2 over the chunk's PN_CHUNK columns.  The RMSNorm's scale per row,
+// rsqrt(sum over chunks of ss / E + eps), is one number per row and commutes with the matrix product that takes
+// xg: that product applies it to its accumulators (gemm_tc_small.cu), working it out from ss while its weights
+// stream.  So no block here waits for a row's other blocks: a (row, chunk) is one block of PN_CHUNK / 4 threads
+// that issues all its loads at once, and the kernel is as long as one round trip to L2, where the norm kernel above
+// is a chain of a row's loads, a block-wide sum and a second pass (4 to 5 us at 8 rows of 3,584).
+constexpr int PN_CHUNK = 512;
+constexpr int PN_PARTS = 8;      // partial sums that a thread asks for at once
+template <typename TD, typename TW>
+__global__ void __launch_bounds__(PN_CHUNK / 4) add_prenorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                                                   int parts, size_t part_stride,
+                                                                   const TW* __restrict__ w,
+                                                                   __nv_bfloat16* __restrict__ xg,
+                                                                   float* __restrict__ ss, int T, int E) {
+    __shared__ float scratch[32];
+    pdl_enter(TR_NORM);
+    const int t = blockIdx.y, chunk = blockIdx.x;
+    const int i = chunk * PN_CHUNK + threadIdx.x * 4;
+    const bool in = i < E;
+    const size_t at = (size_t)t * E + i;
+    float x[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f}, d[PN_PARTS][4];
+    if (in) {
+        load4(h + at, x);
+        load4(w + i, wv);
+#pragma unroll
+        for (int p = 0; p < PN_PARTS; ++p)
+            if (p < parts) load4(delta + p * part_stride + at, d[p]);
+#pragma unroll
+        for (int p = 0; p < PN_PARTS; ++p)
+            if (p < parts) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] += d[p][j];
+            }
+        for (int p = PN_PARTS; p < parts; ++p) {
+            float e[4];
+            load4(delta + p * part_stride + at, e);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] += e[j];
+        }
+        if (parts > 0) store4(h + at, x);
+        float y[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[j] = x[j] * wv[j];
+        store4(xg + at, y);
+    }
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sq += x[j] * x[j];
+    const float total = block_sum(sq, scratch);
+    if (threadIdx.x == 0) ss[(size_t)chunk * T + t] = total;
+}
+
 // ---------------------------------------------------------------- what follows the output matrix
 // logits[r, v] = (logits[r, v] + bias[v]) * scale, then cap * tanh(. / cap) where cap > 0.  In place, float32.
 __global__ void logits_post_kernel(float* __restrict__ logits, const float* __restrict__ bias, float scale, float cap,
@@ -586,6 +640,22 @@ AIR_API int air_add_parts(float* h, const void* delta, int delta_dtype, int part
     const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     AIR_DISPATCH(delta_dtype, TD, return launch(add_parts_kernel<TD>, blocks, 256, 0, stream, h, (const TD*)delta,
                                                 parts, (size_t)n));
+    return 0;
+}
+
+// h [T, E] float32 (in and out); delta: `parts` tensors [T, E] one after the other (null: none); w [E]; xg [T, E]
+// bfloat16; ss [ceil(E / 512), T] float32.  E % 4 == 0, T <= 65535.
+AIR_API int air_add_prenorm(float* h, const void* delta, int delta_dtype, int parts, const void* w, int w_dtype,
+                            void* xg, float* ss, int T, int E, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E % 4 || T > 65535 || !h || !w || !xg || !ss) return AIR_ERR_BAD_ARGUMENT;
+    if (!delta) parts = 0;
+    const dim3 grid((E + PN_CHUNK - 1) / PN_CHUNK, T);
+    const size_t stride = (size_t)T * E;
+    AIR_DISPATCH(delta ? delta_dtype : AIR_F32, TD, AIR_DISPATCH(w_dtype, TW, {
+        return launch(add_prenorm_kernel<TD, TW>, grid, PN_CHUNK / 4, 0, stream, h, (const TD*)delta, parts, stride,
+                      (const TW*)w, (__nv_bfloat16*)xg, ss, T, E);
+    }));
     return 0;
 }
 

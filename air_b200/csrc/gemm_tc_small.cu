@@ -36,6 +36,12 @@ struct TsArgs {
     int T, N, K;
     int splits;
     int* status;
+    // Optional scale per token, applied to the accumulators before the epilogue: rsqrt(sum over ss_tiles of
+    // ss[tile][t] / K + eps), the RMSNorm scale of an input whose rows came as x * weight without it
+    // (add_prenorm_kernel in elementwise.cu writes such rows and the sums of squares).  ss == nullptr: none.
+    const float* ss;
+    int ss_tiles;
+    float eps;
 };
 
 __host__ __device__ constexpr int ts_stages(int nt, int halves) {
@@ -86,6 +92,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint64_t* acc_empty = bars + 2 * STAGES + 2;
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* row_scale = (float*)(tmem_slot + 2);       // [NT]
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -194,6 +201,25 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         pdl_wait();   // nothing is written before the predecessor has completed
         const int quarter = warp & 3;                     // the 32 lanes of tensor memory this warp may read
         const int r = quarter * 32 + lane;                // row of the tile's half
+        if (args.ss) {
+            // the tokens' norm scales, worked out while the weights stream: eight loads in flight at a time,
+            // the sums added in the order of the tiles
+            if (r < NT) {
+                float total = 0.f;
+                if (r < args.T) {
+                    for (int base = 0; base < args.ss_tiles; base += 8) {
+                        float part[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            part[i] = base + i < args.ss_tiles ? args.ss[(size_t)(base + i) * args.T + r] : 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) total += part[i];
+                    }
+                }
+                row_scale[r] = r < args.T ? rsqrtf(total / (float)args.K + args.eps) : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++it) {
             const int split = tile % args.splits;
@@ -206,6 +232,10 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 float gate[NT], up[NT];
                 ts_load_row<NT>(taddr, gate);
                 ts_load_row<NT>(taddr + NT, up);
+                if (args.ss) {
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) { gate[t] *= row_scale[t]; up[t] *= row_scale[t]; }
+                }
                 const int col = n0 / 2 + r;
                 if (col < args.N / 2) {
                     __nv_bfloat16* out = (__nv_bfloat16*)args.out + col;
@@ -219,6 +249,10 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 for (int hf = 0; hf < HALVES; ++hf) {
                     float v[NT];
                     ts_load_row<NT>(taddr + hf * NT, v);
+                    if (args.ss) {
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) v[t] *= row_scale[t];
+                    }
                     const int col = n0 + hf * 128 + r;
                     if (col < args.N) {
                         if constexpr (EPI == TS_BF16) {
@@ -275,7 +309,7 @@ static int ts_launch(const CUtensorMap& mw, const CUtensorMap& mx, const TsArgs&
     constexpr int STAGES = ts_stages(NT, HALVES);
     // always more than half of an SM's shared memory, so that two blocks never share an SM (and its
     // tensor memory)
-    const size_t smem = 1024 + (size_t)STAGES * (HALVES * 128 + NT) * TS_BK * 2 + 16 * STAGES + 256;
+    const size_t smem = 1024 + (size_t)STAGES * (HALVES * 128 + NT) * TS_BK * 2 + 16 * STAGES + 256 + 4 * NT;
     const size_t request = smem < 120 * 1024 ? 120 * 1024 : smem;
     auto kernel = gemm_tc_small_kernel<NT, EPI, HALVES>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)request);
@@ -313,7 +347,8 @@ static int ts_dispatch_tokens(int nt, int epi, const CUtensorMap& mw, const CUte
 // out as TsArgs.out.  tile_rows: 128 or 256 rows of W per tile (256 for epi 2).  max_blocks: the number of
 // SMs to use (0: all).
 AIR_API int air_gemm_tc_small(const void* x, const void* w, void* out, int T, int N, int K, int tile_rows, int epi,
-                              int splits, int max_blocks, int* status, cudaStream_t stream) {
+                              int splits, int max_blocks, int* status, const float* ss, int ss_tiles, float eps,
+                              cudaStream_t stream) {
     using namespace air;
     if (T <= 0 || N <= 0) return 0;
     if (T > 64 || K <= 0 || K % 8 || splits < 1 || (splits > 1 && epi != TS_PARTIAL) || ((uintptr_t)x & 15) ||
@@ -336,7 +371,8 @@ AIR_API int air_gemm_tc_small(const void* x, const void* w, void* out, int T, in
     if (max_blocks > 0 && max_blocks < sms) sms = max_blocks;
     const long long tiles = (long long)((N + tile_rows - 1) / tile_rows) * splits;
     const int blocks = (int)(tiles < sms ? tiles : sms);
-    TsArgs args{out, T, N, K, splits, status};
+    if (ss && ss_tiles < 1) return AIR_ERR_BAD_ARGUMENT;
+    TsArgs args{out, T, N, K, splits, status, ss, ss_tiles, eps};
     if (tile_rows == 256) return ts_dispatch_tokens<2>(nt, epi, mw, mx, args, blocks, stream);
     return ts_dispatch_tokens<1>(nt, epi, mw, mx, args, blocks, stream);
 }

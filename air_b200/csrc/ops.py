@@ -18,6 +18,7 @@ c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_vo
 _SIGNATURES = {
     "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "air_add_parts": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p],
+    "air_add_prenorm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_logits_post": [c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p],
     "air_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                         c_longlong, c_float, c_void_p],
@@ -35,7 +36,7 @@ _SIGNATURES = {
                               c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "air_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "air_gemm_tc_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                          c_void_p],
+                          c_void_p, c_int, c_float, c_void_p],
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                  c_void_p],
@@ -165,6 +166,31 @@ def add_parts(h, delta):
     _check(_get("air_add_parts")(h.data_ptr(), delta.data_ptr(), _DT[delta.dtype], parts, h.numel(), _stream()),
            "add_parts")
     return h
+
+
+PRENORM_CHUNK = 512
+
+
+def add_prenorm(h, delta, weight, xg, ss):
+    """h += delta in place (float32 h [T, E]; delta None, [T, E] or partial sums [parts, T, E]); xg =
+    bfloat16(h * weight); ss[chunk, t] = the sum of h[t]^2 over a chunk of 512 columns.  What add_rmsnorm does, short
+    of the scale per row (rsqrt(sum of a row's ss / E + eps)), which the product that takes xg applies (gemm_tc's
+    row_ss): no block of this kernel waits for another."""
+    T, E = h.shape
+    _req(h, "h", (torch.float32,))
+    parts = 0
+    if delta is not None:
+        parts = 1 if delta.dim() == 2 else delta.shape[0]
+        _req(delta, "delta", _FLOATS, (T, E) if delta.dim() == 2 else (parts, T, E))
+    _req(weight, "weight", _FLOATS, (E,))
+    _req(xg, "xg", (torch.bfloat16,), (T, E))
+    _req(ss, "ss", (torch.float32,), (-(-E // PRENORM_CHUNK), T))
+    if E % 4:
+        raise KernelError(f"add_prenorm: width {E} is not a multiple of 4")
+    _check(_get("air_add_prenorm")(h.data_ptr(), _ptr(delta), _DT[delta.dtype] if delta is not None else 0, parts,
+                                   weight.data_ptr(), _DT[weight.dtype], xg.data_ptr(), ss.data_ptr(), T, E,
+                                   _stream()), "add_prenorm")
+    return xg, ss
 
 
 def logits_post(logits, bias=None, scale=1.0, softcap=0.0):
@@ -450,8 +476,11 @@ def prefill_attention(q, cache, block_table, tiles, out, window, scale, status=N
 EPI_F32, EPI_BF16, EPI_SILU, EPI_PARTIAL = 0, 1, 2, 3
 
 
-def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_as_m=False):
+def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_as_m=False, row_ss=None, eps=0.0):
     """bfloat16 product a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (see gemm_tc.cu).
+    row_ss (float32 [tiles, M]) with eps: the accumulators are multiplied per row by
+    rsqrt(sum over tiles of row_ss / K + eps) before the epilogue (the kernel for few rows only; see
+    add_prenorm).
     epi EPI_F32: out float32 [M,N]; EPI_BF16: out bfloat16 [M,N]; EPI_SILU: w holds gate and up rows
     interleaved in blocks of bn/2, out bfloat16 [M,N/2] = silu(gate)*up; EPI_PARTIAL: out float32
     [splits,M,N] partial sums over parts of k.  With up to 64 rows and bn 128 or 256 the product runs with the
@@ -478,11 +507,17 @@ def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_
         raise KernelError(f"gemm_tc: epilogue {epi}")
     if epi != EPI_SILU and N % 4:
         raise KernelError(f"gemm_tc: N = {N} must be a multiple of 4")
+    if row_ss is not None:
+        _req(row_ss, "row_ss", (torch.float32,), (None, M))
     if small_rows(M, N, bn, epi) and not force_rows_as_m:
         # few tokens: the weights are the M side of the instruction (gemm_tc_small.cu)
         _check(_get("air_gemm_tc_small")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits,
-                                         max_blocks, _ptr(status), _stream()), "gemm_tc_small")
+                                         max_blocks, _ptr(status), _ptr(row_ss),
+                                         0 if row_ss is None else row_ss.shape[0], float(eps), _stream()),
+               "gemm_tc_small")
         return out
+    if row_ss is not None:
+        raise KernelError("gemm_tc: a scale per row is taken by the kernel for up to 64 rows only")
     _check(_get("air_gemm_tc")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits, max_blocks,
                                _ptr(status), _stream()), "gemm_tc")
     return out

@@ -9,7 +9,7 @@ import torch
 from ..config.model_config import ConfigError
 from ..csrc import ops
 from ..weights.loader import TensorSpec
-from .base import HostBatch, Mixer, PagedKV, Plan
+from .base import HostBatch, Mixer, PagedKV, Plan, PreNormed
 from .linear import Linear
 from .registry import register_mixer, POSITION_ENCODINGS
 
@@ -111,6 +111,18 @@ class Attention(Mixer):
         self.position.load(tensors, rt)
         self.scale = 1.0 / math.sqrt(self.head_dim)
 
+    def _fresh(self, ctx) -> bool:
+        """Whether a step of single next tokens takes the decode kernel that starts from the q/k/v product."""
+        table = self.position.table()
+        d = self.head_dim
+        return (self.rt.dtype == torch.bfloat16 and ctx.all_decode and d in ops.DECODE_HEAD_DIMS and table is not None
+                and table.shape[1] == d and ops.tile_pages(self.rt.page_tokens))
+
+    def accepts_prenormed(self, ctx, owns_cache=True):
+        # only on the road of a decode step: the q/k/v product for few rows applies the scale per row and hands
+        # partial sums to the attention kernel
+        return owns_cache and self.qkv.takes_prenormed(ctx.num_tokens) and self._fresh(ctx)
+
     def forward(self, x, ctx, cache, owns_cache=True):
         (pages,) = cache
         T = x.shape[0]
@@ -132,6 +144,8 @@ class Attention(Mixer):
             ops.decode_attention_fresh(qkv, self.bias, table, pages.kv, bt, ctx.token_seq, ctx.positions, out, H,
                                        self.window, self.scale, write_kv=owns_cache, status=ctx.status)
             return self._project(out.view(T, H * d), ctx)
+        if isinstance(x, PreNormed):
+            raise ops.KernelError("attention: rows without their norm's scale reached a road that does not apply it")
         q = torch.empty((T, H, d), dtype=rt.dtype, device=x.device)
         ops.qkv_rope_store(qkv, self.bias, table, ctx.positions, ctx.token_seq, bt, q, pages.kv,
                            H, K, d, write_kv=owns_cache, status=ctx.status)

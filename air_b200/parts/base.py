@@ -159,6 +159,31 @@ class Plan:
     values: Dict[str, object] = field(default_factory=dict)
 
 
+@dataclass
+class PreNormed:
+    """Rows that an RMSNorm would produce, short of the scale per row: x = bfloat16(h * weight), and the sums
+    of squares of h per row in parts (ss [parts, T], to be added in order): the row's scale is
+    rsqrt(sum / width + eps).  One number per row commutes with a matrix product, so a product that takes these
+    rows applies the scale to its accumulators.  A norm of the form x * scale(row) * weight writes its rows so
+    (Norm.forward_prenormed) where the part behind it says that it takes them in this step
+    (Part.accepts_prenormed): the kernel that writes them has no block that waits for a row's other blocks."""
+    x: torch.Tensor
+    ss: torch.Tensor
+    eps: float
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def device(self):
+        return self.x.device
+
+
 class Part:
     # True if forward() only launches work on the current stream from device data (no host
     # reads of the batch or of a result), so that a decode step can be captured in a CUDA graph.
@@ -182,6 +207,10 @@ class Part:
 
     def plan(self, batch: HostBatch) -> Optional[Plan]:
         return None
+
+    def accepts_prenormed(self, ctx, owns_cache: bool = True) -> bool:
+        """Whether forward() in this step takes its input as a PreNormed (see there)."""
+        return False
 
 
 class Norm(Part):

@@ -65,9 +65,17 @@ class PreNormBlock(Block):
     def cache_needs(self):
         return self.mixer.cache_needs()
 
+    @staticmethod
+    def _norm(norm, h, delta, part, ctx, owns_cache=True):
+        """The norm before `part`: where the part takes rows short of their scale in this step and the norm can
+        write them so, the wide kernel whose blocks do not wait for one another."""
+        if getattr(norm, "prenorm", False) and part.accepts_prenormed(ctx, owns_cache):
+            return norm.forward_prenormed(h, delta)
+        return norm.forward(h, delta)
+
     def forward(self, h, pending, ctx, cache, owns_cache=True):
         ctx.residual = h
-        x = self.mixer_norm.forward(h, pending)
+        x = self._norm(self.mixer_norm, h, pending, self.mixer, ctx, owns_cache)
         a = self.mixer.forward(x, ctx, cache, owns_cache)      # None: the mixer has added its output to h itself
-        x = self.ff_norm.forward(h, a)
+        x = self._norm(self.ff_norm, h, a, self.feed_forward, ctx)
         return h, self.feed_forward.forward(x, ctx)

@@ -17,6 +17,7 @@ from typing import Optional
 import torch
 
 from ..csrc import ops
+from .base import PreNormed
 
 SMALL_ROWS = 64      # up to this many rows the tcgen05 kernel is used
 SMS = 148
@@ -52,6 +53,7 @@ class Linear:
         self.gate_up_block = gate_up_block       # > 0: rows are blocks of gate rows and up rows in turn
         self.tc_ok = (weight.dtype == torch.bfloat16 and weight.is_cuda and self.in_features % 8 == 0
                       and self.out_features % 4 == 0)
+        self.tile = 0
         if self.tc_ok:
             self.tile, self.parts = choose_tile(self.out_features, self.in_features)
 
@@ -59,24 +61,44 @@ class Linear:
         """The product with a band of output rows (a view, nothing is copied)."""
         return Linear(self.weight[begin:end], self.status)
 
-    def small(self, x: torch.Tensor) -> bool:
+    def small(self, x) -> bool:
         return self.tc_ok and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_ROWS
 
-    def partial(self, x: torch.Tensor) -> torch.Tensor:
-        """float32 [parts, rows, out]: partial sums over parts of k, for a consumer that adds them."""
-        out = torch.empty((self.parts, x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
-        return ops.gemm_tc(x, self.weight, out, self.tile, ops.EPI_PARTIAL, splits=self.parts, status=self.status)
+    def takes_prenormed(self, rows: int, silu: bool = False) -> bool:
+        """Whether this product (partial sums, or with the activation) can apply an RMSNorm's scale per row to
+        its accumulators (PreNormed input): only the kernel for few rows does."""
+        if not self.tc_ok or rows > SMALL_ROWS:
+            return False
+        if silu:
+            return self.gate_up_block > 0 and ops.small_rows(rows, self.out_features, 2 * self.gate_up_block, ops.EPI_SILU)
+        return ops.small_rows(rows, self.out_features, self.tile, ops.EPI_PARTIAL)
 
-    def full(self, x: torch.Tensor) -> torch.Tensor:
+    @staticmethod
+    def _scaled(x):
+        """(rows, keyword arguments of the scale per row) of a plain or a PreNormed input."""
+        if isinstance(x, PreNormed):
+            return x.x, {"row_ss": x.ss, "eps": x.eps}
+        return x, {}
+
+    def partial(self, x) -> torch.Tensor:
+        """float32 [parts, rows, out]: partial sums over parts of k, for a consumer that adds them."""
+        x, scale = self._scaled(x)
+        out = torch.empty((self.parts, x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
+        return ops.gemm_tc(x, self.weight, out, self.tile, ops.EPI_PARTIAL, splits=self.parts, status=self.status,
+                           **scale)
+
+    def full(self, x) -> torch.Tensor:
         """float32 [rows, out] in one pass of the tcgen05 kernel."""
+        x, scale = self._scaled(x)
         bn, _ = choose_tile(self.out_features, self.in_features, may_split=False)
         out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
-        return ops.gemm_tc(x, self.weight, out, bn, ops.EPI_F32, status=self.status)
+        return ops.gemm_tc(x, self.weight, out, bn, ops.EPI_F32, status=self.status, **scale)
 
-    def silu_mul(self, x: torch.Tensor) -> torch.Tensor:
+    def silu_mul(self, x) -> torch.Tensor:
         """bfloat16 [rows, out / 2] = silu(gate) * up, in the epilogue of the tcgen05 kernel."""
+        x, scale = self._scaled(x)
         out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
-        return ops.gemm_tc(x, self.weight, out, 2 * self.gate_up_block, ops.EPI_SILU, status=self.status)
+        return ops.gemm_tc(x, self.weight, out, 2 * self.gate_up_block, ops.EPI_SILU, status=self.status, **scale)
 
     def adds_into(self, x: torch.Tensor, residual) -> bool:
         """Whether add_into() applies: 16-bit weights, a float32 stream of this product's shape."""

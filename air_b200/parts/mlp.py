@@ -55,6 +55,9 @@ class SwiGLU(FeedForward):
         self.gate_up = Linear(w.contiguous(), rt.status, gate_up_block=block if block != inter else 0)
         self.down = Linear(tensors[p + "down_proj.weight"], rt.status)
 
+    def accepts_prenormed(self, ctx, owns_cache=True):
+        return self.rt.dtype == torch.bfloat16 and self.gate_up.takes_prenormed(ctx.num_tokens, silu=True)
+
     def forward(self, x, ctx):
         if self.gate_up.gate_up_block and self.gate_up.tc_ok and x.dtype == torch.bfloat16 and x.shape[0] <= FUSED_ROWS:
             # few rows or many: the tcgen05 product with SiLU(gate) * up in its epilogue (the 2 I wide

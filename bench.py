@@ -217,15 +217,13 @@ def decode_timeline(engine, requests, context, torch, Entry, LAST):
     print(f"decode step inside the graph: {total:.1f} us from embedding to sampling, {len(step)} kernels")
     for name, (n, us) in sorted(spans.items(), key=lambda x: -x[1][1]):
         print(f"  {name:18s} {n:4d} launches {us:9.1f} us  {100 * us / total:5.1f} %  {us / n:7.1f} us each")
-    # one layer from the middle of the step, kernel by kernel
+    # one layer from the middle of the step, kernel by kernel (from one attention kernel to the next)
     names = [ops.TRACE_NAMES[k] for _, k in step]
-    for i in range(len(step) // 2, len(step) - 10):
-        if names[i:i + 2] == ["add_rmsnorm", "gemm_tc"] and names[i + 2] in ("qkv_rope_store", "decode_attention"):
-            j = next((j for j in range(i + 3, len(step) - 1) if names[j:j + 3] == names[i:i + 3]), None)
-            if j is not None:
-                print("  one layer (us): " + " | ".join(f"{names[q]} {(step[q + 1][0] - step[q][0]) / 1e3:.1f}"
-                                                       for q in range(i, j)))
-            break
+    marks = [i for i in range(len(step) // 2, len(step) - 1) if names[i] == "decode_attention"]
+    if len(marks) >= 2:
+        i, j = marks[0], marks[1]
+        print("  one layer (us): " + " | ".join(f"{names[q]} {(step[q + 1][0] - step[q][0]) / 1e3:.1f}"
+                                               for q in range(i, j)))
 
 
 def prefill_timeline(engine, prompt, torch, Entry):

@@ -121,3 +121,42 @@ def test_refusals():
     for bn in (64, 128):            # both kernels
         with pytest.raises(o.KernelError, match="size or dtype"):
             o.gemm_tc(a, w, torch.zeros(5, 8, 256, device="cuda"), bn, o.EPI_PARTIAL, splits=5)
+
+
+# ------------------------------------------------------------------ an RMSNorm's scale applied by the product
+@pytest.mark.parametrize("T", [3, 30, 64])
+@pytest.mark.parametrize("epi", ["partial", "f32", "silu"])
+def test_scale_per_row_from_sums_of_squares(T, epi):
+    """The products for few rows multiply their accumulators by rsqrt(sum of the parts of ss / K + eps) per row:
+    with x = h * g as input they give what the product of the RMSNorm of h gives."""
+    o = ops()
+    N, K, eps, tiles = 1024, 896, 1e-5, 7
+    g = torch.Generator().manual_seed(T)
+    h = torch.randn(T, K, generator=g) * 3
+    gw = 1 + 0.1 * torch.randn(K, generator=g)
+    x = (h * gw).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    ss = (h.view(T, tiles, 128) ** 2).sum(-1).T.contiguous()
+    scale = torch.rsqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)
+    want = (x.double() @ w.double().T) * scale
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    if epi == "partial":
+        out = torch.zeros(3, T, N, device="cuda")
+        o.gemm_tc(x.cuda(), w.cuda(), out, 128, o.EPI_PARTIAL, splits=3, status=status, row_ss=ss.cuda(), eps=eps)
+        got = out.sum(0).double().cpu()
+    elif epi == "f32":
+        out = torch.zeros(T, N, device="cuda")
+        o.gemm_tc(x.cuda(), w.cuda(), out, 256, o.EPI_F32, status=status, row_ss=ss.cuda(), eps=eps)
+        got = out.double().cpu()
+    else:
+        out = torch.zeros(T, N // 2, dtype=torch.bfloat16, device="cuda")
+        o.gemm_tc(x.cuda(), w.cuda(), out, 256, o.EPI_SILU, status=status, row_ss=ss.cuda(), eps=eps)
+        got = out.double().cpu()
+        blocks = want.view(T, N // 256, 2, 128)
+        gate, up = blocks[:, :, 0].reshape(T, -1), blocks[:, :, 1].reshape(T, -1)
+        want = gate / (1 + torch.exp(-gate)) * up
+    assert status.item() == 0
+    assert float((got - want).abs().max()) <= (1e-2 if epi == "silu" else 1e-4) * float(want.abs().max())
+    with pytest.raises(o.KernelError, match="up to 64 rows"):
+        o.gemm_tc(torch.zeros(100, K, dtype=torch.bfloat16, device="cuda"), w.cuda(), torch.zeros(100, N, device="cuda"),
+                  256, o.EPI_F32, row_ss=torch.zeros(tiles, 100, device="cuda"), eps=eps)

@@ -57,6 +57,39 @@ def test_add_parts_adds_every_form_of_delta_in_order(parts, dtype):
     assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,E,parts", [(1, 3584, 5), (8, 3584, 1), (37, 200, 0), (64, 5120, 9), (3, 1000, 2)])
+def test_add_prenorm_gives_the_norm_short_of_its_scale(T, E, parts, dtype):
+    """h += delta; xg = bfloat16(h * w); sums of squares per chunk of 512 columns: together with the scale per row
+    that follows from the sums they are what add_rmsnorm gives."""
+    g = torch.Generator().manual_seed(T + E)
+    h = torch.randn(T, E, generator=g)
+    w = (1 + 0.1 * torch.randn(E, generator=g)).to(DT[dtype])
+    delta = None if parts == 0 else torch.randn((parts, T, E) if parts > 1 else (T, E), generator=g)
+    chunks = -(-E // 512)
+    hd = dev(h.clone())
+    xg = torch.full((T, E), 9.0, dtype=torch.bfloat16, device="cuda")
+    ss = torch.full((chunks, T), -1.0, device="cuda")
+    ops().add_prenorm(hd, None if delta is None else dev(delta), dev(w), xg, ss)
+    want = h.clone()
+    if delta is not None:
+        for part in (delta if parts > 1 else delta[None]):
+            want = want + part
+    assert torch.equal(hd.cpu(), want)
+    assert float((xg.float().cpu() - want * w.float()).abs().max()) <= 1e-2 * float((want * w.float()).abs().max())
+    pad = torch.zeros(T, chunks * 512, dtype=torch.float64)
+    pad[:, :E] = want.double()
+    want_ss = (pad.view(T, chunks, 512) ** 2).sum(-1).T
+    assert float((ss.double().cpu() - want_ss).abs().max()) <= 1e-5 * float(want_ss.abs().max())
+    # the scale that a consumer derives is the norm's
+    eps = 1e-6
+    scale = torch.rsqrt(ss.double().cpu().sum(0) / E + eps)
+    normed = torch.empty(T, E, dtype=torch.float32, device="cuda")
+    ops().add_rmsnorm(dev(h.clone()), None if delta is None else dev(delta), dev(w), eps, normed)
+    assert float((xg.double().cpu() * scale[:, None] - normed.double().cpu()).abs().max()) <= \
+        1e-2 * float(normed.abs().max())
+
+
 def test_logits_post_adds_scales_and_caps():
     g = torch.Generator().manual_seed(3)
     logits = torch.randn(9, 1001, generator=g) * 20
