@@ -171,6 +171,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int split = tile % args.splits;
                 const int k_begin = split * k_per, k_end = min(k_tiles, k_begin + k_per);
                 const uint32_t acc = it % NACC, acc_phase = (it / NACC) & 1;
+                // (a last row tile that holds at most 128 rows needs no second product per k step: 544 rows
+                // are two tiles of 256 and one of 32, and that one costs half)
+                const int halves_here =
+                    (HALVES == 2 && ((tile / args.splits) % m_tiles) * TILE_M + TC_BM >= args.M) ? 1 : HALVES;
                 ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -188,8 +192,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (int k = 0; k < TC_BK / 16; ++k)
 #pragma unroll
                             for (int hf = 0; hf < HALVES; ++hf)
-                                umma_bf16(d + hf * BN, da + (uint64_t)(hf * (TC_BM * TC_BK * 2 >> 4)) + 2 * k, dw + 2 * k, idesc,
-                                          (kt > k_begin || k > 0) ? 1u : 0u);
+                                if (hf < halves_here)
+                                    umma_bf16(d + hf * BN, da + (uint64_t)(hf * (TC_BM * TC_BK * 2 >> 4)) + 2 * k, dw + 2 * k,
+                                              idesc, (kt > k_begin || k > 0) ? 1u : 0u);
                         umma_commit(&empty[stage]);
                     }
                     __syncwarp();

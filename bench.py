@@ -22,7 +22,10 @@ step of the whole batch.  It prints ONE JSON line:
   mixed      with --mixed D,P: ONE Engine.step of D decoding requests at the context beside one P-token
              portion of a prompt that has (context - P) / 2 tokens in the cache: device_ms (CUDA events around
              the step), host_ms (the host's clock from the call of Engine.step to its return, i.e. packing and
-             launching, nothing waited for), and the shares of the copy bandwidth and of the bf16 peak
+             launching, nothing waited for), the shares of the copy bandwidth and of the bf16 peak, and frac =
+             roofline_ms / device_ms, where roofline_ms adds what the step's phases need one after the other: the
+             decoding requests' cache at the copy bandwidth, the products at the bf16 peak (or their weights at the
+             copy bandwidth, if that is longer), the portion's attention at the bf16 peak
 The pool of cache pages is sized from the device memory that is free once the weights are resident.  The cache
 of the decoding requests is filled with random keys and values instead of running 64 prompts (data: synthetic);
 timing does not depend on the values.  Between timed steps nothing is flushed: a step reads its weights (over
@@ -469,10 +472,17 @@ def main():
         dev_ms, host_ms, prior = mixed_step(engine, D, P, context, max(5, args.repeats), torch, Entry)
         live = (D * context + prior + P) * kv_bytes_per_token
         step_flops = 2 * (D + P) * gemm_params + L * 4 * H * d * (P * prior + P * (P + 1) // 2) + 2 * E * V * D
+        # The step's kernels run one after the other: the decode attention is bound by the cache it reads, the
+        # products and the portion's attention by their flops (or by the weights, if those take longer to read).
+        cache_ms = D * context * kv_bytes_per_token / (pk["hbm_gbs"] * 1e9) * 1e3
+        product_ms = max(2 * (D + P) * gemm_params / (pk["bf16_tflops"] * 1e12), weight_bytes / (pk["hbm_gbs"] * 1e9)) * 1e3
+        attention_ms = L * 4 * H * d * (P * prior + P * (P + 1) // 2) / (pk["bf16_tflops"] * 1e12) * 1e3
         mixed_record = {"decode": D, "portion": P, "portion_prior_tokens": prior, "device_ms": dev_ms,
                         "host_ms": host_ms, "tokens_per_s": (D + P) / (dev_ms / 1e3),
                         "bytes_frac": (weight_bytes + live) / (dev_ms / 1e3) / 1e9 / pk["hbm_gbs"],
-                        "flops_frac": step_flops / (dev_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+                        "flops_frac": step_flops / (dev_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
+                        "roofline_ms": cache_ms + product_ms + attention_ms,
+                        "frac": (cache_ms + product_ms + attention_ms) / dev_ms}
 
     main_r = results[args.batch]
     ms = main_r["ms"]
