@@ -13,8 +13,8 @@ step of the whole batch.  It prints ONE JSON line:
              `repeat_ms_per_step` lists all repeats
   e2e        the same through the Python entry point (InferenceService.run_cycle): every step copies the
              step's token ids from pinned host memory and reads the sampled ids and the status word back
-  prefill    one step of 2,048 prompt tokens of one request, the median of R timed steps;
-             frac = flops / time / bf16 peak
+  prefill    one step of 2,048 prompt tokens of one request, the median of R timed steps, each after a pause
+             of 0.2 s (a prompt is a burst, not a sustained load); frac = flops / time / bf16 peak
   roofline   bytes the decode step has to read (every weight once, the live requests' cache) / its time,
              against the measured copy bandwidth
   points     decode tokens per second at batch 1 and 64 (points_roofline_frac: their share of the copy
@@ -370,6 +370,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (for profiling)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--repeats", type=int, default=5, help="timed repeats of K decode steps and of the prefill step")
+    ap.add_argument("--prefill-pause-ms", type=float, default=200.0, help="idle time before every prefill repeat")
     ap.add_argument("--mixed", default="", help="D,P: also time one step of D decoding requests beside a P-token portion")
     ap.add_argument("--max-tokens", type=int, default=0, help="tokens in the cache pool (default: what device memory is left)")
     ap.add_argument("--output", default="", help="also write the JSON line to this file")
@@ -447,6 +448,10 @@ def main():
     times = []
     for i in range(0 if args.skip_prefill else 2 + max(1, args.repeats)):
         torch.cuda.synchronize()
+        # A prompt's prefill is a burst of some tens of milliseconds, not a sustained load: every repeat starts
+        # after a pause, so that it is not timed at the clocks that the repeats before it left (seven steps back
+        # to back run into the power limit: 23.4, 23.4, 24.3, 25.0, 24.6 ms were measured so).
+        time.sleep(args.prefill_pause_ms / 1e3)
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         engine.step([Entry("p", prompt, [T - 1])])
@@ -462,6 +467,7 @@ def main():
     gemm_params = L * (E * (H + 2 * K) * d + H * d * E + 3 * E * I)
     flops = 2 * T * gemm_params + L * 4 * H * d * (T * (T + 1) // 2) + 2 * E * V
     prefill = {"value": T / (pre_ms / 1e3), "tokens": T, "ms": pre_ms, "repeat_ms": times[2:],
+               "pause_ms": args.prefill_pause_ms,
                "frac": flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
     if "bf16_tflops_sustained" in pk:      # the step is tens of milliseconds long: also against the figure under the power cap
         prefill["frac_sustained"] = flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12)

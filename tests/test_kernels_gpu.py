@@ -525,10 +525,13 @@ def test_decode_attention_from_the_product(H, K, d, P, window, splits):
     assert float((got2.float() - want.float())[keep].abs().max()) <= 2e-2 * max(1.0, float(want.float().abs().max()))
 
 
-@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 1000, 2047])
-def test_decode_attention_finds_one_far_key(far):
-    H, K, d, P, n = 14, 2, 128, 64, 2048
-    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [1], "bfloat16", seed=far, num_pages=40)
+@pytest.mark.parametrize("far,n", [(0, 2048), (15, 2048), (16, 2048), (63, 2048), (64, 2048), (1000, 2048), (2047, 2048),
+                                   (0, 32768), (20001, 32768), (32767, 32768)])
+def test_decode_attention_finds_one_far_key(far, n):
+    """One key among thousands (up to the 32,768 positions of a long context, 512 pages) stands out: the output is
+    its value, wherever it lies."""
+    H, K, d, P = 14, 2, 128, 64
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [1], "bfloat16", seed=far, num_pages=n // P + 8)
     q[:] = 0.5
     cache[bt[0, far // P], 0, :, far % P, :] = 8.0       # score 0.5*8*128/sqrt(128) = 45 against |score| < 6
     out = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
@@ -679,10 +682,11 @@ def test_window_edge_is_exact_in_the_tensor_core_kernels(kernel, n, w, P, holes)
         assert hit == visible, (key, visible)
 
 
-@pytest.mark.parametrize("far", [0, 15, 63, 64, 500, 1023])
-def test_prefill_attention_tc_finds_one_far_key(far):
-    H, K, d, P, n = 8, 2, 128, 64, 1040
-    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [16], "bfloat16", seed=far, num_pages=20)
+@pytest.mark.parametrize("far,n", [(0, 1040), (15, 1040), (63, 1040), (64, 1040), (500, 1040), (1023, 1040), (3, 16400),
+                                   (16383, 16400)])
+def test_prefill_attention_tc_finds_one_far_key(far, n):
+    H, K, d, P = 8, 2, 128, 64
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [16], "bfloat16", seed=far, num_pages=n // P + 4)
     q[:] = 0.5
     cache[bt[0, far // P], 0, :, far % P, :] = 8.0
     out = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
