@@ -394,3 +394,19 @@ def test_a_float32_checkpoint_in_the_bfloat16_engine_runs_the_tensor_core_produc
     assert np.abs(got - want).max() < util.BF16_MAX_TOL * scale
     kept = Engine.from_folder(folder, EngineConfig(dtype="bfloat16", page_tokens=64, max_tokens=256, keep_float32=True))
     assert not kept.model.blocks[0].mixer.qkv.tc_ok and len(kept.load_report.rounded) == 0
+
+
+def test_the_pool_is_sized_from_the_memory_that_is_left():
+    """Without a size the cache pool takes its share of the free device memory, at most what the allowed requests
+    could ever hold; generation runs on it."""
+    from air_b200 import GenerationConfig, InferenceService, SchedulerConfig
+    svc = InferenceService.create(util.model_folder("K"), dtype="bfloat16",
+                                  scheduler=SchedulerConfig(max_active_requests=3, kv_page_tokens=64))
+    cache = svc.engine.cache
+    assert cache.num_pages == 3 * (util.TINY_K["max_position_embeddings"] // 64)      # the cap: 3 requests of 512 tokens
+    r = svc.generate(util.tokens_for("K", 30, 990), GenerationConfig(max_new_tokens=8, stop_on_eos=False))
+    assert r.error is None and len(r.tokens) == 8
+    from air_b200.engine.engine import Engine, EngineConfig
+    engine = Engine.from_folder(util.model_folder("K"), EngineConfig(dtype="bfloat16", page_tokens=64, max_tokens=None,
+                                                                     max_requests=4, memory_fraction=1e-6))
+    assert 1 <= engine.cache.num_pages < 4 * 8, "a sliver of the free memory gives a small pool"

@@ -298,3 +298,32 @@ def test_three_hundred_requests_decode_in_one_step(dtype):
                               max_requests=300)
     util.check_against_plain(got, folder, streams, dtype)
     assert all(size <= 256 for size in engine.graphs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_context_of_eight_thousand_tokens(dtype):
+    """A request that grows to 8,200 tokens: its prompt in four portions of about 2,000 tokens (the tile kernels over
+    a long prefix, 128 pages behind one block table row), then 40 tokens one by one (the decode kernels, split over
+    32 tiles and more).  The logits at the end of every portion and at every decoded token against the plain
+    implementation on the whole sequence."""
+    from air_b200.engine.engine import write_random_model
+    from plain import qwen2_plain as plain
+    cfg = dict(util.TINY_K, max_position_embeddings=8448)
+    with tempfile.TemporaryDirectory() as folder:
+        write_random_model(folder, cfg, 31, "bfloat16")
+        util.sharpen_attention(folder, cfg)
+        toks = np.random.default_rng(8).integers(0, cfg["vocab_size"], size=8200).tolist()
+        cuts = [0, 2048, 4100, 6147, 8160]
+        steps = [util.step_line(i, [("r", toks[a:b], [0, b - a - 1])]) for i, (a, b) in enumerate(zip(cuts, cuts[1:]))]
+        steps += [util.step_line(4 + i, [("r", [toks[8160 + i]], [0])], end=["r"] if i == 39 else []) for i in range(40)]
+        got, _ = util.replay(folder, dtype, steps, max_tokens=8256, page_tokens=64, max_requests=2)
+        pcfg, tensors = plain.read_model(folder)
+        ref = plain.forward(pcfg, tensors, toks)
+        scale = max(1.0, float(np.abs(ref).max()))
+        assert len(got) == 8 + 40
+        for (rid, p), row in got.items():
+            diff = np.abs(row - ref[p])
+            if dtype == "float32":
+                assert diff.max() <= util.FP32_TOL * scale, p
+            else:
+                assert diff.max() <= util.BF16_MAX_TOL * scale and diff.mean() <= util.BF16_MEAN_TOL * scale, p
