@@ -90,7 +90,14 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
     // following products have asked for there
     uint64_t kv_policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(kv_policy));
-    pdl_wait();
+    // With fresh.qkv the predecessor is the q/k/v product, whose output only the consumer warps read: the
+    // producer warp does not wait for it.  What it reads was written long before: the step's positions, slots
+    // and block tables (copied or updated before the step's first kernel, which lets nothing start before that
+    // is done, see embedding_kernel) and keys and values of earlier steps; the token's own key and value never
+    // come from the copy (they are patched into the tile from shared memory).  So the first tiles of old keys
+    // are on their way while the product's last blocks still run.  Without fresh.qkv the token's key and value
+    // were written to the page by the predecessor itself, and everybody waits.
+    if (!(warp == DT_CONSUMERS && fresh.qkv)) pdl_wait();
     trace_point(TR_ATT_DECODE);
 
     const int t = blockIdx.z;

@@ -13,7 +13,12 @@ template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  const int* __restrict__ last_token, float* __restrict__ out, int E, int V,
                                  float multiplier, int* status) {
-    pdl_enter(TR_EMBED);
+    // The step's first kernel.  It lets its successors start only once ITS predecessors are done (the copy of the
+    // step's batch, the update of the block tables): kernels further down the step read those before their own
+    // wait on their predecessor (the decode attention's copy warp).
+    pdl_wait();
+    pdl_trigger();
+    trace_point(TR_EMBED);
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 && last_token) id = last_token[-id - 1];
