@@ -6,7 +6,7 @@ import torch
 from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import FeedForward
-from .linear import Linear
+from .linear import Linear, SMS
 from .registry import register_feed_forward
 
 
@@ -14,6 +14,27 @@ from .registry import register_feed_forward
 # product followed by the activation kernel (measured at 18944 x 3584: 776 against 803 us at 4,096 rows,
 # 1,261 against 1,203 us at 6,144).
 FUSED_ROWS = 4096
+
+
+def fused_gate_up_pays(rows: int, out_features: int) -> bool:
+    """Whether the package's product with the activation in its epilogue is at least as fast as the library's
+    product followed by the activation kernel, for this many rows and 2 x intermediate output features.
+
+    Measured on B200 at the 7B, 14B and 32B widths, CUDA events, cold L2.  Up to 128 rows the two are equal (the
+    kernel for up to 64 rows is another matter and is not asked about here).  From 129 to 511 rows the package's
+    kernel works on tiles of 128 rows, which wait for their operands a third of the time: the library is up to 36 %
+    faster (14B, 384 rows: 124 against 91 us).  From 512 rows on its tiles are 256 x 256 and it is as fast as the
+    library where those tiles fill whole rounds over the SMs and the rows fill the tiles (7B 768 rows: 149.5
+    against 148.3 us; 14B 1,024: 197.7 / 195.5; 2,048: 369.6 / 375.8), and up to 55 % slower where they do not
+    (14B 544 rows, 324 tiles of which the last third is nearly empty: 185.5 against 119.9 us)."""
+    if rows <= 128:
+        return True
+    if rows < 512 or rows > FUSED_ROWS:
+        return False
+    row_tiles, col_tiles = -(-rows // 256), -(-out_features // 256)
+    tiles = row_tiles * col_tiles
+    rounds = -(-tiles // SMS)
+    return (tiles / (rounds * SMS)) * (rows / (row_tiles * 256)) >= 0.9
 
 
 @register_feed_forward("swiglu")
@@ -59,7 +80,8 @@ class SwiGLU(FeedForward):
         return self.rt.dtype == torch.bfloat16 and self.gate_up.takes_prenormed(ctx.num_tokens, silu=True)
 
     def forward(self, x, ctx):
-        if self.gate_up.gate_up_block and self.gate_up.tc_ok and x.dtype == torch.bfloat16 and x.shape[0] <= FUSED_ROWS:
+        if (self.gate_up.gate_up_block and self.gate_up.tc_ok and x.dtype == torch.bfloat16
+                and (self.gate_up.small(x) or fused_gate_up_pays(x.shape[0], self.gate_up.out_features))):
             # few rows or many: the tcgen05 product with SiLU(gate) * up in its epilogue (the 2 I wide
             # intermediate is never written)
             act = self.gate_up.silu_mul(x)
