@@ -10,7 +10,7 @@ from ..config.model_config import ConfigError
 from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import HostBatch, Mixer, PagedKV, Plan, PreNormed
-from .linear import Linear
+from .linear import Linear, SMS
 from .registry import register_mixer, POSITION_ENCODINGS
 
 
@@ -55,27 +55,36 @@ class Attention(Mixer):
     PLAN = "attention.tiles"
 
     def plan_key(self):
-        return self.PLAN
+        return (self.PLAN, self.heads)
 
     def plan(self, batch: HostBatch) -> Plan:
-        """What the tile kernels want to know of a step, worked out once for all attention layers:
-        `decode_prefix`, the number of leading entries that bring a single next token (they take the
-        decode kernel), and for the tokens after them `tiles` [16n, 4] int32 = (slot, first row, its
-        position, rows <= 16): 16-token tiles in groups of 16 per request, filled up with rows = 0."""
+        """What the tile kernels want to know of a step, worked out once for all attention layers with this many
+        heads: `decode_prefix`, the number of leading entries that bring a single next token (they take the decode
+        kernel), and for the tokens after them `tiles` [16n, 4] int32 = (slot, first row, its position, rows <= 16):
+        16-token tiles in groups of 16, filled up with rows = 0.  A group is what one block of the tcgen05 kernel
+        takes per head: two row tiles of 128 consecutive tokens of a request on one stream of keys.  Where that
+        would give fewer blocks than half the SMs (a short portion on top of a long prefix: every block walks the
+        whole prefix), a group holds ONE row tile and eight empty entries instead: twice the blocks, each with
+        half the work, the keys read twice from L2."""
         prefix = 0
         while prefix < len(batch.counts) and batch.counts[prefix] == 1:
             prefix += 1
+        portions = range(prefix, len(batch.counts))
+        pairs = sum(-(-batch.counts[i] // 256) for i in portions)
+        rows_per_group = 128 if 0 < pairs * self.heads <= SMS // 2 else 256
         tiles = []
-        for i in range(prefix, len(batch.counts)):
+        for i in portions:
             n = batch.counts[i]
-            count = -(-n // 16)
-            tile = np.zeros((-(-count // 16) * 16, 4), dtype=np.int32)
-            tile[:, 0] = batch.slots[i]
-            first = np.arange(count, dtype=np.int32) * 16
-            tile[:count, 1] = batch.q_start[i] + first
-            tile[:count, 2] = batch.lengths[i] + first
-            tile[:count, 3] = np.minimum(16, n - first)
-            tiles.append(tile)
+            for g0 in range(0, n, rows_per_group):
+                rows = min(rows_per_group, n - g0)
+                count = -(-rows // 16)
+                tile = np.zeros((16, 4), dtype=np.int32)
+                tile[:, 0] = batch.slots[i]
+                first = g0 + np.arange(count, dtype=np.int32) * 16
+                tile[:count, 1] = batch.q_start[i] + first
+                tile[:count, 2] = batch.lengths[i] + first
+                tile[:count, 3] = np.minimum(16, n - first)
+                tiles.append(tile)
         tiles = np.concatenate(tiles) if tiles else np.zeros((0, 4), dtype=np.int32)
         return Plan(arrays={"tiles": tiles}, values={"decode_prefix": prefix})
 
@@ -152,12 +161,12 @@ class Attention(Mixer):
         out = torch.empty_like(q)
         if rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.all_decode:
             ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
-        elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and self.PLAN in ctx.plans
+        elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and self.plan_key() in ctx.plans
               and ops.tile_pages(pages.kv.shape[3])):
             # a mixed step: the single next tokens at the head of the batch take the decode kernel (a row
             # tile of 128 queries for one token would read its request's whole context for one row), the
             # prompt portions the tile kernels
-            plan = ctx.plans[self.PLAN]
+            plan = ctx.plans[self.plan_key()]
             n = plan.decode_prefix
             if n:
                 ops.decode_attention(q[:n], pages.kv, bt, ctx.token_seq[:n], ctx.positions[:n], out[:n], self.window,

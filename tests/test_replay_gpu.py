@@ -327,3 +327,18 @@ def test_a_context_of_eight_thousand_tokens(dtype):
                 assert diff.max() <= util.FP32_TOL * scale, p
             else:
                 assert diff.max() <= util.BF16_MAX_TOL * scale and diff.mean() <= util.BF16_MEAN_TOL * scale, p
+
+
+@pytest.mark.parametrize("name", ["K", "L"])
+def test_row_tiles_in_pairs_and_alone(name, monkeypatch):
+    """The tcgen05 attention kernel takes two row tiles of 128 tokens per block where that gives enough blocks, one
+    where it does not (parts/attention.py, plan).  Tiny models always fall on the second side; here the first is
+    forced, and both give the plain implementation's logits for prompts of more than 256 tokens in portions."""
+    import air_b200.parts.attention as attention
+    folder = util.model_folder(name)
+    streams = {f"{name}{i}": util.tokens_for(name, n, 70 + i) for i, n in enumerate((300, 129, 410, 257))}
+    steps = util.trace_portions(streams, sizes=(260, 2, 131, 17, 300))
+    for sms in (0, attention.SMS):           # 0: "fewer blocks than half the SMs" never holds, so always pairs
+        monkeypatch.setattr(attention, "SMS", sms)
+        got, _ = util.replay(folder, "bfloat16", steps, max_tokens=util.peak_tokens(steps), page_tokens=64)
+        util.check_against_plain(got, folder, streams, "bfloat16")
