@@ -425,17 +425,9 @@ static int decode_attention_tma(const FreshQkv& fresh, const void* q, const void
     if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || splits < 1 || T > 65535 ||
         (splits > 1 && (!part_o || !part_ml)) || ((uintptr_t)cache & 15))
         return AIR_ERR_BAD_ARGUMENT;
-    EncodeTiled enc = encode_tiled();
-    if (!enc) return AIR_ERR_BAD_ARGUMENT;
     CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)(pages * 2 * K * P)};
-    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)(P < DT_TILE ? P : DT_TILE)};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return 200000 + (int)r;
+    const int map_rc = tensor_map_2d(&map, cache, pages * 2 * K * P, D, P < DT_TILE ? P : DT_TILE);
+    if (map_rc) return map_rc;
     int rc;
     switch (D) {
         case 64:

@@ -272,17 +272,9 @@ AIR_API int air_prefill_attention(const void* q, const void* cache, long long pa
     if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || n_tiles % PF_GROUP || ((uintptr_t)cache & 15) ||
         K * ((H / K + 7) / 8) > 65535)
         return AIR_ERR_BAD_ARGUMENT;
-    EncodeTiled enc = encode_tiled();
-    if (!enc) return AIR_ERR_BAD_ARGUMENT;
     CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)(pages * 2 * K * P)};
-    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)(P < PF_TILE ? P : PF_TILE)};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return 200000 + (int)r;
+    const int map_rc = tensor_map_2d(&map, cache, pages * 2 * K * P, D, P < PF_TILE ? P : PF_TILE);
+    if (map_rc) return map_rc;
     switch (D) {
         case 64:
             return launch_prefill<64>(map, q, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window, scale,

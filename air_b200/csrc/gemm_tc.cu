@@ -297,16 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ------------------------------------------------------------------ host side
 // A tensor map of a row-major bf16 matrix [rows, cols] with boxes of box_rows x 64 and 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
-    EncodeTiled enc = encode_tiled();
-    if (!enc) return AIR_ERR_BAD_ARGUMENT;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 200000 + (int)r;
+    return tensor_map_2d(map, base, rows, cols, box_rows);
 }
 
 template <int BN, int EPI, int AR>

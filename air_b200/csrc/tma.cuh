@@ -71,6 +71,13 @@ typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, v
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+static EncodeTiled encode_tiled();
+
+// A tensor map of a row-major bfloat16 matrix [rows, cols] with boxes of box_rows x 64 elements and the 128-byte
+// swizzle: the only form this library uses.  (Keeping encoded maps from one step to the next was measured and
+// changed nothing in a step's host time: the encode is not where that time goes.)
+static int tensor_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows);
+
 static EncodeTiled encode_tiled() {
     static EncodeTiled fn = nullptr;
     if (!fn) {
@@ -81,6 +88,20 @@ static EncodeTiled encode_tiled() {
             fn = (EncodeTiled)p;
     }
     return fn;
+}
+
+static int tensor_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return AIR_ERR_BAD_ARGUMENT;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 200000 + (int)r;
+    return 0;
 }
 
 }  // namespace air
