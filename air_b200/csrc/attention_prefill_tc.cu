@@ -25,10 +25,19 @@
 // The grid is (heads, pairs) with the last pair of the list first: blocks are handed out in the order of
 // blockIdx.x, then blockIdx.y, so all heads of the heaviest pair of a prompt start first.
 //
+// With a list of segments the grid is that list instead: block i takes segments[i] = (pair, head, first key tile
+// of the pair's stream, key tiles, slot).  The host cuts long streams so when whole (pair, head) items would leave
+// SMs idle (a short portion on top of thousands of tokens: few items, each over the whole context).  A segment
+// with slot >= 0 writes, instead of the output rows, its unnormalised sums part_o[slot][256 rows][D], and per row
+// its reference maximum (in powers of two) and its sum of probabilities part_ml[slot][256] (0 where the row saw no
+// key); prefill_combine_kernel then merges an item's slots, in their order, into the output rows.
+//
 // tiles, q, out, cache, block_table, window as in attention_prefill.cu; the list pads every request
 // to whole pairs of groups.  Head size 64 or 128; pages of a divisor or a multiple of 64 tokens.
 // Every wait on an mbarrier is bounded (tma.cuh); on giving up the block flags *status = 7.  A list
 // whose second group does not go on where the first ends flags *status = 8 (that group is skipped).
+#include <limits.h>
+
 #include "common.cuh"
 #include "tma.cuh"
 #include "umma.cuh"
@@ -96,8 +105,9 @@ template <int D>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_cache,
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tiles,
-                            __nv_bfloat16* __restrict__ out, int H, int K, int P, int window, float scale_log2,
-                            int* __restrict__ status) {
+                            int n_pairs, const int* __restrict__ segments, int n_slots, float* __restrict__ part_o,
+                            float2* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int H, int K, int P,
+                            int window, float scale_log2, int* __restrict__ status) {
     constexpr int SUB = D / 64;                            // 64-column (128-byte) sub-tiles per row
     constexpr int Q_BYTES = SUB * AT_BM * 128;             // one row tile of Q
     constexpr int KV_SUB = AT_BN * 128;                    // one sub-tile of K or V
@@ -151,20 +161,28 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // on where the first, a full one, ends; the host's list pads every request to whole pairs.
     // (blocks are handed out in the order of blockIdx.x, then blockIdx.y: all heads of the heaviest pair
     // first, then all heads of the next, so that the light pairs fill in behind the heavy ones)
-    const int pair = gridDim.y - 1 - blockIdx.y;
+    int pair = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;
+    int seg_first = 0, seg_count = INT_MAX, slot_out = -1;
+    if (segments) {
+        const int* sg = segments + 5 * blockIdx.x;
+        pair = sg[0], h = sg[1], seg_first = sg[2], seg_count = sg[3], slot_out = sg[4];
+    }
+    const bool bad_segment = pair < 0 || pair >= n_pairs || h < 0 || h >= H || seg_first < 0 || seg_count < 0 ||
+                             slot_out >= n_slots;
+    if (bad_segment) pair = 0;
     const int* grp = tiles + 4 * AT_GROUP * AT_ROW_TILES * pair;
     int count_a = 0, count_b = 0;
-    for (int i = 0; i < AT_GROUP; ++i) {
+    for (int i = 0; i < AT_GROUP && !bad_segment; ++i) {
         count_a += grp[4 * i + 3];
         count_b += grp[4 * (AT_GROUP + i) + 3];
     }
+    if (bad_segment && threadIdx.x == 0 && status) atomicExch(status, 8);
     const int slot = grp[0], tok0 = grp[1], pos0 = grp[2];
     if (count_b > 0 && (count_a != AT_BM || grp[4 * AT_GROUP] != slot || grp[4 * AT_GROUP + 1] != tok0 + AT_BM ||
                         grp[4 * AT_GROUP + 2] != pos0 + AT_BM)) {
         if (threadIdx.x == 0 && status) atomicExch(status, 8);
         count_b = 0;
     }
-    const int h = blockIdx.x;
     const int kvh = (int)(((long long)h * K) / H);
     const int* bt = block_table + (size_t)slot * max_blocks;
     const bool has_b = count_b > 0;
@@ -172,16 +190,28 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int pos_last = has_b ? pos0 + AT_BM + count_b - 1 : pos_last_a;
     const int lo_a = window > 0 ? max(0, pos0 - window + 1) : 0;
     const int lo_b = window > 0 ? max(0, pos0 + AT_BM - window + 1) : 0;
-    const int tile0 = lo_a / AT_BN;                                         // the stream's first key tile
-    const int n_stream = count_a > 0 ? pos_last / AT_BN + 1 - tile0 : 0;    // key tiles the block fetches
+    // The pair's whole stream of key tiles, then the part of it that is this block's, and what of that part each
+    // row tile takes.
+    const int tile0_all = lo_a / AT_BN;                                           // the stream's first key tile
+    const int n_all = count_a > 0 ? pos_last / AT_BN + 1 - tile0_all : 0;
+    const int s0 = min(seg_first, n_all);
+    const int s1 = (int)min((long long)n_all, (long long)s0 + seg_count);
+    const int tile0 = tile0_all + s0;                                             // the block's first key tile
+    const int n_stream = s1 - s0;                                                 // key tiles the block fetches
+    auto clipped = [&](int count, int pos, int tok, int first, int n) {
+        const int a = max(first, s0), b = min(first + n, s1);
+        return b > a ? RowTile{count, pos, tok, a - s0, b - a} : RowTile{count, pos, tok, 0, 0};
+    };
     RowTile rt[AT_ROW_TILES];
-    rt[0] = {count_a, pos0, tok0, 0, count_a > 0 ? pos_last_a / AT_BN + 1 - tile0 : 0};
-    const int first_b = has_b ? lo_b / AT_BN - tile0 : 0;
-    rt[1] = {count_b, pos0 + AT_BM, tok0 + AT_BM, first_b, has_b ? n_stream - first_b : 0};
+    rt[0] = clipped(count_a, pos0, tok0, 0, count_a > 0 ? pos_last_a / AT_BN + 1 - tile0_all : 0);
+    const int first_b = has_b ? lo_b / AT_BN - tile0_all : 0;
+    rt[1] = clipped(count_b, pos0 + AT_BM, tok0 + AT_BM, first_b, has_b ? n_all - first_b : 0);
 
     if (warp == 0) {
         if (lane == 0 && n_stream > 0) {
             // ------------------------------------------------ producer
+            // (the lanes holding 32 entries of the block table at a time, instead of one load in front of every
+            // tile's copies, was measured: no change, the ring hides that load)
             mbar_expect_tx(q_full, (uint32_t)(Q_BYTES * (has_b ? 2 : 1)));
             for (int x = 0; x < (has_b ? 2 : 1); ++x)
 #pragma unroll
@@ -285,7 +315,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             pass(me.first + me.n, n_stream);
         }
-    } else if (warp >= 4 && (warp >= 8 ? rt[1].n : rt[0].n) > 0) {
+    } else if (warp >= 4 && (warp >= 8 ? rt[1].n : rt[0].n) == 0) {
+        // a row tile that has no key in this segment: its rows of the slot say so
+        const int x = (warp - 4) >> 2, r = (warp & 3) * 32 + lane;
+        if (slot_out >= 0 && r < (x ? rt[1].count : rt[0].count))
+            part_ml[(size_t)slot_out * (AT_ROW_TILES * AT_BM) + x * AT_BM + r] = make_float2(-INFINITY, 0.f);
+    } else if (warp >= 4) {
         // ---------------------------------------------------- softmax: one thread per query row
         const int x = (warp - 4) >> 2;
         const RowTile me = x ? rt[1] : rt[0];
@@ -399,23 +434,65 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && me.n >= 2) ok = mbar_wait(&my_pv_done[me.n & 1], ((me.n - 2) >> 1) & 1, abort_flag);
         if (ok) ok = mbar_wait(&my_pv_done[(me.n - 1) & 1], ((me.n - 1) >> 1) & 1, abort_flag);
         if (ok) {
+            // The rows leave through the row tile's own Q tile in shared memory, which no product reads any more:
+            // thread r puts its row there in 16-byte chunks (chunk c at place c ^ r of the row: no two lanes of a
+            // quarter-warp on one bank), then the warp copies its 32 rows out, a whole row per instruction.  (A
+            // thread that stores its own row to global memory writes 8 of every 32-byte sector per instruction:
+            // 6-7 us for the tile, measured, against about 1 us so.)
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = out + ((size_t)(me.tok0 + r) * H + h) * D;
+            constexpr int ROWB = D * 2, CHUNKS = ROWB / 16, LANEB = ROWB / 32;
+            uint8_t* stage = sq + x * Q_BYTES;
+            auto put = [&](int chunk, uint4 v) {
+                *reinterpret_cast<uint4*>(stage + r * ROWB + ((chunk ^ (r & (CHUNKS - 1))) << 4)) = v;
+            };
+            auto copy_out = [&](uint8_t* row0, size_t row_bytes) {
+                __syncwarp();
+                const int byte = lane * LANEB;
+                for (int i = 0; i < 32; ++i) {
+                    const int row = quarter * 32 + i;
+                    if (row >= me.count) break;
+                    const uint8_t* src = stage + row * ROWB + (((byte >> 4) ^ (row & (CHUNKS - 1))) << 4) + (byte & 15);
+                    uint8_t* dst = row0 + row * row_bytes + byte;
+                    if constexpr (LANEB == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(src);
+                    else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+                }
+                __syncwarp();
+            };
+            if (slot_out >= 0) {
+                // the segment's sums as they are (float32, half the columns at a time), and what the merge needs
+                // to weigh them
+                const size_t row = (size_t)slot_out * (AT_ROW_TILES * AT_BM) + x * AT_BM;
 #pragma unroll
-            for (int c = 0; c < D; c += 32) {
-                uint32_t ov[32];
-                tmem_ld32(my_o + c, ov);
-                if (r < me.count) {
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int c = 0; c < D / 2; c += 32) {
+                        uint32_t ov[32];
+                        tmem_ld32(my_o + half * (D / 2) + c, ov);
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4) put((c + e) >> 2, make_uint4(ov[e], ov[e + 1], ov[e + 2], ov[e + 3]));
+                    }
+                    copy_out(reinterpret_cast<uint8_t*>(part_o + row * D + half * (D / 2)), (size_t)D * 4);
+                }
+                if (r < me.count) part_ml[row + r] = make_float2(m, l);
+            } else {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(my_o + c, ov);
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
-                        float y[8];
+                        uint32_t pk[4];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) y[k] = __uint_as_float(ov[e + k]) * inv;
-                        store4(dst + c + e, *(const float(*)[4])&y[0]);
-                        store4(dst + c + e + 4, *(const float(*)[4])&y[4]);
+                        for (int k = 0; k < 4; ++k) {
+                            const __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(ov[e + 2 * k]) * inv,
+                                                                             __uint_as_float(ov[e + 2 * k + 1]) * inv);
+                            pk[k] = *reinterpret_cast<const uint32_t*>(&two);
+                        }
+                        put((c + e) >> 3, make_uint4(pk[0], pk[1], pk[2], pk[3]));
                     }
                 }
+                copy_out(reinterpret_cast<uint8_t*>(out + ((size_t)me.tok0 * H + h) * D), (size_t)H * D * 2);
             }
         }
     }
@@ -432,14 +509,85 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
+// Merges the slots of the cut items: out row = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s with M the largest
+// m_s, the slots in their order.  items [m, 4] = (pair, head, first slot, slots).  Grid (items, 32): a block takes 8
+// of the pair's 256 rows, a warp one row, a lane D / 32 columns.  Lane s first weighs slot s (all slots' maxima and
+// sums are loaded at once), then the warp adds the slots' rows, four loads in flight.
+template <int D>
+__global__ void __launch_bounds__(256)
+prefill_combine_kernel(const int* __restrict__ tiles, int n_pairs, const int* __restrict__ items, int n_slots,
+                       const float* __restrict__ part_o, const float2* __restrict__ part_ml,
+                       __nv_bfloat16* __restrict__ out, int H, int* __restrict__ status) {
+    constexpr int CP = D / 32;
+    constexpr int ROWS = AT_ROW_TILES * AT_BM;
+    pdl_enter(TR_ATT_COMBINE);
+    const int* item = items + 4 * blockIdx.x;
+    const int pair = item[0], h = item[1], slot0 = item[2], n = item[3];
+    if (pair < 0 || pair >= n_pairs || h < 0 || h >= H || slot0 < 0 || n < 1 || slot0 + n > n_slots) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 8);
+        return;
+    }
+    const int* grp = tiles + 4 * AT_GROUP * AT_ROW_TILES * pair;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.y * 8 + warp;
+    // rows of the pair that exist: the counts of the 16 entries (lanes 0-15 hold one each)
+    const int mine = lane < AT_GROUP * AT_ROW_TILES ? grp[4 * lane + 3] : 0;
+    const int before = __reduce_add_sync(0xffffffffu, lane < AT_GROUP ? mine : 0);
+    const int after = __reduce_add_sync(0xffffffffu, lane < AT_GROUP ? 0 : mine);
+    if (!(r < AT_BM ? r < before : r - AT_BM < after)) return;
+    const int tok0 = grp[1];
+    float top = -INFINITY, weight = 0.f, acc[CP];
+#pragma unroll
+    for (int c = 0; c < CP; ++c) acc[c] = 0.f;
+    // (more than 32 slots: in rounds; the running sums are rescaled when a round raises the maximum)
+    for (int s0 = 0; s0 < n; s0 += 32) {
+        const int s = s0 + lane;
+        const float2 ml = s < n ? part_ml[(size_t)(slot0 + s) * ROWS + r] : make_float2(-INFINITY, 0.f);
+        const bool live = ml.y > 0.f;
+        const float round_top = warp_max(live ? ml.x : -INFINITY);
+        if (round_top == -INFINITY) continue;
+        const float new_top = fmaxf(top, round_top);
+        const float keep = top == -INFINITY ? 0.f : exp2f(top - new_top);
+        top = new_top;
+        const float w = live ? exp2f(ml.x - top) : 0.f;
+        weight = weight * keep + warp_sum(w * ml.y);
+#pragma unroll
+        for (int c = 0; c < CP; ++c) acc[c] *= keep;
+        const int round = min(32, n - s0);
+        const float* src = part_o + ((size_t)(slot0 + s0) * ROWS + r) * D + lane * CP;
+#pragma unroll 4
+        for (int j = 0; j < round; ++j) {
+            const float wj = __shfl_sync(0xffffffffu, w, j);
+            if (wj > 0.f) {
+                float v[CP];
+                if constexpr (CP == 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(src + (size_t)j * ROWS * D);
+                    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+                } else {
+                    const float2 t = *reinterpret_cast<const float2*>(src + (size_t)j * ROWS * D);
+                    v[0] = t.x, v[1] = t.y;
+                }
+#pragma unroll
+                for (int c = 0; c < CP; ++c) acc[c] += wj * v[c];
+            }
+        }
+    }
+    const float inv = weight > 0.f ? 1.f / weight : 0.f;
+    __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * H + h) * D + lane * CP;
+#pragma unroll
+    for (int c = 0; c < CP; c += 2)
+        *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+}
+
 static int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
     return tensor_map_2d(map, base, rows, cols, box_rows);
 }
 
 template <int D>
 int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* block_table, int max_blocks,
-                      const int* tiles, int n_tiles, void* out, int H, int K, int P, int window, float scale, int* status,
-                      cudaStream_t stream) {
+                      const int* tiles, int n_tiles, const int* segments, int n_segments, const int* items, int n_items,
+                      int n_slots, float* part_o, float* part_ml, void* out, int H, int K, int P, int window, float scale,
+                      int* status, cudaStream_t stream) {
     // (more than half of an SM's shared memory, so that two blocks never share its tensor memory)
     size_t smem = 1024 + (size_t)AT_ROW_TILES * (D / 64) * AT_BM * 128 +
                   (size_t)AT_STAGES * 2 * (D / 64) * AT_BN * 128 + 256;
@@ -447,18 +595,32 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* b
     auto kernel = prefill_attention_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return launch(kernel, dim3(H, n_tiles / (AT_GROUP * AT_ROW_TILES)), AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles,
-                  (__nv_bfloat16*)out, H, K, P, window, scale * 1.4426950408889634f, status);
+    const int n_pairs = n_tiles / (AT_GROUP * AT_ROW_TILES);
+    const dim3 grid = segments ? dim3(n_segments) : dim3(H, n_pairs);
+    int rc = launch(kernel, grid, AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles, n_pairs, segments,
+                    n_slots, part_o, (float2*)part_ml, (__nv_bfloat16*)out, H, K, P, window,
+                    scale * 1.4426950408889634f, status);
+    if (rc || !segments || n_items <= 0) return rc;
+    return launch(prefill_combine_kernel<D>, dim3(n_items, AT_ROW_TILES * AT_BM / 8), 256, 0, stream, tiles, n_pairs,
+                  items, n_slots, (const float*)part_o, (const float2*)part_ml, (__nv_bfloat16*)out, H, status);
 }
 
 }  // namespace air
 
 // q [T, H, D] bf16.  tiles: n_tiles entries in groups of 16 per request.  Head size 64 or 128.
+// segments (or null: one block per pair and head) [n_segments, 5], items [n_items, 4], part_o float32
+// [n_slots, 256, D] and part_ml float32 [n_slots, 256, 2]: see the head of this file.
 AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, long long pages, const int* block_table,
-                                     int max_blocks, const int* tiles, int n_tiles, void* out, int H, int K, int D,
-                                     int P, int window, float scale, int* status, cudaStream_t stream) {
+                                     int max_blocks, const int* tiles, int n_tiles, const int* segments, int n_segments,
+                                     const int* items, int n_items, int n_slots, float* part_o, float* part_ml,
+                                     void* out, int H, int K, int D, int P, int window, float scale, int* status,
+                                     cudaStream_t stream) {
     using namespace air;
     if (n_tiles <= 0) return 0;
+    if (segments && (n_segments <= 0 || n_items < 0 || n_slots < 0 || (n_items > 0 && !items) ||
+                     (n_slots > 0 && (!part_o || !part_ml || ((uintptr_t)part_o & 15) || ((uintptr_t)part_ml & 7)))))
+        return AIR_ERR_BAD_ARGUMENT;
+    if (!segments) n_items = n_slots = 0;
     if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || n_tiles % (AT_GROUP * AT_ROW_TILES) || n_tiles / (AT_GROUP * AT_ROW_TILES) > 65535 ||
         ((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || (D != 64 && D != 128))
         return AIR_ERR_BAD_ARGUMENT;
@@ -468,10 +630,10 @@ AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, lo
     rc = make_map_2d(&mc, cache, pages * 2 * K * P, D, P < AT_BN ? P : AT_BN);
     if (rc) return rc;
     if (D == 64)
-        return launch_prefill_tc<64>(mq, mc, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window, scale, status,
-                                     stream);
-    return launch_prefill_tc<128>(mq, mc, block_table, max_blocks, tiles, n_tiles, out, H, K, P, window, scale, status,
-                                  stream);
+        return launch_prefill_tc<64>(mq, mc, block_table, max_blocks, tiles, n_tiles, segments, n_segments, items, n_items,
+                                     n_slots, part_o, part_ml, out, H, K, P, window, scale, status, stream);
+    return launch_prefill_tc<128>(mq, mc, block_table, max_blocks, tiles, n_tiles, segments, n_segments, items, n_items,
+                                  n_slots, part_o, part_ml, out, H, K, P, window, scale, status, stream);
 }
 
 AIR_API int air_trace_set_attention_prefill_tc(unsigned long long* buffer) { return air::set_trace_here(buffer); }

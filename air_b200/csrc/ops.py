@@ -44,6 +44,7 @@ _SIGNATURES = {
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "air_prefill_attention_tc": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                 c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                    c_void_p, c_void_p],
@@ -534,9 +535,13 @@ def small_rows(M: int, N: int, bn: int, epi: int) -> bool:
 TC_ATTENTION_HEAD_DIMS = (64, 128)
 
 
-def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, status=None):
+def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, status=None, segments=None, items=None,
+                         slots=0):
     """bfloat16 causal attention with both products on the tcgen05 tensor cores (see
-    attention_prefill_tc.cu); arguments as prefill_attention; head size 64 or 128."""
+    attention_prefill_tc.cu); arguments as prefill_attention; head size 64 or 128.
+    segments [n, 5] int32 (pair of the list, head, first key tile, key tiles, slot or -1): which block takes which
+    part of which pair's stream of keys, instead of one block per pair and head; items [m, 4] int32 (pair, head,
+    first slot, slots): the (pair, head)s whose segments write partial sums into `slots` slots, merged here."""
     T, H, d = q.shape
     K, P = cache.shape[2], cache.shape[3]
     _req(q, "q", (torch.bfloat16,))
@@ -550,8 +555,20 @@ def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, statu
         raise KernelError("prefill_attention_tc: the tile list must come in groups of 16 per request")
     if not tile_pages(P):
         raise KernelError(f"prefill_attention_tc: page size {P} is neither a divisor nor a multiple of 64")
+    part_o = part_ml = None
+    n_items = 0
+    if segments is not None:
+        _req(segments, "segments", _I32, (None, 5))
+        if segments.shape[0] == 0:
+            raise KernelError("prefill_attention_tc: an empty list of segments")
+        if slots:
+            _req(items, "items", _I32, (None, 4))
+            n_items = items.shape[0]
+            part_o = torch.empty((slots, 2 * TILE_GROUP * 16, d), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((slots, 2 * TILE_GROUP * 16, 2), dtype=torch.float32, device=q.device)
     _check(_get("air_prefill_attention_tc")(
         q.data_ptr(), T, cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
-        tiles.data_ptr(), tiles.shape[0], out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _ptr(status),
-        _stream()), "prefill_attention_tc")
+        tiles.data_ptr(), tiles.shape[0], _ptr(segments), 0 if segments is None else segments.shape[0],
+        _ptr(items) if n_items else None, n_items, int(slots) if segments is not None else 0, _ptr(part_o), _ptr(part_ml),
+        out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _ptr(status), _stream()), "prefill_attention_tc")
     return out

@@ -14,6 +14,76 @@ from .linear import Linear, SMS
 from .registry import register_mixer, POSITION_ENCODINGS
 
 
+# What a block of the tcgen05 attention kernel costs beside its key tiles (tensor memory, barriers, the chain of
+# loads to its first keys, the pipeline's fill and the write of its rows), in key tiles of one pair of row tiles:
+# with one block per SM a stream of n key tiles takes 11.5 + 1.03 n us, of which about 3.5 us are the launch.  The
+# shortest piece of a stream that is worth a block of its own is as long.
+SEGMENT_COST = 8.0
+MIN_SEGMENT = 8
+TO_THE_END = 1 << 30
+
+
+def plan_segments(key_tiles, heads: int, sms: int = 0):
+    """Which block takes which keys.  `key_tiles[p]` is the number of 64-key tiles in the stream of pair p of the
+    tile list (two row tiles of a request, the same for every head).  An item is a (pair, head); normally one
+    block takes one item, and the answer is None: the kernel's grid is (heads, pairs).  Where that would leave SMs
+    idle for long (few items, each over a long stream: a portion of a prompt on top of thousands of tokens), all
+    items' streams are laid end to end, heaviest first, and cut into `sms` equal ranges; a range's share of an item
+    is a segment, one block.  Segments of a cut item write partial sums (slots), which a second kernel merges.
+
+    Returns None or (segments [n, 5] int32: pair, head, first key tile, key tiles (TO_THE_END for an item's last),
+    slot or -1, longest first; items [m, 4] int32: pair, head, first slot, slots of the cut items; number of
+    slots).  Every item's segments cover its stream exactly once whatever the kernel takes the stream's length to
+    be: the first starts at 0 and the last runs to the end."""
+    sms = sms or SMS
+    pairs = len(key_tiles)
+    if pairs == 0 or heads <= 0:
+        return None
+    n = pairs * heads
+    total = heads * sum(key_tiles)
+    # whole items: the longest one, or all of them spread evenly; cut streams: equal ranges, 1.4 blocks per SM on
+    # the average, and the merge (measured: 81.5 against 64.5 us for 80 items of 68 key tiles, 372 against 90 us
+    # for 28 items of 514; 28.6 against 36.9 us for a whole prompt of 1,024 tokens, which is not cut)
+    # (some SM takes at least ceil(n / sms) items: the lightest ones at best)
+    most, lightest = -(-n // sms), 0.0
+    for tiles in sorted(key_tiles):
+        lightest += min(most, heads) * (tiles + SEGMENT_COST)
+        most -= min(most, heads)
+        if most == 0:
+            break
+    whole = max(max(key_tiles) + SEGMENT_COST, (total + n * SEGMENT_COST) / sms, lightest)
+    shortest = max(MIN_SEGMENT, 1)
+    ranges = min(sms, total // (shortest + 1))        # (cuts are then at least `shortest` apart after rounding)
+    if ranges <= 1 or whole <= 1.15 * (total / ranges + 2.4 * SEGMENT_COST):
+        return None
+    lengths = np.asarray(key_tiles, dtype=np.int64)
+    order = np.argsort(-lengths, kind="stable")
+    size = np.repeat(lengths[order], heads)           # item i is (order[i // heads], i % heads)
+    ends = np.cumsum(size)
+    at = np.rint(total / ranges * np.arange(1, ranges)).astype(np.int64)
+    item = np.searchsorted(ends, at, side="right")
+    offset = at - (ends[item] - size[item])
+    keep = (offset >= shortest) & (size[item] - offset >= shortest)
+    # a segment starts at 0 in every item and at every cut that is kept
+    seg_item = np.concatenate([np.arange(n, dtype=np.int64), item[keep]])
+    seg_first = np.concatenate([np.zeros(n, dtype=np.int64), offset[keep]])
+    by_place = np.argsort(seg_item * (int(lengths[order[0]]) + 1) + seg_first, kind="stable")
+    seg_item, seg_first = seg_item[by_place], seg_first[by_place]
+    goes_on = np.append(seg_item[1:] == seg_item[:-1], False)        # another segment of the item follows
+    until = np.where(goes_on, np.append(seg_first[1:], 0), size[seg_item])
+    work = until - seg_first
+    pieces = np.bincount(seg_item, minlength=n)
+    is_cut = pieces[seg_item] > 1
+    slot = np.where(is_cut, np.cumsum(is_cut) - 1, -1)
+    segments = np.stack([order[seg_item // heads], seg_item % heads, seg_first,
+                         np.where(goes_on, work, TO_THE_END), slot], axis=1)
+    segments = segments[np.argsort(-work, kind="stable")].astype(np.int32)
+    cut = np.nonzero(pieces > 1)[0]
+    first_slot = np.cumsum(pieces[cut]) - pieces[cut]
+    items = np.stack([order[cut // heads], cut % heads, first_slot, pieces[cut]], axis=1).astype(np.int32)
+    return segments, items, int(is_cut.sum())
+
+
 @register_mixer("attention")
 class Attention(Mixer):
     """q, k, v projections (with optional biases), position encoding of q and k, causal
@@ -55,28 +125,23 @@ class Attention(Mixer):
     PLAN = "attention.tiles"
 
     def plan_key(self):
-        return (self.PLAN, self.heads)
+        return (self.PLAN, self.heads, self.window)
 
     def plan(self, batch: HostBatch) -> Plan:
         """What the tile kernels want to know of a step, worked out once for all attention layers with this many
-        heads: `decode_prefix`, the number of leading entries that bring a single next token (they take the decode
-        kernel), and for the tokens after them `tiles` [16n, 4] int32 = (slot, first row, its position, rows <= 16):
-        16-token tiles in groups of 16, filled up with rows = 0.  A group is what one block of the tcgen05 kernel
-        takes per head: two row tiles of 128 consecutive tokens of a request on one stream of keys.  Where that
-        would give fewer blocks than half the SMs (a short portion on top of a long prefix: every block walks the
-        whole prefix), a group holds ONE row tile and eight empty entries instead: twice the blocks, each with
-        half the work, the keys read twice from L2."""
+        heads and this window: `decode_prefix`, the number of leading entries that bring a single next token (they
+        take the decode kernel), and for the tokens after them `tiles` [16n, 4] int32 = (slot, first row, its
+        position, rows <= 16): 16-token tiles in groups of 16, filled up with rows = 0.  A group is a pair of row
+        tiles, 256 consecutive tokens of a request on one stream of keys; `segments`, `items` and `slots` say which
+        block of the tcgen05 kernel takes which part of which pair's stream (plan_segments)."""
         prefix = 0
         while prefix < len(batch.counts) and batch.counts[prefix] == 1:
             prefix += 1
-        portions = range(prefix, len(batch.counts))
-        pairs = sum(-(-batch.counts[i] // 256) for i in portions)
-        rows_per_group = 128 if 0 < pairs * self.heads <= SMS // 2 else 256
-        tiles = []
-        for i in portions:
+        tiles, key_tiles = [], []
+        for i in range(prefix, len(batch.counts)):
             n = batch.counts[i]
-            for g0 in range(0, n, rows_per_group):
-                rows = min(rows_per_group, n - g0)
+            for g0 in range(0, n, 256):
+                rows = min(256, n - g0)
                 count = -(-rows // 16)
                 tile = np.zeros((16, 4), dtype=np.int32)
                 tile[:, 0] = batch.slots[i]
@@ -85,8 +150,17 @@ class Attention(Mixer):
                 tile[:count, 2] = batch.lengths[i] + first
                 tile[:count, 3] = np.minimum(16, n - first)
                 tiles.append(tile)
+                # the pair's keys: from the first one that its first row sees to its last row's own
+                pos0 = batch.lengths[i] + g0
+                lowest = max(0, pos0 - self.window + 1) if self.window else 0
+                key_tiles.append((pos0 + rows - 1) // 64 + 1 - lowest // 64)
         tiles = np.concatenate(tiles) if tiles else np.zeros((0, 4), dtype=np.int32)
-        return Plan(arrays={"tiles": tiles}, values={"decode_prefix": prefix})
+        arrays, values = {"tiles": tiles}, {"decode_prefix": prefix, "segments": None, "items": None, "slots": 0}
+        cut = plan_segments(key_tiles, self.heads)
+        if cut is not None:
+            arrays["segments"], arrays["items"], values["slots"] = cut
+            del values["segments"], values["items"]
+        return Plan(arrays=arrays, values=values)
 
     def tensor_specs(self):
         d, p = self.head_dim, self.prefix
@@ -174,7 +248,8 @@ class Attention(Mixer):
             if plan.tiles.shape[0] == 0:
                 pass
             elif d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
-                ops.prefill_attention_tc(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status)
+                ops.prefill_attention_tc(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status,
+                                         segments=plan.segments, items=plan.items, slots=plan.slots)
             else:
                 ops.prefill_attention(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status)
         else:

@@ -310,6 +310,75 @@ def mixed_step(engine, decoders, portion, context, repeats, torch, Entry):
     return statistics.median(device_ms), statistics.median(host_ms), prior
 
 
+def kernel_prefill_attention(cfg):
+    """The tcgen05 attention kernel alone at the shape's heads: launches replayed as a CUDA graph of ten (a launch
+    from the host costs more than the kernel takes), timed with CUDA events, median of five replays.  First one
+    block per SM with streams of 4 to 128 key tiles (what a block costs beside its key tiles), then whole prompts
+    and portions on top of long prefixes, with whole streams per block and with the planner's cut (if it cuts)."""
+    import math
+    import statistics
+    import numpy as np
+    import torch
+    from air_b200.csrc import ops
+    from air_b200.parts.attention import plan_segments
+    d = cfg.get("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"])
+    heads, kv_heads, P = cfg["num_attention_heads"], cfg["num_key_value_heads"], 64
+
+    def case(H, K, prior, portion):
+        pages = -(-(prior + portion) // P)
+        cache = (torch.randn(pages + 1, 2, K, P, d, device="cuda") * 0.5).to(torch.bfloat16)
+        table = torch.arange(pages, dtype=torch.int32, device="cuda")[None, :].contiguous()
+        q = (torch.randn(portion, H, d, device="cuda") * 0.5).to(torch.bfloat16)
+        tiles = [[0, i, prior + i, min(16, portion - i)] for i in range(0, portion, 16)]
+        tiles += [[0, 0, 0, 0]] * (-len(tiles) % 16)
+        streams = [(prior + min(portion, g + 256) - 1) // 64 + 1 for g in range(0, portion, 256)]
+        return q, cache, table, torch.tensor(tiles, dtype=torch.int32, device="cuda"), streams
+
+    def timed(q, cache, table, tiles, cut=None):
+        out = torch.empty_like(q)
+        more = {}
+        if cut is not None:
+            more = dict(segments=torch.from_numpy(cut[0]).cuda(), items=torch.from_numpy(cut[1]).cuda(), slots=cut[2])
+        call = lambda: ops.prefill_attention_tc(q, cache, table, tiles, out, 0, 1 / math.sqrt(d), **more)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(10):
+                call()
+        graph.replay()
+        torch.cuda.synchronize()
+        us = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 100.0)
+        return statistics.median(us)
+
+    print(f"prefill_attention_tc_kernel<{d}>: one block per SM (148 heads, 256 query rows), us per launch")
+    for prior in (0, 256, 768, 1792, 3840, 7936):
+        q, cache, table, tiles, streams = case(148, 4, prior, 256)
+        print(f"  stream of {streams[0]:4d} key tiles: {timed(q, cache, table, tiles):7.1f}")
+    print(f"{heads} query heads, {kv_heads} kv heads: whole streams per block | the planner's cut")
+    for prior, portion in ((0, 1024), (0, 2048), (0, 8192), (2048, 2048), (3840, 512), (32768, 128), (32768, 512)):
+        q, cache, table, tiles, streams = case(heads, kv_heads, prior, portion)
+        flops = 4.0 * d * heads * sum(min(prior + i + 1, prior + portion) for i in range(portion))
+        whole = timed(q, cache, table, tiles)
+        cut = plan_segments(streams, heads)
+        line = f"  {portion:5d} tokens behind {prior:5d}: {whole:8.1f} us ({flops / whole / 1e6:6.0f} TFLOP/s)"
+        if cut is not None:
+            t = timed(q, cache, table, tiles, cut)
+            line += f" | {t:8.1f} us ({flops / t / 1e6:6.0f} TFLOP/s; {len(cut[0])} blocks, {cut[2]} partial results merged)"
+        else:
+            line += " | not cut"
+        print(line)
+    return 0
+
+
 def reference_arm(args, cfg, context):
     """EmersonDowell/AIR's CUDA executor on the same shape: its own prefill and step_greedy_batch."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -379,6 +448,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling the decode step alone")
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
+    ap.add_argument("--kernel", default="", help="prefill_attention: time that kernel alone at the shape's heads and exit")
     ap.add_argument("--timeline", action="store_true", help="also print the kernels' spans inside the decode graph and in the prefill step")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -395,6 +465,11 @@ def main():
         args.shape = os.path.splitext(os.path.basename(args.shape))[0]
     if args.impl == "reference":
         return reference_arm(args, cfg, context)
+    if args.kernel:
+        if args.kernel != "prefill_attention":
+            print(json.dumps({"error": f"--kernel {args.kernel}: only prefill_attention is timed alone"}))
+            return 2
+        return kernel_prefill_attention(cfg)
     layers_of_model = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers

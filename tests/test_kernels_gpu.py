@@ -613,6 +613,89 @@ def test_prefill_attention_tc(H, K, d, P, window):
     assert np.abs(out.float().cpu().numpy() - want).max() < 1e-2 * max(1.0, np.abs(want).max())
 
 
+def streams_of(tiles, window):
+    """Key tiles in the stream of every pair of a tile list (as the kernel counts them)."""
+    out = []
+    for p in range(len(tiles) // 16):
+        grp = tiles[16 * p: 16 * p + 16]
+        pos0, rows = int(grp[0, 2]), int(grp[:, 3].sum())
+        lowest = max(0, pos0 - window + 1) if window else 0
+        out.append((pos0 + rows - 1) // 64 + 1 - lowest // 64)
+    return out
+
+
+def pieces_of(streams, heads, piece, whole_every=3):
+    """A hand-made list of segments: every (pair, head) cut into pieces of `piece` key tiles, except every third
+    item, which stays whole (slot -1).  The last piece says `to the end`; the order is scrambled."""
+    segments, items, slot = [], [], 0
+    for p, n in enumerate(streams):
+        for h in range(heads):
+            if (p * heads + h) % whole_every == 0 or n <= piece:
+                segments.append([p, h, 0, 1 << 30, -1])
+                continue
+            starts = list(range(0, n, piece))
+            items.append([p, h, slot, len(starts)])
+            for j, first in enumerate(starts):
+                segments.append([p, h, first, piece if j + 1 < len(starts) else 1 << 30, slot])
+                slot += 1
+    order = np.random.default_rng(len(segments)).permutation(len(segments))
+    return (np.array(segments, dtype=np.int32)[order], np.array(items, dtype=np.int32).reshape(-1, 4), slot)
+
+
+@pytest.mark.parametrize("H,K,d,P", [(28, 4, 128, 64), (6, 2, 64, 16), (3, 3, 128, 16), (20, 2, 64, 32), (8, 4, 128, 128)])
+@pytest.mark.parametrize("window", [0, 21, 100])
+@pytest.mark.parametrize("piece", [1, 3])
+def test_prefill_attention_tc_in_segments(H, K, d, P, window, piece):
+    """The same portions with the streams of keys cut into pieces of one and of three key tiles, each piece a block
+    of its own that writes partial sums, merged by the second kernel; some items stay whole.  Pieces fall before a
+    window's start and behind the causal edge of the pair's first row tile (a row tile with no key in its piece)."""
+    lens, q_lens = [150, 1, 64, 33, 333, 200, 700], [150, 1, 1, 33, 18, 77, 260]
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, lens, q_lens, "bfloat16", seed=H + window,
+                                                         num_pages=120)
+    tiles = tiles_for(lens, q_lens)
+    segments, items, slots = pieces_of(streams_of(tiles, window), H, piece)
+    assert slots > 0
+    out = torch.full(q.shape, 7.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().prefill_attention_tc(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(tiles), out, window,
+                               1.0 / math.sqrt(d), status=status, segments=dev(segments), items=dev(items), slots=slots)
+    assert status.item() == 0
+    want = attention_reference(q, ks, vs, positions, seq_of, window)
+    assert np.abs(out.float().cpu().numpy() - want).max() < 1e-2 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("lens,q_lens,H", [([6000], [80], 6), ([3000, 5000], [512, 300], 10), ([40000], [130], 28)])
+def test_prefill_attention_tc_with_the_planner_s_segments(lens, q_lens, H):
+    """Short portions on top of long prefixes: the planner cuts the streams (asserted), the result is the plain one."""
+    from air_b200.parts.attention import plan_segments
+    K, d, P = 2, 128, 64
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, lens, q_lens, "bfloat16", seed=H,
+                                                         num_pages=sum(-(-n // P) for n in lens) + 2)
+    tiles = tiles_for(lens, q_lens)
+    planned = plan_segments(streams_of(tiles, 0), H)
+    assert planned is not None, "the planner is expected to cut these streams"
+    segments, items, slots = planned
+    assert slots > 0 and len(segments) > len(tiles) // 16 * H
+    out = torch.full(q.shape, 7.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().prefill_attention_tc(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(tiles), out, 0,
+                               1.0 / math.sqrt(d), status=status, segments=dev(segments), items=dev(items), slots=slots)
+    assert status.item() == 0
+    want = attention_reference(q, ks, vs, positions, seq_of, 0)
+    assert np.abs(out.float().cpu().numpy() - want).max() < 1e-2 * max(1.0, np.abs(want).max())
+
+
+def test_prefill_attention_tc_reports_a_segment_that_names_no_pair():
+    H, K, d, P = 4, 2, 64, 64
+    q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [100], [100], "bfloat16", seed=3, num_pages=4)
+    segments = np.array([[0, h, 0, 1 << 30, -1] for h in range(H)] + [[1, 0, 0, 4, -1]], dtype=np.int32)
+    out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().prefill_attention_tc(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(tiles_for([100], [100])),
+                               out, 0, 1.0 / math.sqrt(d), status=status, segments=dev(segments))
+    assert status.item() == 8
+
+
 def test_prefill_attention_tc_reports_a_list_that_is_not_in_pairs():
     """Two requests with one group of 8 tiles each, one after the other: the second group does not go on
     where the first ends, so the kernel flags status 8 instead of mixing the requests."""
@@ -684,14 +767,22 @@ def test_window_edge_is_exact_in_the_tensor_core_kernels(kernel, n, w, P, holes)
 
 @pytest.mark.parametrize("far,n", [(0, 1040), (15, 1040), (63, 1040), (64, 1040), (500, 1040), (1023, 1040), (3, 16400),
                                    (16383, 16400)])
-def test_prefill_attention_tc_finds_one_far_key(far, n):
+@pytest.mark.parametrize("cut", [False, True])
+def test_prefill_attention_tc_finds_one_far_key(far, n, cut):
+    """One key among thousands stands out; with `cut` the stream is cut into pieces of four key tiles (the key
+    lies in one of many pieces, and the merge has to give that piece all the weight)."""
     H, K, d, P = 8, 2, 128, 64
     q, cache, bt, positions, seq_of, ks, vs = paged_case(H, K, d, P, [n], [16], "bfloat16", seed=far, num_pages=n // P + 4)
     q[:] = 0.5
     cache[bt[0, far // P], 0, :, far % P, :] = 8.0
     out = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
+    more = {}
+    if cut:
+        segments, items, slots = pieces_of(streams_of(tiles_for([n], [16]), 0), H, 4, whole_every=1 << 30)
+        assert slots > 0
+        more = dict(segments=dev(segments), items=dev(items), slots=slots)
     ops().prefill_attention_tc(dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(bt), dev(tiles_for([n], [16])),
-                               out, 0, 1.0 / math.sqrt(d))
+                               out, 0, 1.0 / math.sqrt(d), **more)
     got = out.float().cpu().numpy()
     for t in range(16):
         for h in range(H):

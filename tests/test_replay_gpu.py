@@ -330,15 +330,19 @@ def test_a_context_of_eight_thousand_tokens(dtype):
 
 
 @pytest.mark.parametrize("name", ["K", "L"])
-def test_row_tiles_in_pairs_and_alone(name, monkeypatch):
-    """The tcgen05 attention kernel takes two row tiles of 128 tokens per block where that gives enough blocks, one
-    where it does not (parts/attention.py, plan).  Tiny models always fall on the second side; here the first is
-    forced, and both give the plain implementation's logits for prompts of more than 256 tokens in portions."""
+def test_streams_of_keys_whole_and_cut(name, monkeypatch):
+    """The tcgen05 attention kernel takes a pair of row tiles with its whole stream of keys per block, or the host
+    cuts the streams where whole ones would leave SMs idle (parts/attention.py, plan_segments).  Tiny models always
+    fall on the first side; here the second is forced, down to one key tile a block, and both give the plain
+    implementation's logits for prompts of more than 256 tokens in portions."""
     import air_b200.parts.attention as attention
     folder = util.model_folder(name)
     streams = {f"{name}{i}": util.tokens_for(name, n, 70 + i) for i, n in enumerate((300, 129, 410, 257))}
     steps = util.trace_portions(streams, sizes=(260, 2, 131, 17, 300))
-    for sms in (0, attention.SMS):           # 0: "fewer blocks than half the SMs" never holds, so always pairs
+    for sms, cost, shortest in ((1, 3.5, 4), (1 << 20, 0.0, 1), (attention.SMS, 0.0, 2)):
         monkeypatch.setattr(attention, "SMS", sms)
+        monkeypatch.setattr(attention, "SEGMENT_COST", cost)
+        monkeypatch.setattr(attention, "MIN_SEGMENT", shortest)
+        assert (attention.plan_segments([5, 3], 2) is not None) == (sms > 1)
         got, _ = util.replay(folder, "bfloat16", steps, max_tokens=util.peak_tokens(steps), page_tokens=64)
         util.check_against_plain(got, folder, streams, "bfloat16")

@@ -318,3 +318,58 @@ def test_random_requests_and_settings_keep_every_promise(seed):
         pass
     assert eng.cache.free_pages() == eng.cache.num_pages and not eng.cache.sequences
     eng.cache.check()
+
+
+# ------------------------------------------------------------------ which attention block takes which keys
+def test_segments_cover_every_stream_exactly_once():
+    """Whatever the planner decides (whole items or cut streams), every (pair, head) has its stream covered from
+    0 to the end without a gap or an overlap, cut items have consecutive slots of their own, and a step that would
+    leave most SMs idle is cut."""
+    import numpy as np
+    from air_b200.parts.attention import MIN_SEGMENT, TO_THE_END, plan_segments
+    rng = np.random.default_rng(5)
+    cases = [([68, 68], 40), ([514], 28), ([4 * p + 4 for p in range(32)], 28), ([2], 2), ([], 4), ([1, 1, 1], 3),
+             ([129], 3), ([7, 300, 9], 5)]
+    cases += [(rng.integers(1, 600, size=rng.integers(1, 12)).tolist(), int(rng.integers(1, 41))) for _ in range(40)]
+    n_cut = 0
+    for streams, heads in cases:
+        planned = plan_segments(streams, heads)
+        if planned is None:          # one block per (pair, head): the kernel's own grid
+            continue
+        n_cut += 1
+        segments, items, slots = planned
+        assert segments.dtype == np.int32 and items.dtype == np.int32 and slots > 0
+        by_item, seen_slots = {}, set()
+        for pair, head, first, count, slot in segments.tolist():
+            by_item.setdefault((pair, head), []).append((first, count, slot))
+        assert set(by_item) == {(p, h) for p in range(len(streams)) for h in range(heads)}
+        cut = {}
+        for (pair, head), pieces in by_item.items():
+            pieces.sort()
+            at = 0
+            for j, (first, count, slot) in enumerate(pieces):
+                assert first == at
+                last = j == len(pieces) - 1
+                assert (count == TO_THE_END) == last
+                assert last or count >= MIN_SEGMENT
+                at += count
+                assert (slot == -1) == (len(pieces) == 1)
+                if slot >= 0:
+                    assert slot not in seen_slots
+                    seen_slots.add(slot)
+            assert pieces[-1][0] < streams[pair]
+            if len(pieces) > 1:
+                cut[(pair, head)] = [s for _, _, s in pieces]
+        assert seen_slots == set(range(slots))
+        assert {(p, h): list(range(s0, s0 + n)) for p, h, s0, n in items.tolist()} == cut
+    assert n_cut >= 10
+    # a 512-token portion behind 3,840 tokens at 40 heads: 80 items would hold 80 of 148 SMs for the whole stream
+    segments, items, slots = plan_segments([68, 68], 40)
+    assert len(items) == 80 and 148 <= len(segments) <= 2 * 148 + 80
+    work = [68 - first if count == TO_THE_END else count for _, _, first, count, _ in segments.tolist()]
+    assert work == sorted(work, reverse=True), "the longest segments are launched first"
+    # 224 equal items on 148 SMs: two rounds for some SMs unless the streams are cut
+    assert plan_segments([518] * 8, 28) is not None
+    # a whole prompt of 2,048 tokens: 224 items of graded length fill the SMs as they are; nothing to plan either
+    assert plan_segments([4 * p + 4 for p in range(8)], 28) is None
+    assert plan_segments([], 4) is None and plan_segments([2], 2) is None
