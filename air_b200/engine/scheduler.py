@@ -9,10 +9,11 @@ walk moves on from step to step so that nobody starves.
 
 The form is this engine's.  A cycle here is ONE step of one flat batch, so the plan is the batch itself: a
 list of `Entry` that `Engine.step` takes as it is.  Reservations are counted in cache pages.  A portion
-that the budget or the limit cuts (not the prompt's end) is shortened so that the next portion of the
-request starts on a row tile of the prefill kernels (`row_tile` positions), or at least on a page of the
-cache: the later portions' first key tile and first page are then whole.  A step that only decodes says which
-captured graph it will replay (`StepPlan.graph_size`; a step of 65 tokens runs the graph made for 96).
+that the budget or the limit cuts (not the prompt's end) is shortened so that the step's rows, decoding
+requests included, fill whole row tiles of the matrix products (`row_tile` rows; nine tenths of a prompt
+step's time are products, and 416 rows cost them what 512 do), or else so that the request's next portion
+starts on a page of the cache.  A step that only decodes says which captured graph it will replay
+(`StepPlan.graph_size`; a step of 65 tokens runs the graph made for 96).
 """
 from __future__ import annotations
 
@@ -82,15 +83,19 @@ class StepScheduler:
         return Admission(True, pages, "admitted")
 
     # ------------------------------------------------------------------ what runs
-    def _cut(self, position: int, count: int) -> int:
-        """A portion of `count` tokens from `position` that does not end its prompt: shortened to end
-        on a row tile, else on a page, where that leaves it any tokens."""
+    def _cut(self, position: int, count: int, rows_before: int) -> int:
+        """A portion of `count` tokens from `position` that does not end its prompt, in a step that holds
+        `rows_before` tokens already.  The matrix products work on tiles of `row_tile` rows of the whole step, so
+        the portion is shortened to make the step's rows a multiple of that (a budget that is one needs no
+        shortening), unless that would take more than half of it; else it ends on a page of its request, where
+        that leaves it any tokens."""
+        total = rows_before + count
+        fitting = total - total % self.row_tile - rows_before
+        if fitting > 0 and 2 * fitting >= count:
+            return fitting
         end = position + count
-        for edge in (self.row_tile, self.page_tokens):
-            aligned = end - end % edge
-            if aligned > position:
-                return aligned - position
-        return count
+        aligned = end - end % self.page_tokens
+        return aligned - position if aligned > position else count
 
     def plan(self, runnable: Sequence[Runnable]) -> StepPlan:
         plan = StepPlan()
@@ -114,7 +119,7 @@ class StepScheduler:
                 rest = len(r.prompt) - r.done
                 count = min(rest, self.portion_limit, left)
                 if count < rest:
-                    count = self._cut(r.done, count)
+                    count = self._cut(r.done, count, self.token_budget - left)
                 last = count == rest
                 plan.entries.append(Entry(r.request, r.prompt[r.done:r.done + count],
                                           [count - 1] if last and r.wants_token else []))

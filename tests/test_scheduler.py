@@ -66,15 +66,24 @@ def test_rotation_when_the_budget_does_not_reach_everybody():
     assert [s.plan(cands).entries[0].request for _ in range(4)] == ["x", "y", "x", "y"]
 
 
-def test_cut_portions_end_on_a_row_tile_or_a_page():
+def test_cut_portions_fill_the_step_s_row_tiles_or_end_on_a_page():
     s = StepScheduler(8, token_budget=300, portion_limit=300, page_tokens=16, row_tile=128)
-    # 300 tokens from position 40 would end at 340: shortened to end at 256, a row tile
-    assert s.plan([prompt("a", 1000, done=40)]).portions == [("a", 216)]
+    # 300 rows are 2.3 tiles of the products: shortened to 256
+    assert s.plan([prompt("a", 1000, done=40)]).portions == [("a", 256)]
     # a portion that ends its prompt is not shortened
     assert s.plan([prompt("a", 340, done=40)]).portions == [("a", 300)]
+    # decoding requests count: 3 single tokens and 253 of the prompt are 256 rows; a budget that is a multiple of
+    # the tile is used whole
+    assert s.plan([decoding("d0"), decoding("d1"), decoding("d2"), prompt("a", 1000, done=7)]).portions == [("a", 253)]
+    s = StepScheduler(8, token_budget=512, portion_limit=2048, page_tokens=64, row_tile=128)
+    assert s.plan([decoding(f"d{i}") for i in range(32)] + [prompt("a", 9000, done=3840)]).portions == [("a", 480)]
+    # with two prompts in a step each portion leaves the step on a tile's edge
+    s = StepScheduler(8, token_budget=512, portion_limit=200, page_tokens=64, row_tile=128)
+    assert s.plan([prompt("a", 9000), prompt("b", 9000)]).portions == [("a", 128), ("b", 128)]
+    # less than half a tile within reach: the portion ends on a page of its request, or stays as it is
     s = StepScheduler(8, token_budget=50, portion_limit=50, page_tokens=16, row_tile=128)
-    assert s.plan([prompt("a", 1000, done=100)]).portions == [("a", 28)]      # ends at 128
-    assert s.plan([prompt("a", 1000, done=130)]).portions == [("a", 46)]      # no tile edge within reach: page edge 176
+    assert s.plan([prompt("a", 1000, done=100)]).portions == [("a", 44)]      # ends at 144
+    assert s.plan([prompt("a", 1000, done=130)]).portions == [("a", 46)]      # ends at 176
     s = StepScheduler(8, token_budget=6, portion_limit=6, page_tokens=16, row_tile=128)
     assert s.plan([prompt("a", 1000, done=2)]).portions == [("a", 6)]         # no edge within reach: as it is
     # whatever the cuts, a prompt is run completely and in order
