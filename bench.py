@@ -325,13 +325,18 @@ def kernel_prefill_attention(cfg):
     heads, kv_heads, P = cfg["num_attention_heads"], cfg["num_key_value_heads"], 64
 
     def case(H, K, prior, portion):
-        pages = -(-(prior + portion) // P)
-        cache = (torch.randn(pages + 1, 2, K, P, d, device="cuda") * 0.5).to(torch.bfloat16)
-        table = torch.arange(pages, dtype=torch.int32, device="cuda")[None, :].contiguous()
-        q = (torch.randn(portion, H, d, device="cuda") * 0.5).to(torch.bfloat16)
-        tiles = [[0, i, prior + i, min(16, portion - i)] for i in range(0, portion, 16)]
-        tiles += [[0, 0, 0, 0]] * (-len(tiles) % 16)
-        streams = [(prior + min(portion, g + 256) - 1) // 64 + 1 for g in range(0, portion, 256)]
+        """One request, or several (lists): `portion` new tokens each behind `prior` tokens."""
+        priors, portions = (prior, portion) if isinstance(prior, (list, tuple)) else ([prior], [portion])
+        most = max(-(-(a + b) // P) for a, b in zip(priors, portions))
+        cache = (torch.randn(most * len(priors) + 1, 2, K, P, d, device="cuda") * 0.5).to(torch.bfloat16)
+        table = torch.arange(most * len(priors), dtype=torch.int32, device="cuda").view(len(priors), most).contiguous()
+        q = (torch.randn(sum(portions), H, d, device="cuda") * 0.5).to(torch.bfloat16)
+        tiles, streams, row = [], [], 0
+        for slot, (a, n) in enumerate(zip(priors, portions)):
+            tiles += [[slot, row + i, a + i, min(16, n - i)] for i in range(0, n, 16)]
+            tiles += [[slot, 0, 0, 0]] * (-len(tiles) % 16)
+            streams += [(a + min(n, g + 256) - 1) // 64 + 1 for g in range(0, n, 256)]
+            row += n
         return q, cache, table, torch.tensor(tiles, dtype=torch.int32, device="cuda"), streams
 
     def timed(q, cache, table, tiles, cut=None):
@@ -364,17 +369,21 @@ def kernel_prefill_attention(cfg):
         q, cache, table, tiles, streams = case(148, 4, prior, 256)
         print(f"  stream of {streams[0]:4d} key tiles: {timed(q, cache, table, tiles):7.1f}")
     print(f"{heads} query heads, {kv_heads} kv heads: whole streams per block | the planner's cut")
-    for prior, portion in ((0, 1024), (0, 2048), (0, 8192), (2048, 2048), (3840, 512), (32768, 128), (32768, 512)):
+    for prior, portion in ((0, 1024), (0, 2048), (0, 8192), (2048, 2048), (3840, 512), (32768, 128), (32768, 512),
+                           ([0, 0, 0, 0], [512, 2048, 256, 1024]), ([0, 1024, 8192, 0], [1024, 512, 128, 512])):
         q, cache, table, tiles, streams = case(heads, kv_heads, prior, portion)
-        flops = 4.0 * d * heads * sum(min(prior + i + 1, prior + portion) for i in range(portion))
+        several = isinstance(prior, list)
+        flops = sum(4.0 * d * heads * sum(a + i + 1 for i in range(n))
+                    for a, n in (zip(prior, portion) if several else [(prior, portion)]))
         whole = timed(q, cache, table, tiles)
         cut = plan_segments(streams, heads)
-        line = f"  {portion:5d} tokens behind {prior:5d}: {whole:8.1f} us ({flops / whole / 1e6:6.0f} TFLOP/s)"
+        name = f"{portion} behind {prior}" if several else f"{portion:5d} tokens behind {prior:5d}"
+        line = f"  {name}: {whole:8.1f} us ({flops / whole / 1e6:6.0f} TFLOP/s)"
         if cut is not None:
             t = timed(q, cache, table, tiles, cut)
             line += f" | {t:8.1f} us ({flops / t / 1e6:6.0f} TFLOP/s; {len(cut[0])} blocks, {cut[2]} partial results merged)"
         else:
-            line += " | not cut"
+            line += " | as it is"
         print(line)
     return 0
 
