@@ -7,7 +7,7 @@ src/cuda/cuda_backend.cu with six sources of its core (model, storage, architect
 sampling, generation, verification) links against cudart and cuBLAS alone.  This script
 
   * copies AIR's `include/` and `src/` into baseline/_ref/ (git-ignored) when they are not there,
-    from --reference or $AIR_REFERENCE_DIR,
+    from --reference, $AIR_REFERENCE_DIR or a folder `reference` beside this repository,
   * compiles them with nvcc for sm_100 together with baseline/air_cuda_driver.cpp (this
     repository's driver, which only calls AIR's public classes),
   * `check`: runs the golden tiny model of tests/golden/ through AIR's CUDA executor on the GPU and
@@ -50,10 +50,12 @@ def fetch(reference=None):
     """AIR's sources in baseline/_ref/, copied unmodified."""
     if os.path.exists(os.path.join(REF, "src", "cuda", "cuda_backend.cu")):
         return
-    reference = reference or os.environ.get("AIR_REFERENCE_DIR")
-    if not reference or not os.path.exists(os.path.join(reference, "src", "cuda", "cuda_backend.cu")):
+    beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")      # a checkout next to this repository
+    reference = next((r for r in (reference, os.environ.get("AIR_REFERENCE_DIR"), beside)
+                      if r and os.path.exists(os.path.join(r, "src", "cuda", "cuda_backend.cu"))), None)
+    if reference is None:
         raise Unavailable("AIR's sources are not in baseline/_ref and no checkout was given "
-                          "(--reference DIR or AIR_REFERENCE_DIR)")
+                          "(--reference DIR, AIR_REFERENCE_DIR, or a folder `reference` beside the repository)")
     os.makedirs(REF, exist_ok=True)
     for sub in ("include", "src"):
         shutil.copytree(os.path.join(reference, sub), os.path.join(REF, sub), dirs_exist_ok=True)
