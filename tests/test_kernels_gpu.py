@@ -103,7 +103,7 @@ def test_logits_post_adds_scales_and_caps():
 
 @pytest.mark.parametrize("E", [200, 1000, 3584, 5120, 9000])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("R", [37, 150])            # (few rows and many take different kernels)
+@pytest.mark.parametrize("R", [37, 150, 1100])      # (few rows, many, and very many take different kernels)
 def test_add_rmsnorm(E, dtype, R):
     g = torch.Generator().manual_seed(E)
     h = torch.randn(R, E, generator=g) * 3
@@ -130,6 +130,11 @@ def test_add_rmsnorm(E, dtype, R):
     out3 = torch.empty(3, E, dtype=DT[dtype], device="cuda")
     ops().add_rmsnorm(dev(h.clone()), dev(delta), dev(w), eps, out3, rows=dev(rows))
     assert same(out3.cpu(), out.cpu()[rows.long()])
+    # nothing to add (the stream as the products' epilogues left it): for many rows the kernel that the copy
+    # engine feeds, the same bits again
+    out5 = torch.full((R, E), 5.0, dtype=DT[dtype], device="cuda")
+    ops().add_rmsnorm(hd, None, dev(w), eps, out5)
+    assert torch.equal(hd, before) and same(out5.cpu(), out.cpu())
     # partial sums of a split product are added in their order
     three = torch.randn(3, R, E, generator=g)
     h3 = dev(h.clone())
@@ -168,7 +173,7 @@ def rope_reference(x, positions, theta, rot):
 @pytest.mark.parametrize("H,K,d,rot", [(5, 1, 48, 48), (6, 3, 80, 80), (4, 2, 128, 64), (3, 3, 16, 16), (28, 4, 128, 128),
                                        (40, 8, 128, 128)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n0,n1", [(14, 9), (70, 40)])       # (few tokens and many take different kernels)
+@pytest.mark.parametrize("n0,n1", [(14, 9), (70, 40), (700, 400)])       # (few tokens, many and very many take different kernels)
 def test_qkv_rope_store(H, K, d, rot, dtype, n0, n1):
     from air_b200.parts.rope import RopeHalf
     from air_b200.parts.spec import PartSpec
@@ -181,10 +186,17 @@ def test_qkv_rope_store(H, K, d, rot, dtype, n0, n1):
     positions = np.array(list(range(30, 30 + n0)) + list(range(n1)), dtype=np.int32)
     token_seq = np.array([0] * n0 + [1] * n1, dtype=np.int32)
     block_table = np.array([[7, 2, 9, 0, 11, 5, 3], [4, 8, 1, -1, -1, -1, -1]], dtype=np.int32)
-    pe = RopeHalf(PartSpec("rope_half", {"rotary_dim": rot, "theta": theta, "max_positions": 128}))
+    pages = 12
+    if T > 112:         # more pages than the hand-made table has: shuffled ones
+        need = [-(-(30 + n0) // P), -(-n1 // P)]
+        pages = sum(need) + 2
+        perm = rng.permutation(pages)
+        block_table = np.full((2, max(need)), -1, dtype=np.int32)
+        block_table[0, :need[0]], block_table[1, :need[1]] = perm[:need[0]], perm[need[0]:sum(need)]
+    pe = RopeHalf(PartSpec("rope_half", {"rotary_dim": rot, "theta": theta, "max_positions": 30 + n0 + 8}))
     pe.load({}, Runtime(torch.device("cuda"), DT[dtype], P))
     q_out = torch.zeros(T, H, d, dtype=DT[dtype], device="cuda")
-    cache = torch.zeros(12, 2, K, P, d, dtype=DT[dtype], device="cuda")
+    cache = torch.zeros(pages, 2, K, P, d, dtype=DT[dtype], device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     ops().qkv_rope_store(dev(qkv), dev(bias), pe.table(), dev(positions), dev(token_seq), dev(block_table),
                          q_out, cache, H, K, d, status=status)
