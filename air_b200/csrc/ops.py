@@ -535,13 +535,20 @@ def small_rows(M: int, N: int, bn: int, epi: int) -> bool:
 TC_ATTENTION_HEAD_DIMS = (64, 128)
 
 
+def prefill_attention_scratch(slots: int, head_dim: int, device):
+    """Where the segments of cut items leave their partial sums: (float32 [slots, 256, d], float32 [slots, 256, 2])."""
+    return (torch.empty((slots, 2 * TILE_GROUP * 16, head_dim), dtype=torch.float32, device=device),
+            torch.empty((slots, 2 * TILE_GROUP * 16, 2), dtype=torch.float32, device=device))
+
+
 def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, status=None, segments=None, items=None,
-                         slots=0):
+                         slots=0, scratch=None):
     """bfloat16 causal attention with both products on the tcgen05 tensor cores (see
     attention_prefill_tc.cu); arguments as prefill_attention; head size 64 or 128.
     segments [n, 5] int32 (pair of the list, head, first key tile, key tiles, slot or -1): which block takes which
     part of which pair's stream of keys, instead of one block per pair and head; items [m, 4] int32 (pair, head,
-    first slot, slots): the (pair, head)s whose segments write partial sums into `slots` slots, merged here."""
+    first slot, slots): the (pair, head)s whose segments write partial sums into `slots` slots, merged here.
+    scratch: what prefill_attention_scratch gives (or None to allocate): the layers of a step can share it."""
     T, H, d = q.shape
     K, P = cache.shape[2], cache.shape[3]
     _req(q, "q", (torch.bfloat16,))
@@ -564,8 +571,11 @@ def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, statu
         if slots:
             _req(items, "items", _I32, (None, 4))
             n_items = items.shape[0]
-            part_o = torch.empty((slots, 2 * TILE_GROUP * 16, d), dtype=torch.float32, device=q.device)
-            part_ml = torch.empty((slots, 2 * TILE_GROUP * 16, 2), dtype=torch.float32, device=q.device)
+            part_o, part_ml = scratch if scratch is not None else prefill_attention_scratch(slots, d, q.device)
+            _req(part_o, "scratch[0]", (torch.float32,), (None, 2 * TILE_GROUP * 16, d))
+            _req(part_ml, "scratch[1]", (torch.float32,), (None, 2 * TILE_GROUP * 16, 2))
+            if part_o.shape[0] < slots or part_ml.shape[0] < slots:
+                raise KernelError("prefill_attention_tc: the scratch tensors hold fewer slots than the segments name")
     _check(_get("air_prefill_attention_tc")(
         q.data_ptr(), T, cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
         tiles.data_ptr(), tiles.shape[0], _ptr(segments), 0 if segments is None else segments.shape[0],

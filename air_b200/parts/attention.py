@@ -250,8 +250,12 @@ class Attention(Mixer):
             if plan.tiles.shape[0] == 0:
                 pass
             elif d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
+                if plan.slots and getattr(plan, "scratch", None) is None:
+                    # (the step's layers run one after the other on one stream and share the partial sums' memory)
+                    plan.scratch = ops.prefill_attention_scratch(plan.slots, d, q.device)
                 ops.prefill_attention_tc(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status,
-                                         segments=plan.segments, items=plan.items, slots=plan.slots)
+                                         segments=plan.segments, items=plan.items, slots=plan.slots,
+                                         scratch=getattr(plan, "scratch", None))
             else:
                 ops.prefill_attention(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status)
         else:
