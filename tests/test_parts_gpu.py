@@ -581,6 +581,74 @@ def test_a_toy_block_with_a_norm_after_each_part():
         engine.cache.check()
 
 
+def test_a_toy_block_with_mixer_and_feed_forward_side_by_side():
+    """A third arrangement, again a block class of the test alone: ONE norm, and the mixer and the feed-forward
+    both read its rows; their outputs are added to the stream together (three roles).  Whatever form the two
+    outputs have (rows, or partial sums of a split product), the base class's add_delta completes the stream with
+    the first and the block hands the second on."""
+    from air_b200.engine.batch import Entry
+    from air_b200.parts import (Block, Norm, PartSpec, BlockSpec, ModelSpec, RunStep, register_block,
+                                register_architecture, registry)
+
+    @register_block("toy_side_by_side")
+    class ToySideBySide(Block):
+        def __init__(self, spec):
+            super().__init__(spec)
+            build = lambda reg, role: reg.get(spec.part(role).kind)(spec.part(role), spec.name(role))
+            self.norm = build(registry.NORMS, "norm")
+            self.mixer, self.ff = build(registry.MIXERS, "mixer"), build(registry.FEED_FORWARDS, "ff")
+
+        def parts(self):
+            return (self.norm, self.mixer, self.ff)
+
+        def cache_needs(self):
+            return self.mixer.cache_needs()
+
+        def forward(self, h, pending, ctx, cache, owns_cache=True):
+            ctx.residual = None
+            x = self.norm.forward(h, pending)
+            a = self.mixer.forward(x, ctx, cache, owns_cache)
+            f = self.ff.forward(x, ctx)
+            Norm.add_delta(h, a)
+            return h, f
+
+    eps = 1e-6
+
+    def toy_spec(c):
+        rms = PartSpec("rms", {"size": c.hidden_size, "eps": eps})
+        layers = tuple(BlockSpec("toy_side_by_side", f"model.layers.{i}.",
+                                 {"norm": rms, "mixer": attention_spec(c.hidden_size, 6, 3, 16, False),
+                                  "ff": PartSpec("swiglu", {"hidden": c.hidden_size, "intermediate": 80})})
+                       for i in range(c.num_hidden_layers))
+        return ModelSpec(c.architecture, c.hidden_size, c.vocab_size, 128, layers,
+                         tuple(RunStep(i) for i in range(c.num_hidden_layers)), rms, "model.embed_tokens.weight",
+                         "model.norm.", "lm_head.weight")
+
+    def oracle(w, tokens):
+        h = plain.embed(w["model.embed_tokens.weight"], np.asarray(tokens))
+        for i in range(3):
+            p = f"model.layers.{i}."
+            x = plain.rms_norm(h, w[p + "norm.weight"], eps)
+            h = (h + plain_attention(x, w, p + "mixer.", 6, 3, 16) + plain_swiglu(x, w, p + "ff.")).astype(np.float32)
+        return plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+    register_architecture("ToySideBySideForCausalLM", ToyConfig, toy_spec)
+    cfg = {"architectures": ["ToySideBySideForCausalLM"], "hidden_size": 96, "vocab_size": 83, "num_hidden_layers": 3}
+    a = [t % 83 for t in util.tokens_for("A", 40, 7)]
+    b = [t % 83 for t in util.tokens_for("A", 23, 8)]
+    for dtype, tol in (("float32", 3e-5), ("bfloat16", 5e-2)):
+        engine, w = engine_and_weights(cfg, seed=13, dtype=dtype)
+        assert type(engine.model.blocks[0]).__name__ == "ToySideBySide"
+        want_a, want_b = oracle(w, a), oracle(w, b)
+        scale = max(1.0, np.abs(want_a).max())
+        whole = engine.step([Entry("w", a, range(40))]).cpu().numpy()
+        engine.finish("w")
+        assert np.abs(whole - want_a).max() < tol * scale
+        got_a, got_b = in_portions(engine, a, b)
+        assert np.abs(got_a - want_a).max() < tol * scale and np.abs(got_b - want_b).max() < tol * scale
+        engine.cache.check()
+
+
 def test_a_toy_mixer_that_pages_one_latent_per_token():
     """Another kind of cache, defined here: instead of keys and values a mixer keeps ONE short vector per
     token, in pages of a shape of its own.  The need states the shape; the cache manager, which knows no
