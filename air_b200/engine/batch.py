@@ -65,35 +65,45 @@ def build_context(entries: Sequence[Entry], cache, device, status=None, planners
     """Packs the batch.  `cache` is the CacheManager; every request is open and has its pages
     reserved for this step.  `planners`: the parts of the model that plan on the host, one per plan
     key (Model.planners()); their arrays travel in the same copy as the batch."""
-    ids: List[np.ndarray] = []
-    pos: List[np.ndarray] = []
-    tseq: List[np.ndarray] = []
+    # (single next tokens, the many entries of a mixed step, are written as plain numbers: an array per entry
+    # costs more than the whole rest of the packing)
+    T = sum(len(e.tokens) for e in entries)
+    S = len(entries)
+    ids = np.empty(T, dtype=np.int32)
+    pos = np.empty(T, dtype=np.int32)
+    tseq = np.empty(T, dtype=np.int32)
     q_start = [0]
     kv_len: List[int] = []
     slots: List[int] = []
     lengths: List[int] = []
     rows: List[int] = []
     row_slots: List[int] = []
+    at = 0
     for e in entries:
         seq = cache.sequences[e.request]
         n = len(e.tokens)
-        t = np.asarray(e.tokens, dtype=np.int64)
-        ids.append(np.where(t >= 0, t, -(seq.slot + 1)).astype(np.int32))
-        pos.append(np.arange(seq.length, seq.length + n, dtype=np.int32))
-        tseq.append(np.full(n, seq.slot, dtype=np.int32))
+        if n == 1:
+            t = int(e.tokens[0])
+            ids[at] = t if t >= 0 else -(seq.slot + 1)
+            pos[at] = seq.length
+            tseq[at] = seq.slot
+        elif n:
+            t = np.asarray(e.tokens, dtype=np.int64)
+            ids[at:at + n] = np.where(t >= 0, t, -(seq.slot + 1))
+            pos[at:at + n] = np.arange(seq.length, seq.length + n, dtype=np.int32)
+            tseq[at:at + n] = seq.slot
         for w in e.want:
             if not (0 <= w < n):
                 raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
-            rows.append(q_start[-1] + int(w))
+            rows.append(at + int(w))
             row_slots.append(seq.slot)
-        q_start.append(q_start[-1] + n)
+        at += n
+        q_start.append(at)
         kv_len.append(seq.length + n)
         lengths.append(seq.length)
         slots.append(seq.slot)
-    T, S = q_start[-1], len(entries)
     cache.flush_tables()
-    empty = np.zeros(0, dtype=np.int32)
-    sections = [np.concatenate(x) if x else empty for x in (ids, pos, tseq)]
+    sections = [ids, pos, tseq]
     sections += [np.asarray(x, dtype=np.int32) for x in (q_start, kv_len, slots, rows, row_slots)]
     planned = []      # (plan key, name, shape, section index), and the plans' host values
     values = {}

@@ -294,6 +294,9 @@ def mixed_step(engine, decoders, portion, context, repeats, torch, Entry):
         open_requests(engine, requests, context - 1)
         open_requests(engine, ["portion"], prior)
         entries = [Entry(r, [5 + i], [0]) for i, r in enumerate(requests)] + [Entry("portion", tokens, [])]
+        # (the pages of requests that earlier steps brought to their lengths are in the device's tables already:
+        # without this the timed step would send the thousands of entries that opening the requests here made)
+        engine.cache.flush_tables()
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
