@@ -141,21 +141,20 @@ class Attention(Mixer):
             prefix += 1
         tiles, key_tiles = [], []
         for i in range(prefix, len(batch.counts)):
-            n = batch.counts[i]
+            n, pos0 = batch.counts[i], batch.lengths[i]
+            pairs = -(-n // 256)
+            first = np.arange(pairs * 16, dtype=np.int32) * 16          # the entry's 16-token tiles, pairs filled up
+            rows = np.clip(n - first, 0, 16)
+            tile = np.zeros((pairs * 16, 4), dtype=np.int32)
+            tile[:, 0] = batch.slots[i]
+            tile[:, 1] = np.where(rows > 0, batch.q_start[i] + first, 0)
+            tile[:, 2] = np.where(rows > 0, pos0 + first, 0)
+            tile[:, 3] = rows
+            tiles.append(tile)
             for g0 in range(0, n, 256):
-                rows = min(256, n - g0)
-                count = -(-rows // 16)
-                tile = np.zeros((16, 4), dtype=np.int32)
-                tile[:, 0] = batch.slots[i]
-                first = g0 + np.arange(count, dtype=np.int32) * 16
-                tile[:count, 1] = batch.q_start[i] + first
-                tile[:count, 2] = batch.lengths[i] + first
-                tile[:count, 3] = np.minimum(16, n - first)
-                tiles.append(tile)
                 # the pair's keys: from the first one that its first row sees to its last row's own
-                pos0 = batch.lengths[i] + g0
-                lowest = max(0, pos0 - self.window + 1) if self.window else 0
-                key_tiles.append((pos0 + rows - 1) // 64 + 1 - lowest // 64)
+                lowest = max(0, pos0 + g0 - self.window + 1) if self.window else 0
+                key_tiles.append((pos0 + min(n, g0 + 256) - 1) // 64 + 1 - lowest // 64)
         tiles = np.concatenate(tiles) if tiles else np.zeros((0, 4), dtype=np.int32)
         arrays, values = {"tiles": tiles}, {"decode_prefix": prefix, "segments": None, "items": None, "slots": 0}
         cut = plan_segments(key_tiles, self.heads)
