@@ -391,6 +391,74 @@ def kernel_prefill_attention(cfg):
     return 0
 
 
+def kernel_prompt_elementwise(cfg, rows):
+    """The memory-bound kernels of a prompt step alone at the shape's widths, each beside a plain copy of the same
+    bytes: ten launches replayed as a CUDA graph (data in L2), and the same with a 512 MB buffer written before
+    each launch (data from memory; the time of the writes alone is subtracted)."""
+    import statistics
+    import torch
+    from air_b200.csrc import ops
+    E, H, K = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d, I, P, T = cfg.get("head_dim", E // H), cfg["intermediate_size"], 64, rows
+    big = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def graph_time(calls, reps=10):
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                for c in calls:
+                    c()
+        graph.replay()
+        torch.cuda.synchronize()
+        us = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 1e3 / reps)
+        return statistics.median(us)
+
+    flush = lambda: big.zero_()
+    t_flush = graph_time([flush])
+
+    def report(name, f, nbytes):
+        warm, cold = graph_time([f]), graph_time([flush, f]) - t_flush
+        print(f"  {name:44s} {nbytes / 1e6:7.1f} MB  in L2 {warm:6.1f} us ({nbytes / warm / 1e6:5.2f} TB/s)  "
+              f"from memory {cold:6.1f} us ({nbytes / cold / 1e6:5.2f} TB/s)", flush=True)
+    print(f"{T} rows: hidden {E}, {H}/{K} heads of {d}, intermediate {I}")
+    h = torch.randn(T, E, device="cuda")
+    w = torch.ones(E, dtype=torch.bfloat16, device="cuda")
+    x = torch.empty(T, E, dtype=torch.bfloat16, device="cuda")
+    report("copy float32 -> bfloat16 [rows, hidden]", lambda: x.copy_(h), T * E * 6)
+    report("add_rmsnorm, nothing to add", lambda: ops.add_rmsnorm(h, None, w, 1e-6, x), T * E * 6)
+    delta = torch.randn(T, E, device="cuda")
+    report("add_rmsnorm, a float32 delta", lambda: ops.add_rmsnorm(h, delta, w, 1e-6, x), T * E * 14)
+    W = (H + 2 * K) * d
+    qkv, bias = torch.randn(T, W, device="cuda"), torch.randn(W, device="cuda")
+    table = torch.randn(T + 8, d, device="cuda")
+    positions = torch.arange(T, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(T, dtype=torch.int32, device="cuda")
+    pages = -(-T // P)
+    bt = torch.arange(pages, dtype=torch.int32, device="cuda")[None, :].contiguous()
+    q = torch.empty(T, H, d, dtype=torch.bfloat16, device="cuda")
+    cache = torch.zeros(pages, 2, K, P, d, dtype=torch.bfloat16, device="cuda")
+    report("bias + rotation + cache write", lambda: ops.qkv_rope_store(qkv, bias, table, positions, seq, bt, q, cache, H, K, d),
+           T * W * 6)
+    y = torch.empty(T, W, dtype=torch.bfloat16, device="cuda")
+    report("copy float32 -> bfloat16 [rows, (H + 2K) d]", lambda: y.copy_(qkv), T * W * 6)
+    gu = torch.randn(T, 2 * I, device="cuda").to(torch.bfloat16)
+    act = torch.empty(T, I, dtype=torch.bfloat16, device="cuda")
+    report("silu(gate) * up, blocks of 128", lambda: ops.silu_mul(gu, act, block=128), T * I * 6)
+    z = torch.empty(T, 2 * I, dtype=torch.bfloat16, device="cuda")
+    report("copy bfloat16 [rows, 2 x intermediate]", lambda: z.copy_(gu), T * I * 8)
+    return 0
+
+
 def reference_arm(args, cfg, context):
     """EmersonDowell/AIR's CUDA executor on the same shape: its own prefill and step_greedy_batch."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -460,7 +528,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling the decode step alone")
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
-    ap.add_argument("--kernel", default="", help="prefill_attention: time that kernel alone at the shape's heads and exit")
+    ap.add_argument("--kernel", default="", help="prefill_attention, or prompt_elementwise (at --prefill-tokens rows): time those kernels alone and exit")
     ap.add_argument("--timeline", action="store_true", help="also print the kernels' spans inside the decode graph and in the prefill step")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -478,8 +546,10 @@ def main():
     if args.impl == "reference":
         return reference_arm(args, cfg, context)
     if args.kernel:
+        if args.kernel == "prompt_elementwise":
+            return kernel_prompt_elementwise(cfg, args.prefill_tokens)
         if args.kernel != "prefill_attention":
-            print(json.dumps({"error": f"--kernel {args.kernel}: only prefill_attention is timed alone"}))
+            print(json.dumps({"error": f"--kernel {args.kernel}: prefill_attention and prompt_elementwise are timed alone"}))
             return 2
         return kernel_prefill_attention(cfg)
     layers_of_model = cfg["num_hidden_layers"]
