@@ -810,7 +810,9 @@ AIR_API int air_qkv_rope_store(const void* qkv, int in_dtype, int parts, const v
         if (rot == d && d % 8 == 0) {
             // few tokens: one item per thread, so that every load of the block is in flight at once
             const int items = (write_kv ? H + 2 * K : H) * (d / 8);
-            const int threads = T <= 64 ? min(ROPE_THREADS, max(128, (items + 31) / 32 * 32)) : 256;
+            // (from a thousand tokens on, blocks of 128 threads: sixteen to an SM, so that 2,048 tokens run in one round of
+            // blocks, 9.7 against 11.7 us; with fewer tokens the wider block is faster, 4.2 against 5.1 us at 544)
+            const int threads = T <= 64 ? min(ROPE_THREADS, max(128, (items + 31) / 32 * 32)) : (T >= 1024 ? 128 : 256);
             return launch(T <= 64 ? qkv_rope_store_vec4_kernel<TI, TB, TO> : qkv_rope_store_vec4_many_kernel<TI, TB, TO>, T,
                           threads, 0, stream, (const TI*)qkv, parts,
                           (size_t)T * (H + 2 * K) * d, (const TB*)bias, table, positions, token_seq, block_table,
