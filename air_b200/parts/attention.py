@@ -16,8 +16,9 @@ from .registry import register_mixer, POSITION_ENCODINGS
 
 # What a block of the tcgen05 attention kernel costs beside its key tiles (tensor memory, barriers, the chain of
 # loads to its first keys, the pipeline's fill and the write of its rows), in key tiles of one pair of row tiles:
-# with one block per SM a stream of n key tiles takes 11.5 + 1.03 n us, of which about 3.5 us are the launch.  The
-# shortest piece of a stream that is worth a block of its own is as long.
+# with one block per SM a stream of n key tiles takes 7.5 + 1.03 n us, of which about 3 us are the launch, and a
+# block that writes partial sums for the merge a few more.  The shortest piece of a stream that is worth a block of
+# its own is as long.
 SEGMENT_COST = 8.0
 MIN_SEGMENT = 8
 TO_THE_END = 1 << 30
@@ -31,20 +32,21 @@ def plan_segments(key_tiles, heads: int, sms: int = 0):
     items' streams are laid end to end, heaviest first, and cut into `sms` equal ranges; a range's share of an item
     is a segment, one block.  Segments of a cut item write partial sums (slots), which a second kernel merges.
 
-    Returns None (whole items: nothing to say) or (segments [n, 5] int32: pair, head, first key
-    tile, key tiles (TO_THE_END for an item's last), slot or -1, longest first; items [m, 4] int32: pair, head,
-    first slot, slots of the cut items; number of slots).  Every item's segments cover its stream exactly once whatever the kernel takes the stream's length to
-    be: the first starts at 0 and the last runs to the end."""
+    Returns None (whole items: nothing to say) or (segments [n, 5] int32: pair, head, first key tile, key tiles
+    (TO_THE_END for an item's last), slot or -1, longest first; items [m, 4] int32: pair, head, first slot, slots of
+    the cut items; number of slots).  Every item's segments cover its stream exactly once whatever the kernel takes
+    the stream's length to be: the first starts at 0 and the last runs to the end."""
     sms = sms or SMS
     pairs = len(key_tiles)
     if pairs == 0 or heads <= 0:
         return None
     n = pairs * heads
     total = heads * sum(key_tiles)
-    # whole items: the longest one, or all of them spread evenly; cut streams: equal ranges, 1.4 blocks per SM on
-    # the average, and the merge (measured: 81.5 against 64.5 us for 80 items of 68 key tiles, 372 against 90 us
-    # for 28 items of 514; 28.6 against 36.9 us for a whole prompt of 1,024 tokens, which is not cut)
-    # (some SM takes at least ceil(n / sms) items: the lightest ones at best)
+    # Whole items take as long as the longest one, or as all of them spread evenly, or as the items of the SM that
+    # has most of them (some SM takes at least ceil(n / sms) items: the lightest ones at best).  Cut streams: equal
+    # ranges, 1.4 blocks per SM on the average, and the merge.  (Measured: 81.5 against 64.5 us for 80 items of 68
+    # key tiles, 372 against 90 us for 28 items of 514; 28.6 against 36.9 us for a whole prompt of 1,024 tokens,
+    # which is not cut.)
     most, lightest = -(-n // sms), 0.0
     for tiles in sorted(key_tiles):
         lightest += min(most, heads) * (tiles + SEGMENT_COST)
